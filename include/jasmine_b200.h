@@ -1,0 +1,265 @@
+/*
+ * jasmine_b200 — C ABI of the B200 (sm_100a) implementation of jasmine's
+ * transformer-inference hot path.
+ *
+ * jasmine (the reference) is a header-only C++20 library with no FFI of its
+ * own: its "plugin surface" is the template/concept surface of its headers.
+ * The C++20 headers under include/jasmine/ keep those spellings and lower every
+ * materialisation point (`.clone()`, conversion to mat_t, `forward`) to one of
+ * the calls declared here.  Each entry point cites the reference code whose
+ * arithmetic it replaces (paths are relative to the reference project root).
+ *
+ * Conventions
+ *  - Every call returns a jsm_status; on failure a thread-local message is
+ *    available through jsm_last_error().
+ *  - All pointers named d_* / jsm_mat::data are DEVICE pointers; h_* are host.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *    Calls are asynchronous on that stream unless stated otherwise.
+ *  - No call falls back to the CPU.  Without a usable device every compute call
+ *    returns JSM_CUDA.
+ */
+#ifndef JASMINE_B200_H_
+#define JASMINE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef enum jsm_status {
+    JSM_OK = 0,
+    JSM_INVALID_ARG = 1, /* maps to std::invalid_argument (mat_express_t.hpp:709-712) */
+    JSM_SHAPE = 2,       /* maps to std::runtime_error   (mat_mha_t.hpp:268-269)      */
+    JSM_OOM = 3,
+    JSM_CUDA = 4,
+    JSM_NCCL = 5,
+    JSM_TIMEOUT = 6, /* a bounded device-side wait ran out */
+    JSM_UNSUPPORTED = 7
+} jsm_status;
+
+typedef enum jsm_dtype { JSM_F32 = 0, JSM_BF16 = 1, JSM_I32 = 2 } jsm_dtype;
+
+/* ---- library ---------------------------------------------------------- */
+const char* jsm_last_error(void);
+int jsm_version(void);
+/* Number of CUDA devices visible; 0 (and JSM_CUDA) when there is none. */
+jsm_status jsm_device_count(int* count);
+/* Count of kernels launched by this library in this process (all threads). */
+uint64_t jsm_launch_count(void);
+
+/* ---- device memory (mat_t storage: mat_t.hpp:30-69 new[]/memset/delete[]) */
+jsm_status jsm_malloc(void** d_ptr, size_t bytes); /* zero-filled like init_matrix */
+jsm_status jsm_free(void* d_ptr);
+jsm_status jsm_upload(void* d_dst, const void* h_src, size_t bytes, void* stream);
+jsm_status jsm_download(void* h_dst, const void* d_src, size_t bytes, void* stream); /* synchronises */
+jsm_status jsm_memset(void* d_dst, int byte, size_t bytes, void* stream);
+jsm_status jsm_stream_sync(void* stream);
+
+/* ---- seeded synthetic data -------------------------------------------- */
+/* Counter-based generator, bit-identical on host and device: element i of
+ * tensor (seed, tensor_id).  dist 0: normal(mean=a, std=b) (12-uniform sum),
+ * dist 1: uniform [a, b), dist 2: integer uniform [a, b) (I32 only).
+ * jsm_fill_host writes the same values to host memory (f32 / bf16 bits / i32). */
+jsm_status jsm_fill(void* d_dst, jsm_dtype dtype, size_t n, uint64_t seed, uint64_t tensor_id, int dist,
+                    float a, float b, void* stream);
+jsm_status jsm_fill_host(void* h_dst, jsm_dtype dtype, size_t n, uint64_t seed, uint64_t tensor_id, int dist,
+                         float a, float b);
+jsm_status jsm_convert(void* d_dst, jsm_dtype dst_dtype, const void* d_src, jsm_dtype src_dtype, size_t n,
+                       void* stream);
+
+/* ---- matrix operand ----------------------------------------------------
+ * A strided 2-D window.  Element (r, c) lives at data[(r % rows) * row_stride +
+ * (c % cols) * col_stride]: the modulo broadcast of mat_t::operator()
+ * (mat_t.hpp:302-320).  A mat_view_t (mat_view_t.hpp:7-135) is the same struct
+ * with an offset pointer; a transposed view swaps the strides. */
+typedef struct jsm_mat {
+    void* data;
+    int32_t rows, cols;
+    int64_t row_stride, col_stride; /* in elements */
+    int32_t dtype;                  /* jsm_dtype */
+} jsm_mat;
+
+/* ---- expression programs (mat_express_t.hpp:35-509) --------------------
+ * An expression tree is lowered by the header layer to a postfix program over
+ * a value stack (depth <= 8).  Result shape = max of the leaf shapes
+ * (mat_express_t.hpp:51-59). */
+typedef enum jsm_op {
+    JSM_OP_LEAF = 0, /* push leaves[arg](r, c)                            */
+    JSM_OP_IMM = 1,  /* push imm (scalar operand, storage_selector :18-33) */
+    JSM_OP_ADD = 2,  /* mat_add_t :189-223  */
+    JSM_OP_SUB = 3,  /* mat_sub_t :253-286  */
+    JSM_OP_MUL = 4,  /* mat_mul_t :288-321  */
+    JSM_OP_DIV = 5,  /* mat_div_t :323-358  */
+    JSM_OP_GT = 6,   /* mat_greater_t :119-152 -> 1.0 / 0.0 */
+    JSM_OP_LT = 7,   /* mat_less_t :154-187 */
+    JSM_OP_EXP = 8,  /* mat_exp_t :439-468  */
+    JSM_OP_SIGMOID = 9, /* mat_sigmoid_t :479-509 */
+    JSM_OP_POW = 10,    /* pow(x, imm) :587-596 */
+    JSM_OP_SQRT = 11,   /* sqrt :804-813 */
+    JSM_OP_NEG = 12,
+    JSM_OP_RELU = 13, /* (x > 0) * x, relu_net_t::forward mat_net_t.hpp:146-153 */
+    JSM_OP_GELU = 14, /* erf form; not in the reference */
+    JSM_OP_SILU = 15, /* x * sigmoid(x); not in the reference */
+    JSM_OP_TANH = 16
+} jsm_op;
+
+typedef struct jsm_instr {
+    int32_t op;
+    int32_t arg;
+    float imm;
+} jsm_instr;
+
+#define JSM_MAX_INSTR 32
+#define JSM_MAX_LEAVES 8
+#define JSM_MAX_STACK 8
+
+/* out(r,c) = program(leaves)(r,c) for the whole result shape.
+ * Replaces mat_express_*_stable_t::clone / operator mat_t (mat_express_t.hpp:96-112, 416-432)
+ * and operator+= (:225-251, out aliased with leaf 0). */
+jsm_status jsm_eval_elementwise(const jsm_instr* prog, int n_instr, const jsm_mat* leaves, int n_leaves,
+                                jsm_mat out, void* stream);
+
+/* Reductions / normalisations along one axis of the value of a program.
+ * axis 1: along each row  (h* functions: hsum hmax hmean hsoftmax, mat_express_t.hpp:548-628, 681-694)
+ * axis 0: along each column (v* functions vsum vmean :531-546, 566-571;
+ *         layer_norm_net_t::forward normalises columns, mat_net_t.hpp:209-225) */
+typedef enum jsm_rows_kind {
+    JSM_ROWS_SUM = 0,
+    JSM_ROWS_MAX = 1,
+    JSM_ROWS_MEAN = 2,
+    JSM_ROWS_ARGMAX = 3,   /* out is I32; first maximum wins */
+    JSM_ROWS_SOFTMAX = 4,  /* exp(x - max) / sum(exp(x - max)) */
+    JSM_ROWS_LAYERNORM = 5, /* gain * (x - mean) / sqrt(mean((x-mean)^2) + eps) + bias; eps = 0 is reference-exact */
+    JSM_ROWS_RMSNORM = 6    /* gain * x / sqrt(mean(x^2) + eps); not in the reference */
+} jsm_rows_kind;
+
+/* gain / bias: F32 vectors indexed along the normalised axis, or NULL (1 / 0).
+ * out: reductions -> [R,1] (axis 1) or [1,C] (axis 0); others -> [R,C]. */
+jsm_status jsm_eval_rows(int kind, int axis, const jsm_instr* prog, int n_instr, const jsm_mat* leaves,
+                         int n_leaves, const float* d_gain, const float* d_bias, float eps, jsm_mat out,
+                         void* stream);
+
+/* Whole-matrix reductions: sum / mean / max (mat_express_t.hpp:518-529, 573-585, 598-609) into d_out[0]
+ * (F32), and the whole-matrix softmax of mat_softmax_t (:630-679, global max and sum). */
+jsm_status jsm_eval_full(int kind /* SUM, MAX, MEAN, SOFTMAX */, const jsm_instr* prog, int n_instr,
+                         const jsm_mat* leaves, int n_leaves, jsm_mat out, void* stream);
+
+/* ---- dense contraction, fp32 (mat_dot_t, mat_express_t.hpp:696-777) -----
+ * C = A . B (+ bias broadcast by modulo, + epilogue), all F32, any strides.
+ * Every output element is accumulated in ascending k with separately rounded
+ * multiply and add, i.e. the order of mat_dot_t::operator() (:730-736).
+ * JSM_INVALID_ARG when A.cols != B.rows (:709-712).
+ * epilogue: 0 none, 1 relu, 2 gelu(erf), 3 add residual R (same shape as C). */
+jsm_status jsm_dot_f32(jsm_mat A, jsm_mat B, const jsm_mat* bias, int epilogue, const jsm_mat* R, jsm_mat C,
+                       void* stream);
+
+/* ---- projections in bf16 (weight_net_t::forward, mat_net_t.hpp:38-49) ---
+ * Y[t, n] = sum_k X[t, k] * W[n, k] (+ bias[n]); X:[T,K] bf16 token-major,
+ * W:[N,K] bf16 (the reference's [out,in] layout), fp32 accumulation.
+ * T <= 4 runs a CUDA-core weight-streaming kernel, larger T the tcgen05 kernel.
+ * out_dtype: JSM_BF16 or JSM_F32.
+ * epilogue: 0 none, 1 relu, 2 gelu, 3 silu(gate)*up where W holds N gate rows followed by N up rows
+ * (Y is [T,N]), 4 add residual R[t,n] (bf16). */
+jsm_status jsm_linear_bf16(const void* d_X, const void* d_W, const float* d_bias, int epilogue, const void* d_R,
+                           void* d_Y, int out_dtype, int T, int N, int K, void* stream);
+
+/* ---- RoPE (mat_RoPE_t::init mat_RoPE_t.hpp:99-134, RoPE_net_t::forward :166-188)
+ * Table entry for (pair i, position m): (cos A, sin A, cos B, sin B);
+ *   out0 = cosA*x0 - sinB*x1 ; out1 = sinA*x0 + cosB*x1.
+ * mode 0 "reference": A = 2m / theta^(i/d), B = (2m+1) / theta^(i/d)  (the reference's table indexing)
+ * mode 1 "standard" : A = B = m / theta^(2i/d).
+ * d_table: F32 [max_pos, d/2, 4]. Built on the host with the reference's
+ * sequence of roundings and uploaded (synchronous). */
+jsm_status jsm_rope_table(float* d_table, int mode, int d, float theta, int max_pos, void* stream);
+/* x, out: token-major [T, n_heads*d] (F32 or BF16); positions: I32 [T] or NULL (= t). */
+jsm_status jsm_rope_apply(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
+                          const int32_t* d_positions, int T, void* stream);
+
+/* ---- attention (mat_head_gen_t::forward, mat_mha_t.hpp:45-74) -----------
+ * q:[T_q, Hq*D], k,v:[T_k, Hkv*D] token-major, per sequence b of `batch`
+ * equally long sequences; out:[T_q, Hq*D].  scores = q.k / sqrt(D) (scale passed
+ * explicitly), causal mask j > i + (T_k - T_q) -> -inf (:58-67), row softmax
+ * (:69), out = P.V (:71).  GQA: query head h reads kv head h / (Hq/Hkv).
+ * F32: CUDA-core kernel, fp32 throughout.  BF16: tcgen05/TMEM flash kernel when
+ * D == 128, fp32 accumulation; rope tables (or NULL) are applied to q and k on load. */
+jsm_status jsm_attn_prefill(const void* d_q, const void* d_k, const void* d_v, void* d_out, jsm_dtype dtype,
+                            int batch, int T_q, int T_k, int Hq, int Hkv, int D, int causal, float scale,
+                            const float* d_rope_table, int impl /* 0 auto, 1 cuda-core, 2 tcgen05 */,
+                            void* stream);
+
+/* ---- paged KV cache (new: the reference recomputes the whole prefix per
+ *      token, transformer_test.hpp:227-241) --------------------------------
+ * Pool layout: [n_pages][2 (K,V)][Hkv][page_size][D] bf16, page_size = 64.
+ * block_table: I32 [n_seqs, max_pages]; context_lens: I32 [n_seqs]. */
+#define JSM_PAGE_SIZE 64
+/* Append T new tokens (token t belongs to sequence seq_ids[t] at position positions[t]);
+ * k is rotated with the rope table row of its position when d_rope_table != NULL. */
+jsm_status jsm_kv_append(void* d_pool, const int32_t* d_block_table, int max_pages, const void* d_k,
+                         const void* d_v, int64_t kv_row_stride, const int32_t* d_seq_ids,
+                         const int32_t* d_positions, int T, int Hkv, int D, const float* d_rope_table,
+                         void* stream);
+/* One query token per sequence against its cached context (split-K over the
+ * context, then a combine pass).  q:[n_seqs, Hq*D] bf16 (rotated here when a
+ * rope table is given, at position context_len-1), out:[n_seqs, Hq*D] bf16.
+ * d_scratch: F32, jsm_attn_decode_scratch_bytes() bytes. */
+size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int max_context);
+jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_pool,
+                           const int32_t* d_block_table, int max_pages, const int32_t* d_context_lens,
+                           int n_seqs, int Hq, int Hkv, int D, float scale, const float* d_rope_table,
+                           int max_context, void* d_scratch, void* d_out, void* stream);
+
+/* ---- token-level helpers (not in the reference) ------------------------- */
+/* out[t, :] = table[ids[t], :] (+ pos_table[positions[t], :]) */
+jsm_status jsm_embedding(const void* d_table, const void* d_pos_table, const int32_t* d_ids,
+                         const int32_t* d_positions, void* d_out, jsm_dtype dtype, int T, int d, void* stream);
+/* bf16/f32 RMSNorm / LayerNorm of token-major activations with optional fused residual add:
+ * h_out = h (+ delta) ; y = norm(h_out) * gain (+ bias).  kind: JSM_ROWS_LAYERNORM / JSM_ROWS_RMSNORM. */
+jsm_status jsm_add_norm(int kind, const void* d_h, const void* d_delta, void* d_h_out, void* d_y,
+                        jsm_dtype dtype, const float* d_gain, const float* d_bias, float eps, int T, int d,
+                        void* stream);
+
+/* ---- decoder-only model (new; block wiring composed from the parts above;
+ *      stack loop: encoder_t::forward mat_transformer_kernel_t.hpp:103-110) -- */
+typedef struct jsm_model_config {
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ffn, vocab;
+    int32_t max_batch, max_context; /* cache capacity */
+    float norm_eps, rope_theta;
+    int32_t tp_rank, tp_size; /* heads and FFN columns are split across tp_size ranks */
+} jsm_model_config;
+
+typedef struct jsm_model jsm_model;
+/* all-reduce hook: sum `count` bf16 (dtype 1) / f32 (dtype 0) elements in place across the TP group, on `stream`. */
+typedef int (*jsm_allreduce_fn)(void* d_buf, size_t count, int dtype, void* stream, void* user);
+
+/* LLaMA-shape model (RMSNorm, SwiGLU, RoPE, bf16).  Weights are generated from
+ * (seed, tensor id, index) ~ N(0, 0.02), norm gains 1; each TP rank generates its own shard. */
+jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_model** out);
+jsm_status jsm_llama_destroy(jsm_model* m);
+jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user);
+/* Device pointer / element count of a named weight of this rank's shard ("layers.3.wqkv", "lm_head", ...). */
+jsm_status jsm_llama_weight(jsm_model* m, const char* name, void** d_ptr, size_t* n_elems);
+/* Prefill `T` prompt tokens of sequence `seq` (positions 0..T-1); writes the argmax of the last position to d_next[seq]. */
+jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T, int32_t* d_next, float* d_logits_last,
+                             void* stream);
+/* One greedy decode step for sequences 0..batch-1: d_ids[b] is appended at the
+ * sequence's current length; d_next[b] = argmax of the logits; d_logits (or NULL): F32 [batch, vocab]. */
+jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, int32_t* d_next, float* d_logits,
+                                 void* stream);
+/* Host-side bookkeeping of context lengths (advance after a captured step is replayed). */
+jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len);
+jsm_status jsm_llama_reset(jsm_model* m);
+/* bytes of weights read by one decode step on this rank, and KV bytes per cached token */
+jsm_status jsm_llama_step_bytes(jsm_model* m, uint64_t* weight_bytes, uint64_t* kv_bytes_per_token);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* JASMINE_B200_H_ */

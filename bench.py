@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Headline benchmark: LLaMA-7B-shape greedy decode (random-init bf16, synthetic prompt) in tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+A "step" is one decode step: one new token for each of the B sequences of the batch, every weight byte
+of the model and every cached K/V byte read once.  With N > 1 (launched by torch.distributed.run, one
+rank per GPU) the model is tensor-parallel over attention heads and FFN columns with one all-reduce per
+attention block and one per FFN block; the total work is fixed (strong scaling).
+
+Rank 0 prints ONE JSON line.  `value` is timed on the device with CUDA events around K replayed steps
+(inputs resident in HBM); `e2e` is the same loop driven through the C-ABI entry points with the token
+ids coming from pinned host memory and the next tokens read back every step; `roofline` is the
+weight-streaming projection kernel timed alone against the measured HBM peak; `cpu_baseline` is the
+CPU oracle timed on a bounded sample of the same per-token work.
+
+`--impl reference` times the reference's own CPU code (the jasmine headers behind oracle/_ref) on a
+bounded sample of the per-token work and extrapolates by multiply-accumulate count.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA7B = dict(n_layers=32, d_model=4096, n_heads=32, n_kv_heads=32, d_ffn=11008, vocab=32000)
+PROMPT, GEN = 512, 128
+SEED = 4
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- clocks ----------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- CPU legs (the only places that touch oracle/) ------------------------------------------------
+def per_token_macs(ctx: int) -> int:
+    c = LLAMA7B
+    d, ffn, L = c["d_model"], c["d_ffn"], c["n_layers"]
+    return L * (4 * d * d + 3 * d * ffn + 2 * ctx * d) + c["vocab"] * d
+
+
+def cpu_port_baseline():
+    """Times the CPU oracle (port) on a slice of one decoder layer for one token and extrapolates by MAC count."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import numpy as np
+    import oracle_lib as ol
+    d, rows, ctx = LLAMA7B["d_model"], 2048, 512
+    cores = os.cpu_count() or 1
+    W = ol.fill(rows * d, SEED, 1, 0, 0.0, 0.02, to_bf16=True).reshape(rows, d)
+    x = ol.fill(d, SEED, 2, 0, 0.0, 1.0, to_bf16=True).reshape(1, d)
+    kv = ol.fill(ctx * d, SEED, 3, 0, 0.0, 1.0, to_bf16=True).reshape(ctx, d)
+    po = ol.port_oracle()
+    po.linear(x, W, np.zeros(rows, np.float32))  # warm
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0:
+        po.linear(x, W, np.zeros(rows, np.float32))
+        ol.attention(x, kv, kv, 1, 32, 32, 128, False, exact_div=False)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    macs = rows * d + 2 * ctx * d
+    tok_s = 1.0 / (dt * per_token_macs(PROMPT + GEN // 2) / macs)
+    return {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{rows}x{d} projection + one attention row over {ctx} cached tokens for 1 token, OpenMP over "
+                      f"{cores} threads, ~10 s, extrapolated by multiply-accumulate count to the full model"}
+
+
+def run_reference_arm(args):
+    """The reference's own weight_net_t::forward / attention code on the host cores (bounded sample per step)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sys.path.insert(0, str(ROOT / "tests"))
+    import numpy as np
+    import oracle_lib as ol
+    ref = ol.ref_oracle()
+    kind = "reference"
+    if ref is None:
+        ref, kind = ol.port_oracle(), "port"
+    d, rows = LLAMA7B["d_model"], 256
+    cores = os.cpu_count() or 1
+    W = ol.fill(rows * d, SEED, 1, 0, 0.0, 0.02, to_bf16=True).reshape(rows, d)
+    x = ol.fill(d, SEED, 2, 0, 0.0, 1.0, to_bf16=True).reshape(1, d)
+    b = np.zeros(rows, np.float32)
+
+    def step():
+        # the reference is single-threaded by construction: independent row slices are farmed over the cores
+        ts = [threading.Thread(target=ref.linear, args=(x, W, b)) for _ in range(cores)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    macs = cores * rows * d
+    tok_s = 1.0 / (dt * per_token_macs(PROMPT + GEN // 2) / macs)
+    sample = (f"per step: {cores} concurrent weight_net_t::forward calls ({rows}x{d} rows each, 1 token) through the "
+              f"{'jasmine headers (oracle/_ref)' if kind == 'reference' else 'CPU oracle port'}; tok/s extrapolated by "
+              f"multiply-accumulate count to one token of the 7B model at context {PROMPT + GEN // 2}")
+    line = {"impl": "reference", "metric": "llama7b_decode_tokens_per_s", "value": tok_s, "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, 1),
+            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, n):
+    return {"workload": f"llama7b_decode_b{args.batch}", "layers": 32, "d_model": 4096, "heads": "32x128", "d_ffn": 11008,
+            "vocab": 32000, "batch": args.batch, "prompt_len": PROMPT, "generated": GEN,
+            "parallelism": f"tp{n}", "l2": "inputs larger than L2 (13.2 GB of weights per step)"}
+
+
+# ---- the GPU arm --------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=GEN)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=int(os.environ.get("JSM_BENCH_BATCH", "8")))
+    ap.add_argument("--impl", default="jasmine_b200")
+    ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    import jasmine_b200 as jb
+    from jasmine_b200.model import Llama
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    B, K, W = args.batch, args.steps, args.warmup
+    max_ctx = PROMPT + W + 2 * K + 8
+    cfg = dict(LLAMA7B, n_layers=args.layers)
+    model = Llama(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["d_ffn"], cfg["vocab"],
+                  max_batch=B, max_context=max_ctx, seed=SEED, tp_rank=rank, tp_size=world)
+    if world > 1:
+        def allreduce(ptr, count, dtype, stream):
+            iface = {"shape": (count,), "typestr": "<u2" if dtype == jb.BF16 else "<f4", "data": (ptr, False), "version": 2}
+            holder = type("DevBuf", (), {"__cuda_array_interface__": iface})()
+            t = torch.as_tensor(holder, device="cuda")
+            if dtype == jb.BF16:
+                t = t.view(torch.bfloat16)
+            dist.all_reduce(t)
+        model.set_allreduce(allreduce)
+
+    # synthetic prompt: B sequences of PROMPT token ids, uniform in [0, vocab)
+    nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+    t_pre0 = time.perf_counter()
+    for b in range(B):
+        ids = torch.empty(PROMPT, dtype=torch.int32, device="cuda")
+        jb.fill(ids, SEED, 5000 + b, 2, 0, cfg["vocab"])
+        model.prefill(ids, b, nxt)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t_pre0
+    ids = nxt.clone()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up steps (eager: first-use set-up happens here), then capture one step
+    launches0 = jb.launch_count()
+    for _ in range(W):
+        model.decode_step(ids, nxt)
+        ids.copy_(nxt)
+    torch.cuda.synchronize()
+    launches_per_step = (jb.launch_count() - launches0) // W
+    graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                model.decode_step(ids, nxt)
+                ids.copy_(nxt)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = g
+    except Exception as e:  # multi-rank capture of the collective can be refused: run the step eagerly
+        if rank == 0:
+            print(f"# graph capture failed ({type(e).__name__}: {e}); timing eager steps", file=sys.stderr)
+        torch.cuda.synchronize()
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            model.decode_step(ids, nxt)
+            ids.copy_(nxt)
+
+    one_step()  # one replay outside the timed region
+    clocks = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        clocks.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        one_step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clock_info = clocks.stop() if rank == 0 else None
+    tok_s = B * K / (ms / 1e3)
+    ctx_mid = PROMPT + W + 1 + K // 2  # mean context length over the timed steps
+
+    # end-to-end through the C ABI with host buffers: ids from pinned memory in, next tokens out, every step
+    h_ids = torch.empty(B, dtype=torch.int32).pin_memory()
+    h_next = torch.empty(B, dtype=torch.int32).pin_memory()
+    h_ids.copy_(ids.cpu())
+    Ke = min(K, 64)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        ids.copy_(h_ids, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+        else:
+            model.decode_step(ids, nxt)
+        h_next.copy_(nxt, non_blocking=True)
+        torch.cuda.synchronize()
+        h_ids.copy_(h_next)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_tok_s = B * Ke / e2e_s
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # roofline of the dominant kernel, timed alone: the SwiGLU gate/up weight stream of one layer
+    # (2 x 11008 x 4096 bf16 = 180 MB per launch, a different layer every launch: larger than L2)
+    peak, peak_kind = measured_peaks()
+    d, ffn_l = cfg["d_model"], cfg["d_ffn"] // world
+    x = torch.empty(B, d, device="cuda", dtype=torch.bfloat16)
+    jb.fill(x, SEED, 7000, 0, 0.0, 1.0)
+    y = torch.empty(B, ffn_l, device="cuda", dtype=torch.bfloat16)
+    wptrs = []
+    for l in range(cfg["n_layers"]):
+        p, n = C.c_void_p(), C.c_size_t()
+        jb.check(jb.lib().jsm_llama_weight(model._h, f"layers.{l}.wgu".encode(), C.byref(p), C.byref(n)))
+        wptrs.append(p.value)
+
+    def stream_once(l):
+        jb.check(jb.lib().jsm_linear_bf16(x.data_ptr(), wptrs[l], None, 3, None, y.data_ptr(), jb.BF16, B, ffn_l, d,
+                                          jb.stream_ptr()))
+    for l in range(min(4, len(wptrs))):
+        stream_once(l)
+    torch.cuda.synchronize()
+    reps = 3 * len(wptrs)
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for i in range(reps):
+        stream_once(i % len(wptrs))
+    r1.record()
+    torch.cuda.synchronize()
+    k_ms = r0.elapsed_time(r1) / reps
+    alg_bytes = 2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2
+    achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+    wbytes, kv_per_tok = model.step_bytes()
+    step_bytes = wbytes + B * ctx_mid * kv_per_tok
+    step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
+
+    line = {
+        "metric": "llama7b_decode_tokens_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args, world),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "gate/up projection weight stream (jsm_linear_bf16, silu*up epilogue)",
+                     "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes},
+        "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_gbs, "frac": step_gbs / peak,
+                          "note": "all weights + cached K/V of the step over the measured step time"},
+        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "steps": Ke},
+        "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "cuda_graph": graph is not None,
+        "prefill_s": prefill_s, "clocks": clock_info,
+    }
+    if args.layers != 32:
+        line["invalid"] = "debug run with fewer layers"
+    if not args.no_cpu and world == 1:
+        try:
+            line["cpu_baseline"] = cpu_port_baseline()
+        except Exception as e:
+            line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"failed: {type(e).__name__}: {e}"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

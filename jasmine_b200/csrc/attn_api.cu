@@ -1,0 +1,24 @@
+// C entry point of prefill attention: argument checks and the choice between the
+// CUDA-core fp32 kernel and the tcgen05 flash kernel.
+#include "common.cuh"
+#include "attn.cuh"
+
+using namespace jsm;
+
+extern "C" jsm_status jsm_attn_prefill(const void* d_q, const void* d_k, const void* d_v, void* d_out, jsm_dtype dtype, int batch,
+                                       int T_q, int T_k, int Hq, int Hkv, int D, int causal, float scale, const float* d_rope_table,
+                                       int impl, void* stream) {
+    if (batch <= 0 || T_q <= 0) return JSM_OK;
+    if (!d_q || !d_k || !d_v || !d_out) JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_prefill: null pointer");
+    if (T_k <= 0) JSM_FAIL(JSM_SHAPE, "jsm_attn_prefill: no keys");
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) JSM_FAIL(JSM_SHAPE, "d_model must be divisible by num_heads (Hq %d, Hkv %d)", Hq, Hkv);
+    if (D <= 0 || D % 2 || D > 128) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_prefill: head_dim %d (even, <= 128)", D);
+    if (dtype != JSM_F32 && dtype != JSM_BF16) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_prefill: dtype %d", (int)dtype);
+    if (causal && T_k < T_q) JSM_FAIL(JSM_SHAPE, "jsm_attn_prefill: causal attention needs T_k >= T_q");
+    cudaStream_t st = as_stream(stream);
+    const bool flash_ok = dtype == JSM_BF16 && D == 128 && flash_available();
+    if (impl == 2 && !flash_ok) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_prefill: the tcgen05 kernel needs bf16 and head_dim 128");
+    if (impl == 2 || (impl == 0 && flash_ok && T_q >= 128))
+        return flash_prefill_launch(d_q, d_k, d_v, d_out, batch, T_q, T_k, Hq, Hkv, causal, scale, d_rope_table, st);
+    return attn_simt_launch(d_q, d_k, d_v, d_out, dtype, batch, T_q, T_k, Hq, Hkv, D, causal, scale, d_rope_table, st);
+}

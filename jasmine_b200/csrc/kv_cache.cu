@@ -1,0 +1,290 @@
+// Paged KV cache: append and split-K decode attention.
+//
+// The reference has no cache: generation recomputes the whole prefix for every
+// token (transformer_test.hpp:227-241).  Here K (already rotated) and V of every
+// position are kept in pages of 64 tokens, pool layout
+// [page][K|V][kv_head][token in page][head_dim] bf16, and one decode step reads
+// each cached byte once.  The arithmetic per (sequence, head) is the row of
+// mat_head_gen_t::forward (mat_mha_t.hpp:53-71) for the newest query:
+// scores = q.k * scale, softmax over the context, weighted sum of V.
+//
+// Decode kernel: grid (context chunk, kv head, sequence).  A CTA of 4 warps
+// streams its chunk of K and V with 128-bit loads (16 lanes per key, two keys per
+// warp load), all G = Hq/Hkv query heads of the group share every loaded byte,
+// and the running (max, sum, weighted V) is kept per warp, merged through shared
+// memory and written as one partial per chunk; a second kernel merges the
+// partials of a sequence.
+#include "common.cuh"
+#include <math.h>
+
+namespace jsm {
+
+constexpr int DEC_CHUNK = 512;   // context positions per CTA
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_UNROLL = 4;    // warp loads of K (and V) in flight per step: 8 keys
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+    f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
+    f[4] = bf16lo(w.z); f[5] = bf16hi(w.z); f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
+}
+
+// ---- append ----------------------------------------------------------------------
+__global__ void __launch_bounds__(128) kv_append_kernel(__nv_bfloat16* __restrict__ pool, const int32_t* __restrict__ block_table,
+                                                        int max_pages, const __nv_bfloat16* __restrict__ k,
+                                                        const __nv_bfloat16* __restrict__ v, long long row_stride,
+                                                        const int32_t* __restrict__ seq_ids, const int32_t* __restrict__ positions,
+                                                        int Hkv, int D, const float4* __restrict__ rope) {
+    const int t = blockIdx.x, hk = blockIdx.y;
+    const int seq = seq_ids ? seq_ids[t] : 0;
+    const int pos = positions[t];
+    const int page = block_table[(long long)seq * max_pages + pos / JSM_PAGE_SIZE];
+    const long long page_elems = 2ll * Hkv * JSM_PAGE_SIZE * D;
+    __nv_bfloat16* kdst = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + pos % JSM_PAGE_SIZE) * D;
+    __nv_bfloat16* vdst = kdst + (long long)Hkv * JSM_PAGE_SIZE * D;
+    const __nv_bfloat16* ksrc = k + t * row_stride + (long long)hk * D;
+    const __nv_bfloat16* vsrc = v + t * row_stride + (long long)hk * D;
+    const int half = D / 2;
+    for (int pr = threadIdx.x; pr < half; pr += blockDim.x) {
+        uint32_t kw = *reinterpret_cast<const uint32_t*>(ksrc + 2 * pr);
+        if (rope) {
+            const float4 e = rope[(long long)pos * half + pr];
+            const float x0 = bf16lo(kw), x1 = bf16hi(kw);
+            kw = pack_bf16x2(__fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1)), __fadd_rn(__fmul_rn(e.y, x0), __fmul_rn(e.z, x1)));
+        }
+        *reinterpret_cast<uint32_t*>(kdst + 2 * pr) = kw;
+        *reinterpret_cast<uint32_t*>(vdst + 2 * pr) = *reinterpret_cast<const uint32_t*>(vsrc + 2 * pr);
+    }
+}
+
+// ---- decode: one partial per (sequence, kv head, chunk) -------------------------------
+// scratch: [n_seqs][Hq][n_chunks][D + 2] floats: o[D] (unnormalised), m (log2 domain), l
+template <int G>
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ pool,
+    const int32_t* __restrict__ block_table, int max_pages, const int32_t* __restrict__ context_lens, int Hq, int Hkv,
+    float scale_log2, const float4* __restrict__ rope, int n_chunks, float* __restrict__ scratch) {
+    constexpr int D = 128;
+    const int chunk = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
+    const int ctx = context_lens[seq];
+    const int c_begin = chunk * DEC_CHUNK;
+    if (c_begin >= ctx) return;
+    const int c_end = min(ctx, c_begin + DEC_CHUNK);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ks = lane >> 4;          // which of the two keys of a warp load
+    const int dsub = (lane & 15) * 8;  // this lane's 8 dims
+
+    // query heads of the group, this lane's 8 dims, pre-scaled into the log2 domain
+    float qf[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const uint4 w = *reinterpret_cast<const uint4*>(q + seq * q_stride + (long long)(hk * G + g) * D + dsub);
+        unpack8(w, qf[g]);
+        if (rope) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float4 e = rope[(long long)(ctx - 1) * (D / 2) + dsub / 2 + p];
+                const float x0 = qf[g][2 * p], x1 = qf[g][2 * p + 1];
+                // rounded to bf16 like a stored, rotated q would be
+                const uint32_t pk = pack_bf16x2(__fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1)),
+                                                __fadd_rn(__fmul_rn(e.y, x0), __fmul_rn(e.z, x1)));
+                qf[g][2 * p] = bf16lo(pk);
+                qf[g][2 * p + 1] = bf16hi(pk);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qf[g][i] *= scale_log2;
+    }
+
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
+    }
+    const long long page_elems = 2ll * Hkv * JSM_PAGE_SIZE * D;
+    const long long v_off = (long long)Hkv * JSM_PAGE_SIZE * D;
+    const int32_t* bt = block_table + (long long)seq * max_pages;
+    constexpr int STEP = 2 * DEC_UNROLL;  // keys per warp step
+
+    for (int base = c_begin + warp * STEP; base < c_end; base += DEC_WARPS * STEP) {
+        const int page = bt[base / JSM_PAGE_SIZE];
+        const __nv_bfloat16* kp = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + base % JSM_PAGE_SIZE) * D;
+        uint4 kw[DEC_UNROLL], vw[DEC_UNROLL];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int key = base + 2 * u + ks;
+            if (key < c_end) {
+                kw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + (long long)(2 * u + ks) * D + dsub));
+                vw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + v_off + (long long)(2 * u + ks) * D + dsub));
+            } else {
+                kw[u] = make_uint4(0, 0, 0, 0);
+                vw[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float s[DEC_UNROLL][G];
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float kf[8];
+            unpack8(kw[u], kf);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float d = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) d = fmaf(qf[g][i], kf[i], d);
+                s[u][g] = d;
+            }
+        }
+        // sum over the 16 lanes that share a key
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u)
+#pragma unroll
+                for (int g = 0; g < G; ++g) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                if (base + 2 * u + ks >= c_end) s[u][g] = -INFINITY;
+                mx = fmaxf(mx, s[u][g]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[g], mx);  // finite: key `base` is always valid
+            const float corr = exp2f(m[g] - m_new);
+            m[g] = m_new;
+            l[g] *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] *= corr;
+#pragma unroll
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                const float p = exp2f(s[u][g] - m_new);
+                s[u][g] = p;
+                l[g] += p;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            float vf[8];
+            unpack8(vw[u], vf);
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(s[u][g], vf[i], acc[g][i]);
+        }
+    }
+    // the two key slots of the warp hold disjoint keys under the same running max: add them
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        l[g] += __shfl_xor_sync(0xffffffffu, l[g], 16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] += __shfl_xor_sync(0xffffffffu, acc[g][i], 16);
+    }
+    // merge the warps of the CTA
+    __shared__ float sm_m[DEC_WARPS][G], sm_l[DEC_WARPS][G];
+    __shared__ float sm_o[DEC_WARPS][G][D];
+    if (ks == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sm_o[warp][g][dsub + i] = acc[g][i];
+            if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * D; e += DEC_WARPS * 32) {
+        const int g = e / D, d = e % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][g]);
+        float o = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = sm_m[w][g] == -INFINITY ? 0.0f : exp2f(sm_m[w][g] - M);
+            o += f * sm_o[w][g][d];
+            L += f * sm_l[w][g];
+        }
+        float* dst = scratch + (((long long)seq * Hq + hk * G + g) * n_chunks + chunk) * (D + 2);
+        dst[d] = o;
+        if (d == 0) { dst[D] = M; dst[D + 1] = L; }
+    }
+}
+
+// merge the chunk partials of one (sequence, query head): 128 threads, one per dim
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ scratch,
+                                                                const int32_t* __restrict__ context_lens, int Hq, int n_chunks,
+                                                                __nv_bfloat16* __restrict__ out) {
+    constexpr int D = 128;
+    const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
+    const int n = (context_lens[seq] + DEC_CHUNK - 1) / DEC_CHUNK;
+    const float* src = scratch + ((long long)seq * Hq + h) * n_chunks * (D + 2);
+    float M = -INFINITY;
+    for (int c = 0; c < n; ++c) M = fmaxf(M, src[c * (D + 2) + D]);
+    float o = 0.0f, L = 0.0f;
+    for (int c = 0; c < n; ++c) {
+        const float f = exp2f(src[c * (D + 2) + D] - M);
+        o += f * src[c * (D + 2) + d];
+        L += f * src[c * (D + 2) + D + 1];
+    }
+    out[((long long)seq * Hq + h) * D + d] = __float2bfloat16_rn(n > 0 ? o / L : 0.0f);
+}
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" jsm_status jsm_kv_append(void* d_pool, const int32_t* d_block_table, int max_pages, const void* d_k, const void* d_v,
+                                    int64_t kv_row_stride, const int32_t* d_seq_ids, const int32_t* d_positions, int T, int Hkv,
+                                    int D, const float* d_rope_table, void* stream) {
+    if (T == 0) return JSM_OK;
+    if (!d_pool || !d_block_table || !d_k || !d_v || !d_positions) JSM_FAIL(JSM_INVALID_ARG, "jsm_kv_append: null pointer");
+    if (D <= 0 || D % 2 || Hkv <= 0 || max_pages <= 0) JSM_FAIL(JSM_SHAPE, "jsm_kv_append: Hkv %d D %d max_pages %d", Hkv, D, max_pages);
+    dim3 grid(T, Hkv);
+    kv_append_kernel<<<grid, 64, 0, as_stream(stream)>>>((__nv_bfloat16*)d_pool, d_block_table, max_pages, (const __nv_bfloat16*)d_k,
+                                                         (const __nv_bfloat16*)d_v, kv_row_stride, d_seq_ids, d_positions, Hkv, D,
+                                                         (const float4*)d_rope_table);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+extern "C" size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int max_context) {
+    if (n_seqs <= 0 || Hq <= 0 || D <= 0 || max_context <= 0) return 0;
+    const size_t n_chunks = (size_t)(max_context + DEC_CHUNK - 1) / DEC_CHUNK;
+    return (size_t)n_seqs * Hq * n_chunks * (D + 2) * sizeof(float);
+}
+
+extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_pool, const int32_t* d_block_table,
+                                      int max_pages, const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                      const float* d_rope_table, int max_context, void* d_scratch, void* d_out, void* stream) {
+    if (n_seqs == 0) return JSM_OK;
+    if (!d_q || !d_pool || !d_block_table || !d_context_lens || !d_scratch || !d_out)
+        JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode: null pointer");
+    if (D != 128) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_decode: head_dim %d (128 only)", D);
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) JSM_FAIL(JSM_SHAPE, "d_model must be divisible by num_heads (Hq %d, Hkv %d)", Hq, Hkv);
+    if (max_context <= 0 || (q_row_stride % 8)) JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode: max_context %d, q stride %lld", max_context, (long long)q_row_stride);
+    const int G = Hq / Hkv;
+    const int n_chunks = (max_context + DEC_CHUNK - 1) / DEC_CHUNK;
+    dim3 grid(n_chunks, Hkv, n_seqs);
+    cudaStream_t st = as_stream(stream);
+    const float sl2 = scale * LOG2E;
+#define JSM_DEC(GG)                                                                                                            \
+    attn_decode_kernel<GG><<<grid, DEC_WARPS * 32, 0, st>>>((const __nv_bfloat16*)d_q, q_row_stride, (const __nv_bfloat16*)d_pool, \
+                                                            d_block_table, max_pages, d_context_lens, Hq, Hkv, sl2,               \
+                                                            (const float4*)d_rope_table, n_chunks, (float*)d_scratch)
+    switch (G) {
+        case 1: JSM_DEC(1); break;
+        case 2: JSM_DEC(2); break;
+        case 4: JSM_DEC(4); break;
+        case 8: JSM_DEC(8); break;
+        default: JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_decode: %d query heads per kv head (1, 2, 4 or 8)", G);
+    }
+#undef JSM_DEC
+    JSM_LAUNCH_CHECK();
+    attn_decode_merge_kernel<<<dim3(Hq, n_seqs), 128, 0, st>>>((const float*)d_scratch, d_context_lens, Hq, n_chunks,
+                                                               (__nv_bfloat16*)d_out);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}

@@ -1,0 +1,443 @@
+// bf16 projections Y[t,n] = sum_k X[t,k] * W[n,k] with fp32 accumulation: the
+// device form of weight_net_t::forward (mat_net_t.hpp:38-49, Y = W.X + b with W
+// stored [out, in]).
+//
+// Two kernels:
+//  * linear_tc_kernel  — tcgen05: W tiles (128 output features x 64 k) are the A
+//    operand, X tiles (BN tokens x 64 k) the B operand, both staged by TMA with
+//    the 128-byte swizzle through a ring of shared-memory stages; the 128 x BN fp32
+//    accumulator lives in TMEM.  Roles: warp 0 issues TMA, warp 1 issues MMAs,
+//    warps 2-5 read the accumulator back (one TMEM lane = one output feature per
+//    thread) and apply the epilogue.  With few tokens the kernel is a weight
+//    stream: every byte of W crosses HBM once and the grid is split along K so that
+//    all SMs pull at once (fp32 partials, folded by the caller).
+//  * gemv_kernel — CUDA cores, up to 4 tokens: each warp streams 4 weight rows with
+//    128-bit loads that bypass L1 allocation and reduces with shuffles.
+#include "tc_utils.cuh"
+#include "linear_bf16.cuh"
+#include <math.h>
+#include <mutex>
+
+namespace jsm {
+
+using namespace tc;
+
+// ---- driver entry point for tensor maps (no link-time dependency on libcuda) -------------
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn get_encode() {
+    static encode_tiled_fn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<encode_tiled_fn>(p);
+    });
+    return fn;
+}
+
+jsm_status make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                             uint32_t box_rows, uint32_t box_cols) {
+    encode_tiled_fn enc = get_encode();
+    if (!enc) JSM_FAIL(JSM_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver)");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_elems * 2) % 16)
+        JSM_FAIL(JSM_INVALID_ARG, "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride_elems * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) JSM_FAIL(JSM_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu)", (int)r,
+                                    (unsigned long long)rows, (unsigned long long)cols);
+    return JSM_OK;
+}
+
+jsm_status make_tmap_bf16_3d(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems,
+                             uint64_t s2_elems, uint32_t b0, uint32_t b1, uint32_t b2) {
+    encode_tiled_fn enc = get_encode();
+    if (!enc) JSM_FAIL(JSM_CUDA, "cuTensorMapEncodeTiled is not available (no CUDA driver)");
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1_elems * 2) % 16 || (s2_elems * 2) % 16)
+        JSM_FAIL(JSM_INVALID_ARG, "TMA operand must be 16-byte aligned with 16-byte multiple pitches");
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {s1_elems * 2, s2_elems * 2};
+    cuuint32_t box[3] = {b0, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) JSM_FAIL(JSM_CUDA, "cuTensorMapEncodeTiled (3d) failed with %d", (int)r);
+    return JSM_OK;
+}
+
+int* tc_error_word() {
+    static int* words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(p, 0, sizeof(int));
+        words[dev] = p;
+    }
+    return words[dev];
+}
+
+// ---- epilogue helpers -----------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// ---- tcgen05 kernel ----------------------------------------------------------------------------
+constexpr int BM = 128;  // output features per tile (MMA M, TMEM lanes)
+constexpr int BK = 64;   // k per stage: one 128-byte swizzled row
+constexpr int TC_THREADS = 192;
+
+struct TcParams {
+    int T, N, K;          // tokens, output features, reduction length
+    int kb_per_split;     // k-blocks (of 64) per grid.z slice
+    int epilogue;         // LIN_*
+    int out_mode;         // 0 bf16 Y, 1 f32 Y, 2 f32 partial [split][T][N]
+    const float* bias;
+    const __nv_bfloat16* R;
+    void* Y;
+    int* err;
+};
+
+template <int BN, bool GATEUP>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, TcParams P, int stages) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int A_BYTES = BM * BK * 2 * (GATEUP ? 2 : 1);
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS_NEEDED = GATEUP ? 2 * BN : BN;
+    constexpr int TMEM_COLS = TMEM_COLS_NEEDED < 32 ? 32 : TMEM_COLS_NEEDED;
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+    constexpr int MAX_STAGES = 12;
+
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
+    __shared__ __align__(8) uint64_t acc_bar;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;   // first output feature of the tile
+    const int t0 = blockIdx.y * BN;   // first token of the tile
+    const int kb_total = (P.K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * P.kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_w);
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ---- producer: one thread streams W and X tiles into the ring
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
+                uint8_t* st = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                const int kx = (kb_begin + i) * BK;
+                tma_load_2d(st, &tmap_w, kx, n0, &full_bar[s]);
+                if (GATEUP) tma_load_2d(st + BM * BK * 2, &tmap_w, kx, P.N + n0, &full_bar[s]);
+                tma_load_2d(st + A_BYTES, &tmap_x, kx, t0, &full_bar[s]);
+                issued = i + 1;
+            }
+            // on an abort, wait (bounded) for the copies still in flight before the CTA may exit
+            if (abort_flag) {
+                for (int i = max(0, issued - stages); i < issued; ++i) {
+                    const long long t_start = clock64();
+                    while (!mbar_try_wait(&full_bar[i % stages], (i / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (!mbar_wait(&full_bar[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+                const uint64_t a_desc = smem_desc_sw128(a_addr);
+                const uint64_t b_desc = smem_desc_sw128(b_addr);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    mma_ss(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, acc);
+                    if (GATEUP) {
+                        const uint64_t u_desc = smem_desc_sw128(a_addr + BM * BK * 2);
+                        mma_ss(tmem_base + BN, u_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, acc);
+                    }
+                }
+                mma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+            }
+            if (ok) mma_commit(&acc_bar);    // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 -> TMEM lane quadrants (warp % 4)
+        const int quad = warp & 3;
+        const int feat = n0 + quad * 32 + lane;
+        bool ok = n_kb > 0;
+        if (ok) ok = mbar_wait(&acc_bar, 0, &abort_flag, P.err, TC_TIMEOUT_ACC);
+        tc_fence_after();
+        if (ok) {
+            const float bias = (P.bias && feat < P.N && (P.out_mode != 2 || blockIdx.z == 0)) ? P.bias[feat] : 0.0f;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= P.T) break;
+                uint32_t r[16], u[16];
+                tmem_ld16(lane_addr + c0, r);
+                if (GATEUP) tmem_ld16(lane_addr + BN + c0, u);
+                tmem_ld_wait();
+                if (feat < P.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < P.T) {
+                            float v = __uint_as_float(r[j]) + bias;
+                            if (GATEUP) v = silu_f(v) * __uint_as_float(u[j]);
+                            else if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
+                            else if (P.epilogue == LIN_GELU) v = gelu_f(v);
+                            else if (P.epilogue == LIN_RESIDUAL) v += __bfloat162float(P.R[(size_t)t * P.N + feat]);
+                            if (P.out_mode == 0)
+                                reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + feat] = __float2bfloat16_rn(v);
+                            else if (P.out_mode == 1)
+                                reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + feat] = v;
+                            else
+                                reinterpret_cast<float*>(P.Y)[((size_t)blockIdx.z * P.T + t) * P.N + feat] = v;
+                        }
+                    }
+                }
+            }
+        } else if (n_kb == 0 && P.out_mode == 2 && feat < P.N) {
+            for (int t = t0; t < min(P.T, t0 + BN); ++t)
+                reinterpret_cast<float*>(P.Y)[((size_t)blockIdx.z * P.T + t) * P.N + feat] = 0.0f;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- CUDA-core weight stream for up to 4 tokens --------------------------------------------------
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x) {
+    float s = bf16lo(w.x) * bf16lo(x.x);
+    s = fmaf(bf16hi(w.x), bf16hi(x.x), s);
+    s = fmaf(bf16lo(w.y), bf16lo(x.y), s);
+    s = fmaf(bf16hi(w.y), bf16hi(x.y), s);
+    s = fmaf(bf16lo(w.z), bf16lo(x.z), s);
+    s = fmaf(bf16hi(w.z), bf16hi(x.z), s);
+    s = fmaf(bf16lo(w.w), bf16lo(x.w), s);
+    s = fmaf(bf16hi(w.w), bf16hi(x.w), s);
+    return s;
+}
+
+// Each warp owns ROWS output rows (GATEUP: ROWS/2 gate rows and the matching up rows).
+template <int TOK, bool GATEUP>
+__global__ void __launch_bounds__(256) gemv_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
+                                                   const float* __restrict__ bias, int epilogue, const __nv_bfloat16* __restrict__ R,
+                                                   void* __restrict__ Y, int out_f32, int N, int K) {
+    constexpr int ROWS = 4;
+    constexpr int OUTS = GATEUP ? ROWS / 2 : ROWS;
+    const int warp = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int o0 = warp * OUTS;  // first output of this warp
+    if (o0 >= N) return;
+    const uint4* wrow[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        int row;
+        if (GATEUP) row = (r < OUTS) ? o0 + r : N + o0 + (r - OUTS);
+        else row = o0 + r;
+        const int lim = GATEUP ? 2 * N : N;
+        if (row >= lim) row = lim - 1;
+        wrow[r] = reinterpret_cast<const uint4*>(W + (size_t)row * K);
+    }
+    float acc[ROWS][TOK];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) acc[r][t] = 0.0f;
+    const int nvec = K / 8;
+#pragma unroll 4
+    for (int v = lane; v < nvec; v += 32) {
+        uint4 w[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) w[r] = __ldcs(wrow[r] + v);
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(X + (size_t)t * K) + v);
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc[r][t] += dot8(w[r], x);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) acc[r][t] = warp_sum(acc[r][t]);
+    if (lane == 0) {
+#pragma unroll
+        for (int o = 0; o < OUTS; ++o) {
+            const int n = o0 + o;
+            if (n >= N) break;
+#pragma unroll
+            for (int t = 0; t < TOK; ++t) {
+                float v = acc[o][t] + (bias ? bias[n] : 0.0f);
+                if (GATEUP) v = silu_f(v) * acc[o + OUTS][t];
+                else if (epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
+                else if (epilogue == LIN_GELU) v = gelu_f(v);
+                else if (epilogue == LIN_RESIDUAL) v += __bfloat162float(R[(size_t)t * N + n]);
+                if (out_f32) reinterpret_cast<float*>(Y)[(size_t)t * N + n] = v;
+                else reinterpret_cast<__nv_bfloat16*>(Y)[(size_t)t * N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+template <int TOK>
+static void launch_gemv(const void* X, const void* W, const float* bias, int epi, const void* R, void* Y, int out_f32, int N, int K,
+                        cudaStream_t st) {
+    const bool gu = epi == LIN_SILU_MUL;
+    const int outs_per_warp = gu ? 2 : 4;
+    const int warps = (N + outs_per_warp - 1) / outs_per_warp;
+    const int blocks = (warps + 7) / 8;
+    if (gu)
+        gemv_kernel<TOK, true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                                                       (const __nv_bfloat16*)R, Y, out_f32, N, K);
+    else
+        gemv_kernel<TOK, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                                                        (const __nv_bfloat16*)R, Y, out_f32, N, K);
+}
+
+template <int BN, bool GATEUP>
+static jsm_status launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& P, int splits, cudaStream_t st) {
+    constexpr int A_BYTES = BM * BK * 2 * (GATEUP ? 2 : 1);
+    constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
+    int stages = (200 * 1024) / STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    if (stages < 2) stages = 2;
+    const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+    static bool attr_done = false;  // per instantiation
+    if (!attr_done) {
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_tc_kernel<BN, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_done = true;
+    }
+    dim3 grid((P.N + BM - 1) / BM, (P.T + BN - 1) / BN, splits);
+    linear_tc_kernel<BN, GATEUP><<<grid, TC_THREADS, smem, st>>>(mw, mx, P, stages);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st) {
+    if (a.T <= 0 || a.N <= 0) return JSM_OK;
+    if (!a.X || !a.W || !a.Y) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: null pointer");
+    if (a.K <= 0 || a.K % 8) JSM_FAIL(JSM_UNSUPPORTED, "linear_bf16: K (%d) must be a positive multiple of 8", a.K);
+    if (a.epilogue < LIN_NONE || a.epilogue > LIN_RESIDUAL) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: epilogue %d", a.epilogue);
+    if (a.epilogue == LIN_RESIDUAL && !a.R) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: residual epilogue without R");
+    if (a.splits > 1 && (a.out_mode != 2 || a.epilogue != LIN_NONE))
+        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K writes raw f32 partials only");
+    const bool use_gemv = a.impl == 1 || (a.impl == 0 && a.T <= 4 && a.splits <= 1 && a.out_mode != 2);
+    if (use_gemv) {
+        if (a.T > 4) JSM_FAIL(JSM_UNSUPPORTED, "linear_bf16: the CUDA-core kernel takes at most 4 tokens");
+        const int f32 = a.out_mode == 1;
+        switch (a.T) {
+            case 1: launch_gemv<1>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
+            case 2: launch_gemv<2>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
+            case 3: launch_gemv<3>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
+            default: launch_gemv<4>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
+        }
+        JSM_LAUNCH_CHECK();
+        return JSM_OK;
+    }
+    const bool gu = a.epilogue == LIN_SILU_MUL;
+    CUtensorMap mw, mx;
+    const int bn = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : 128;
+    jsm_status s = make_tmap_bf16_2d(&mw, a.W, (uint64_t)(gu ? 2 * a.N : a.N), (uint64_t)a.K, (uint64_t)a.K, BM, BK);
+    if (s != JSM_OK) return s;
+    s = make_tmap_bf16_2d(&mx, a.X, (uint64_t)a.T, (uint64_t)a.K, (uint64_t)a.K, bn, BK);
+    if (s != JSM_OK) return s;
+    TcParams P;
+    P.T = a.T; P.N = a.N; P.K = a.K;
+    const int kb_total = (a.K + BK - 1) / BK;
+    const int splits = a.splits < 1 ? 1 : (a.splits > kb_total ? kb_total : a.splits);
+    P.kb_per_split = (kb_total + splits - 1) / splits;
+    P.epilogue = a.epilogue; P.out_mode = a.out_mode; P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y;
+    P.err = tc_error_word();
+    const int grid_z = a.out_mode == 2 ? (a.splits < 1 ? 1 : a.splits) : 1;
+    if (gu) {
+        switch (bn) {
+            case 16: return launch_tc<16, true>(mw, mx, P, grid_z, st);
+            case 32: return launch_tc<32, true>(mw, mx, P, grid_z, st);
+            case 64: return launch_tc<64, true>(mw, mx, P, grid_z, st);
+            default: return launch_tc<128, true>(mw, mx, P, grid_z, st);
+        }
+    }
+    switch (bn) {
+        case 16: return launch_tc<16, false>(mw, mx, P, grid_z, st);
+        case 32: return launch_tc<32, false>(mw, mx, P, grid_z, st);
+        case 64: return launch_tc<64, false>(mw, mx, P, grid_z, st);
+        default: return launch_tc<128, false>(mw, mx, P, grid_z, st);
+    }
+}
+
+jsm_status tc_check_error(cudaStream_t st, const char* who) {
+    int* w = tc_error_word();
+    if (!w) return JSM_OK;
+    int h = 0;
+    JSM_CUDA_CHECK(cudaMemcpyAsync(&h, w, sizeof(int), cudaMemcpyDeviceToHost, st));
+    JSM_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (h != 0) {
+        cudaMemsetAsync(w, 0, sizeof(int), st);
+        JSM_FAIL(JSM_TIMEOUT, "%s: a bounded device-side wait ran out (code %d)", who, h);
+    }
+    return JSM_OK;
+}
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" jsm_status jsm_linear_bf16(const void* d_X, const void* d_W, const float* d_bias, int epilogue, const void* d_R,
+                                      void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
+    if (out_dtype != JSM_BF16 && out_dtype != JSM_F32) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16: out dtype %d", out_dtype);
+    LinearArgs a;
+    a.X = d_X; a.W = d_W; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.Y = d_Y;
+    a.out_mode = out_dtype == JSM_F32 ? 1 : 0;
+    a.T = T; a.N = N; a.K = K; a.splits = 1; a.impl = 0;
+    return linear_bf16_launch(a, as_stream(stream));
+}

@@ -1,0 +1,523 @@
+// Decoder-only LLaMA-shape model on one GPU (one tensor-parallel rank): weights,
+// paged KV cache, prefill and greedy decode step.  The block wiring is composed
+// from the library's kernels the way the reference composes its stack from nets
+// (encoder_t::forward loops the layers, mat_transformer_kernel_t.hpp:103-110;
+// residual_net_t adds f(x) + x, mat_net_t.hpp:326-329), with the LLaMA parts the
+// reference lacks (RMSNorm, SwiGLU, dense QKV, RoPE on q/k, GQA, token embedding,
+// logits and argmax).
+//
+// Tensor parallelism: query/kv heads and FFN columns are split across tp_size
+// ranks (one process per GPU).  The partial outputs of the attention output
+// projection and of the FFN down projection are summed by one all-reduce each,
+// issued through a callback so that the host owns the communicator.
+#include "common.cuh"
+#include "linear_bf16.cuh"
+#include "attn.cuh"
+#include <math.h>
+#include <string.h>
+#include <string>
+#include <vector>
+
+namespace jsm {
+
+struct LayerW {
+    float* g1;
+    __nv_bfloat16* wqkv;  // [(Hq_l + 2 Hkv_l) * D, d]
+    __nv_bfloat16* wo;    // [d, Hq_l * D]
+    float* g2;
+    __nv_bfloat16* wgu;   // [2 * ffn_l, d]: gate rows, then up rows
+    __nv_bfloat16* wdown; // [d, ffn_l]
+    __nv_bfloat16* pool;  // KV pages of this layer
+};
+
+}  // namespace jsm
+
+struct jsm_model {
+    jsm_model_config c;
+    int Hq_l, Hkv_l, ffn_l, qkv_dim, pages_per_seq, max_tokens, max_splits;
+    std::vector<jsm::LayerW> layers;
+    __nv_bfloat16* emb = nullptr;
+    __nv_bfloat16* lm_head = nullptr;
+    float* gf = nullptr;
+    float* rope = nullptr;
+    int32_t* block_table = nullptr;
+    int32_t* ctx = nullptr;      // context length per sequence (device)
+    int32_t* pos = nullptr;      // scratch: positions of the tokens of the current call
+    int32_t* seq_ids = nullptr;  // scratch: sequence of each token of the current call
+    __nv_bfloat16 *h = nullptr, *xn = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *red = nullptr;
+    float* partial = nullptr;
+    float* logits = nullptr;
+    float* dec_scratch = nullptr;
+    std::vector<void*> allocs;
+    jsm_allreduce_fn allreduce = nullptr;
+    void* allreduce_user = nullptr;
+    uint64_t weight_bytes = 0;
+};
+
+namespace jsm {
+
+// value (r, c) of a shard = element ((row0 + r) * full_cols + col0 + c) of the full tensor: all TP layouts agree
+__global__ void fill_shard_kernel(__nv_bfloat16* dst, long long rows, long long cols, long long full_cols, long long row0,
+                                  long long col0, uint64_t key, float std) {
+    const long long n = rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols, c = i % cols;
+        const float v = rng_value(key, (uint64_t)((row0 + r) * full_cols + col0 + c), 0, 0.0f, std);
+        dst[i] = __float2bfloat16_rn(v);
+    }
+}
+__global__ void fill_const_kernel(float* dst, long long n, float v) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = v;
+}
+__global__ void iota_kernel(int32_t* pos, int32_t* seq_ids, int T, int seq, int pos0) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < T) { pos[i] = pos0 + i; seq_ids[i] = seq; }
+}
+__global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = value; }
+// decode bookkeeping on the device so that a captured step can be replayed: the new token of
+// sequence b goes to position ctx[b], then the context grows by one
+__global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) { pos[b] = ctx[b]; seq_ids[b] = b; ctx[b] = ctx[b] + 1; }
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* smem) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += smem[w];
+    return s;
+}
+
+// h[t,:] += sum_s partial[s][t][:] (+ delta[t,:]); h stored in bf16; y = RMSNorm(h) * gain.
+// One CTA per token, d <= 256 * 8 * MAXV.
+template <int MAXV>
+__global__ void __launch_bounds__(256) fold_add_norm_kernel(__nv_bfloat16* __restrict__ h, const float* __restrict__ partial, int splits,
+                                                            long long split_stride, const __nv_bfloat16* __restrict__ delta,
+                                                            const float* __restrict__ gain, float eps, __nv_bfloat16* __restrict__ y, int d) {
+    __shared__ float smem[8];
+    const long long base = (long long)blockIdx.x * d;
+    float v[MAXV][8];
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < d) {
+            const uint4 w = *reinterpret_cast<const uint4*>(h + base + c);
+            v[i][0] = bf16lo(w.x); v[i][1] = bf16hi(w.x); v[i][2] = bf16lo(w.y); v[i][3] = bf16hi(w.y);
+            v[i][4] = bf16lo(w.z); v[i][5] = bf16hi(w.z); v[i][6] = bf16lo(w.w); v[i][7] = bf16hi(w.w);
+            for (int s = 0; s < splits; ++s) {
+                const float4 a = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c);
+                const float4 b = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c + 4);
+                v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+                v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+            }
+            if (delta) {
+                const uint4 e = *reinterpret_cast<const uint4*>(delta + base + c);
+                v[i][0] += bf16lo(e.x); v[i][1] += bf16hi(e.x); v[i][2] += bf16lo(e.y); v[i][3] += bf16hi(e.y);
+                v[i][4] += bf16lo(e.z); v[i][5] += bf16hi(e.z); v[i][6] += bf16lo(e.w); v[i][7] += bf16hi(e.w);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[i][0], v[i][1]); o.y = pack_bf16x2(v[i][2], v[i][3]);
+            o.z = pack_bf16x2(v[i][4], v[i][5]); o.w = pack_bf16x2(v[i][6], v[i][7]);
+            if (splits > 0 || delta) *reinterpret_cast<uint4*>(h + base + c) = o;
+            // normalise what was stored
+            v[i][0] = bf16lo(o.x); v[i][1] = bf16hi(o.x); v[i][2] = bf16lo(o.y); v[i][3] = bf16hi(o.y);
+            v[i][4] = bf16lo(o.z); v[i][5] = bf16hi(o.z); v[i][6] = bf16lo(o.w); v[i][7] = bf16hi(o.w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q += v[i][j] * v[i][j];
+        }
+    }
+    if (!y) return;
+    q = block_sum_256(q, smem) / (float)d;
+    const float sd = sqrtf(q + eps);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < d) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = gain[c + j] * (v[i][j] / sd);
+            uint4 w;
+            w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]); w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(y + base + c) = w;
+        }
+    }
+}
+
+// out[t,:] = bf16(sum_s partial[s][t][:]) : the rank-local sum that goes into the all-reduce
+__global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partial, int splits, long long split_stride,
+                                                            __nv_bfloat16* __restrict__ out, long long n) {
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+        float4 a = *reinterpret_cast<const float4*>(partial + i);
+        for (int s = 1; s < splits; ++s) {
+            const float4 b = *reinterpret_cast<const float4*>(partial + s * split_stride + i);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        uint2 o;
+        o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+        *reinterpret_cast<uint2*>(out + i) = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const float* row = x + (long long)blockIdx.x * n;
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float v = row[i];
+        if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, m, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+        if (ov > m || (ov == m && oi < mi)) { m = ov; mi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = m; si[threadIdx.x >> 5] = mi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > m || (sv[w] == m && si[w] < mi)) { m = sv[w]; mi = si[w]; }
+        out[blockIdx.x] = mi == 0x7fffffff ? 0 : mi;
+    }
+}
+
+template <typename T>
+static jsm_status dev_alloc(jsm_model* m, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        JSM_FAIL(JSM_OOM, "jsm_llama_create: cudaMalloc of %zu bytes failed: %s", n * sizeof(T), cudaGetErrorString(e));
+    }
+    m->allocs.push_back(q);
+    *p = reinterpret_cast<T*>(q);
+    return JSM_OK;
+}
+
+static void fill_shard(__nv_bfloat16* dst, long long rows, long long cols, long long full_cols, long long row0, long long col0,
+                       uint64_t seed, uint64_t tid, float std, cudaStream_t st) {
+    const long long n = rows * cols;
+    long long blocks = (n + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    fill_shard_kernel<<<(unsigned)blocks, 256, 0, st>>>(dst, rows, cols, full_cols, row0, col0, rng_key(seed, tid), std);
+    g_launches.fetch_add(1);
+}
+
+static int pick_splits(int T, int N, int K) {
+    // enough CTAs to pull from every SM: tiles * splits >= ~SM count, each split at least 4 k-blocks
+    const int tiles = ((N + 127) / 128) * ((T + 127) / 128);
+    const int kb = (K + 63) / 64;
+    int s = (sm_count() + tiles - 1) / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && kb / s < 4) --s;
+    return s < 1 ? 1 : s;
+}
+
+// Y_partial = X . W^T into the residual stream h, then xn = RMSNorm(h) * gain (gain may be null: no norm)
+static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
+                                        const float* next_gain, cudaStream_t st) {
+    const bool tp = m->c.tp_size > 1;
+    LinearArgs a;
+    a.X = X; a.W = W; a.bias = nullptr; a.R = nullptr; a.T = T; a.N = N; a.K = K; a.impl = 0;
+    const int d = m->c.d_model;
+    if (T <= 4) {
+        if (!tp) {
+            a.epilogue = LIN_RESIDUAL; a.R = m->h; a.Y = m->h; a.out_mode = 0; a.splits = 1;
+            jsm_status s = linear_bf16_launch(a, st);
+            if (s != JSM_OK) return s;
+            if (next_gain) {
+                fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d);
+                JSM_LAUNCH_CHECK();
+            }
+            return JSM_OK;
+        }
+        a.epilogue = LIN_NONE; a.Y = m->red; a.out_mode = 0; a.splits = 1;
+        jsm_status s = linear_bf16_launch(a, st);
+        if (s != JSM_OK) return s;
+    } else {
+        const int splits = pick_splits(T, N, K);
+        a.epilogue = LIN_NONE; a.Y = m->partial; a.out_mode = 2; a.splits = splits;
+        jsm_status s = linear_bf16_launch(a, st);
+        if (s != JSM_OK) return s;
+        if (!tp) {
+            fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, m->partial, splits, (long long)T * N, nullptr, next_gain, m->c.norm_eps,
+                                                       next_gain ? m->xn : nullptr, d);
+            JSM_LAUNCH_CHECK();
+            return JSM_OK;
+        }
+        const long long n = (long long)T * N;
+        long long blocks = (n / 4 + 255) / 256;
+        if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
+        fold_partials_kernel<<<(unsigned)blocks, 256, 0, st>>>(m->partial, splits, n, m->red, n);
+        JSM_LAUNCH_CHECK();
+    }
+    // tensor parallel: sum the rank-local outputs, then add into the residual stream
+    if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
+    if (m->allreduce(m->red, (size_t)T * N, JSM_BF16, st, m->allreduce_user) != 0) JSM_FAIL(JSM_NCCL, "all-reduce callback failed");
+    fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, m->red, next_gain, m->c.norm_eps, next_gain ? m->xn : nullptr, d);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool decode, int batch, int prefill_seq, cudaStream_t st) {
+    const jsm_model_config& c = m->c;
+    const int d = c.d_model, D = c.head_dim;
+    jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
+    if (s != JSM_OK) return s;
+    fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, m->layers[0].g1, c.norm_eps, m->xn, d);
+    JSM_LAUNCH_CHECK();
+    const float scale = 1.0f / sqrtf((float)D);
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerW& L = m->layers[l];
+        LinearArgs a;
+        a.X = m->xn; a.W = L.wqkv; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = m->qkv; a.out_mode = 0;
+        a.T = T; a.N = m->qkv_dim; a.K = d; a.splits = 1; a.impl = 0;
+        s = linear_bf16_launch(a, st);
+        if (s != JSM_OK) return s;
+        const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
+        const __nv_bfloat16* vv = kk + (long long)m->Hkv_l * D;
+        s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
+        if (s != JSM_OK) return s;
+        if (decode) {
+            s = jsm_attn_decode(m->qkv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch, m->Hq_l, m->Hkv_l, D, scale,
+                                m->rope, c.max_context, m->dec_scratch, m->attn, st);
+        } else {
+            // prompt of one sequence starting at position 0: attention over the fresh q, k, v with RoPE applied on load
+            const bool flash = flash_available() && T >= 128;
+            if (flash)
+                s = flash_prefill_launch(m->qkv, kk, vv, m->attn, 1, T, T, m->Hq_l, m->Hkv_l, 1, scale, m->rope, st, m->qkv_dim,
+                                         m->qkv_dim, (long long)m->Hq_l * D);
+            else
+                s = attn_simt_launch(m->qkv, kk, vv, m->attn, JSM_BF16, 1, T, T, m->Hq_l, m->Hkv_l, D, 1, scale, m->rope, st,
+                                     m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
+        }
+        if (s != JSM_OK) return s;
+        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, L.g2, st);
+        if (s != JSM_OK) return s;
+        a.X = m->xn; a.W = L.wgu; a.epilogue = LIN_SILU_MUL; a.Y = m->act; a.N = m->ffn_l; a.K = d;
+        s = linear_bf16_launch(a, st);
+        if (s != JSM_OK) return s;
+        const float* next_gain = (l + 1 < c.n_layers) ? m->layers[l + 1].g1 : m->gf;
+        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, next_gain, st);
+        if (s != JSM_OK) return s;
+    }
+    (void)prefill_seq;
+    return JSM_OK;
+}
+
+static jsm_status logits_and_argmax(jsm_model* m, const __nv_bfloat16* xn_rows, int rows, int32_t* d_next, float* d_logits,
+                                    cudaStream_t st) {
+    float* lg = d_logits ? d_logits : m->logits;
+    LinearArgs a;
+    a.X = xn_rows; a.W = m->lm_head; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = lg; a.out_mode = 1;
+    a.T = rows; a.N = m->c.vocab; a.K = m->c.d_model; a.splits = 1; a.impl = 0;
+    jsm_status s = linear_bf16_launch(a, st);
+    if (s != JSM_OK) return s;
+    if (d_next) {
+        argmax_rows_kernel<<<rows, 256, 0, st>>>(lg, d_next, m->c.vocab);
+        JSM_LAUNCH_CHECK();
+    }
+    return JSM_OK;
+}
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" {
+
+jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_model** out) {
+    if (!cfg || !out) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_create: null argument");
+    *out = nullptr;
+    const jsm_model_config& c = *cfg;
+    if (c.n_layers <= 0 || c.d_model <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.d_ffn <= 0 || c.vocab <= 0 || c.max_batch <= 0 ||
+        c.max_context <= 0)
+        JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_create: non-positive dimension");
+    if (c.head_dim != 128) JSM_FAIL(JSM_UNSUPPORTED, "jsm_llama_create: head_dim %d (128 only)", c.head_dim);
+    if (c.n_heads % c.n_kv_heads) JSM_FAIL(JSM_SHAPE, "d_model must be divisible by num_heads (heads %d, kv heads %d)", c.n_heads, c.n_kv_heads);
+    if (c.tp_size < 1 || c.tp_rank < 0 || c.tp_rank >= c.tp_size) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_create: tp rank %d of %d", c.tp_rank, c.tp_size);
+    if (c.n_kv_heads % c.tp_size || c.d_ffn % c.tp_size || (c.d_ffn / c.tp_size) % 8)
+        JSM_FAIL(JSM_SHAPE, "jsm_llama_create: kv heads %d / ffn %d not divisible across %d ranks", c.n_kv_heads, c.d_ffn, c.tp_size);
+    if (c.d_model % 8 || c.d_model > 4096) JSM_FAIL(JSM_UNSUPPORTED, "jsm_llama_create: d_model %d (multiple of 8, <= 4096)", c.d_model);
+    int ndev = 0;
+    jsm_status s = jsm_device_count(&ndev);
+    if (s != JSM_OK) return s;
+    if (ndev == 0) JSM_FAIL(JSM_CUDA, "jsm_llama_create: no CUDA device");
+
+    jsm_model* m = new jsm_model();
+    m->c = c;
+    m->Hq_l = c.n_heads / c.tp_size;
+    m->Hkv_l = c.n_kv_heads / c.tp_size;
+    m->ffn_l = c.d_ffn / c.tp_size;
+    const int D = c.head_dim, d = c.d_model;
+    m->qkv_dim = (m->Hq_l + 2 * m->Hkv_l) * D;
+    m->pages_per_seq = (c.max_context + JSM_PAGE_SIZE - 1) / JSM_PAGE_SIZE;
+    m->max_tokens = c.max_batch > 512 ? c.max_batch : 512;
+    m->max_splits = 8;
+    m->layers.resize(c.n_layers);
+    cudaStream_t st = nullptr;
+    const float std = 0.02f;
+#define JSM_TRY(x)                  \
+    do {                            \
+        jsm_status s__ = (x);       \
+        if (s__ != JSM_OK) {        \
+            jsm_llama_destroy(m);   \
+            return s__;             \
+        }                           \
+    } while (0)
+    const long long n_pages = (long long)c.max_batch * m->pages_per_seq;
+    const size_t page_elems = (size_t)2 * m->Hkv_l * JSM_PAGE_SIZE * D;
+    uint64_t wbytes = 0;
+    for (int l = 0; l < c.n_layers; ++l) {
+        LayerW& L = m->layers[l];
+        const uint64_t t0 = (uint64_t)l * 16;
+        JSM_TRY(dev_alloc(m, &L.g1, (size_t)d));
+        JSM_TRY(dev_alloc(m, &L.g2, (size_t)d));
+        JSM_TRY(dev_alloc(m, &L.wqkv, (size_t)m->qkv_dim * d));
+        JSM_TRY(dev_alloc(m, &L.wo, (size_t)d * m->Hq_l * D));
+        JSM_TRY(dev_alloc(m, &L.wgu, (size_t)2 * m->ffn_l * d));
+        JSM_TRY(dev_alloc(m, &L.wdown, (size_t)d * m->ffn_l));
+        JSM_TRY(dev_alloc(m, &L.pool, (size_t)n_pages * page_elems));
+        fill_const_kernel<<<16, 256, 0, st>>>(L.g1, d, 1.0f);
+        fill_const_kernel<<<16, 256, 0, st>>>(L.g2, d, 1.0f);
+        // full tensors: wq [Hq*D, d] (id +0), wk [Hkv*D, d] (+1), wv (+2), wo [d, Hq*D] (+3), wgate [ffn, d] (+4), wup (+5), wdown [d, ffn] (+6)
+        const long long qr = (long long)m->Hq_l * D, kr = (long long)m->Hkv_l * D;
+        fill_shard(L.wqkv, qr, d, d, c.tp_rank * qr, 0, seed, t0 + 0, std, st);
+        fill_shard(L.wqkv + qr * d, kr, d, d, c.tp_rank * kr, 0, seed, t0 + 1, std, st);
+        fill_shard(L.wqkv + (qr + kr) * d, kr, d, d, c.tp_rank * kr, 0, seed, t0 + 2, std, st);
+        fill_shard(L.wo, d, qr, (long long)c.n_heads * D, 0, c.tp_rank * qr, seed, t0 + 3, std, st);
+        fill_shard(L.wgu, m->ffn_l, d, d, (long long)c.tp_rank * m->ffn_l, 0, seed, t0 + 4, std, st);
+        fill_shard(L.wgu + (long long)m->ffn_l * d, m->ffn_l, d, d, (long long)c.tp_rank * m->ffn_l, 0, seed, t0 + 5, std, st);
+        fill_shard(L.wdown, d, m->ffn_l, c.d_ffn, 0, (long long)c.tp_rank * m->ffn_l, seed, t0 + 6, std, st);
+        wbytes += 2ull * ((uint64_t)m->qkv_dim * d + (uint64_t)d * m->Hq_l * D + 2ull * m->ffn_l * d + (uint64_t)d * m->ffn_l) + 8ull * d;
+    }
+    JSM_TRY(dev_alloc(m, &m->emb, (size_t)c.vocab * d));
+    JSM_TRY(dev_alloc(m, &m->lm_head, (size_t)c.vocab * d));
+    JSM_TRY(dev_alloc(m, &m->gf, (size_t)d));
+    fill_shard(m->emb, c.vocab, d, d, 0, 0, seed, 1000000, std, st);
+    fill_shard(m->lm_head, c.vocab, d, d, 0, 0, seed, 1000001, std, st);
+    fill_const_kernel<<<16, 256, 0, st>>>(m->gf, d, 1.0f);
+    wbytes += 2ull * (uint64_t)c.vocab * d + 4ull * d;
+    m->weight_bytes = wbytes;
+    JSM_TRY(dev_alloc(m, &m->rope, (size_t)c.max_context * (D / 2) * 4));
+    JSM_TRY(jsm_rope_table(m->rope, 1, D, c.rope_theta, c.max_context, st));
+    JSM_TRY(dev_alloc(m, &m->block_table, (size_t)n_pages));
+    {
+        std::vector<int32_t> bt((size_t)n_pages);
+        for (long long i = 0; i < n_pages; ++i) bt[(size_t)i] = (int32_t)i;
+        cudaError_t e = cudaMemcpy(m->block_table, bt.data(), bt.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: block table upload: %s", cudaGetErrorString(e)); }
+    }
+    JSM_TRY(dev_alloc(m, &m->ctx, (size_t)c.max_batch));
+    JSM_TRY(dev_alloc(m, &m->pos, (size_t)m->max_tokens));
+    JSM_TRY(dev_alloc(m, &m->seq_ids, (size_t)m->max_tokens));
+    const size_t Tm = (size_t)m->max_tokens;
+    JSM_TRY(dev_alloc(m, &m->h, Tm * d));
+    JSM_TRY(dev_alloc(m, &m->xn, Tm * d));
+    JSM_TRY(dev_alloc(m, &m->red, Tm * d));
+    JSM_TRY(dev_alloc(m, &m->qkv, Tm * m->qkv_dim));
+    JSM_TRY(dev_alloc(m, &m->attn, Tm * m->Hq_l * D));
+    JSM_TRY(dev_alloc(m, &m->act, Tm * m->ffn_l));
+    JSM_TRY(dev_alloc(m, &m->partial, (size_t)m->max_splits * Tm * d));
+    JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
+    JSM_TRY(dev_alloc(m, &m->dec_scratch, jsm_attn_decode_scratch_bytes(c.max_batch, m->Hq_l, D, c.max_context) / sizeof(float) + 4));
+    cudaError_t e = cudaMemset(m->ctx, 0, sizeof(int32_t) * c.max_batch);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: initialisation failed: %s", cudaGetErrorString(e)); }
+#undef JSM_TRY
+    *out = m;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_destroy(jsm_model* m) {
+    if (!m) return JSM_OK;
+    cudaDeviceSynchronize();
+    for (void* p : m->allocs) cudaFree(p);
+    delete m;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user) {
+    if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_set_allreduce: null model");
+    m->allreduce = fn;
+    m->allreduce_user = user;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_weight(jsm_model* m, const char* name, void** d_ptr, size_t* n_elems) {
+    if (!m || !name || !d_ptr || !n_elems) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_weight: null argument");
+    const int d = m->c.d_model, D = m->c.head_dim;
+    std::string s(name);
+    if (s == "emb") { *d_ptr = m->emb; *n_elems = (size_t)m->c.vocab * d; return JSM_OK; }
+    if (s == "lm_head") { *d_ptr = m->lm_head; *n_elems = (size_t)m->c.vocab * d; return JSM_OK; }
+    if (s == "gf") { *d_ptr = m->gf; *n_elems = d; return JSM_OK; }
+    int l = -1;
+    char field[32] = "";
+    if (sscanf(name, "layers.%d.%31s", &l, field) == 2 && l >= 0 && l < m->c.n_layers) {
+        LayerW& L = m->layers[l];
+        std::string f(field);
+        if (f == "g1") { *d_ptr = L.g1; *n_elems = d; return JSM_OK; }
+        if (f == "g2") { *d_ptr = L.g2; *n_elems = d; return JSM_OK; }
+        if (f == "wqkv") { *d_ptr = L.wqkv; *n_elems = (size_t)m->qkv_dim * d; return JSM_OK; }
+        if (f == "wo") { *d_ptr = L.wo; *n_elems = (size_t)d * m->Hq_l * D; return JSM_OK; }
+        if (f == "wgu") { *d_ptr = L.wgu; *n_elems = (size_t)2 * m->ffn_l * d; return JSM_OK; }
+        if (f == "wdown") { *d_ptr = L.wdown; *n_elems = (size_t)d * m->ffn_l; return JSM_OK; }
+    }
+    JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_weight: unknown tensor '%s'", name);
+}
+
+jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T, int32_t* d_next, float* d_logits_last, void* stream) {
+    if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_prefill: null argument");
+    if (seq < 0 || seq >= m->c.max_batch) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_prefill: sequence %d outside 0..%d", seq, m->c.max_batch - 1);
+    if (T <= 0 || T > m->max_tokens || T > m->c.max_context) JSM_FAIL(JSM_SHAPE, "jsm_llama_prefill: %d tokens (1..%d)", T, m->max_tokens);
+    cudaStream_t st = as_stream(stream);
+    iota_kernel<<<(T + 255) / 256, 256, 0, st>>>(m->pos, m->seq_ids, T, seq, 0);
+    JSM_LAUNCH_CHECK();
+    jsm_status s = forward_tokens(m, d_ids, T, false, 1, seq, st);
+    if (s != JSM_OK) return s;
+    set_ctx_kernel<<<1, 1, 0, st>>>(m->ctx, seq, T);
+    JSM_LAUNCH_CHECK();
+    const __nv_bfloat16* last = m->xn + (long long)(T - 1) * m->c.d_model;
+    return logits_and_argmax(m, last, 1, d_next ? d_next + seq : nullptr, d_logits_last, st);
+}
+
+jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, int32_t* d_next, float* d_logits, void* stream) {
+    if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step: null argument");
+    if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step: batch %d (1..%d)", batch, m->c.max_batch);
+    cudaStream_t st = as_stream(stream);
+    advance_kernel<<<(batch + 255) / 256, 256, 0, st>>>(m->ctx, m->pos, m->seq_ids, batch);
+    JSM_LAUNCH_CHECK();
+    jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
+    if (s != JSM_OK) return s;
+    return logits_and_argmax(m, m->xn, batch, d_next, d_logits, st);
+}
+
+jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len) {
+    if (!m || seq < 0 || seq >= m->c.max_batch || context_len < 0 || context_len > m->c.max_context)
+        JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_set_context: sequence %d, length %d", seq, context_len);
+    JSM_CUDA_CHECK(cudaMemcpy(m->ctx + seq, &context_len, sizeof(int32_t), cudaMemcpyHostToDevice));
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_reset(jsm_model* m) {
+    if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_reset: null model");
+    JSM_CUDA_CHECK(cudaMemset(m->ctx, 0, sizeof(int32_t) * m->c.max_batch));
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_step_bytes(jsm_model* m, uint64_t* weight_bytes, uint64_t* kv_bytes_per_token) {
+    if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_step_bytes: null model");
+    // the embedding table is gathered, not streamed: one row per token
+    if (weight_bytes) *weight_bytes = m->weight_bytes - 2ull * (uint64_t)m->c.vocab * m->c.d_model;
+    if (kv_bytes_per_token) *kv_bytes_per_token = (uint64_t)m->c.n_layers * 2ull * m->Hkv_l * m->c.head_dim * 2ull;
+    return JSM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+// Table-driven rotary position embedding.
+// The table holds, per (position m, pair i), (cos A, sin A, cos B, sin B) and the
+// rotation is out0 = cosA*x0 - sinB*x1, out1 = sinA*x0 + cosB*x1: the 2x2 block
+// product of RoPE_net_t::forward (mat_RoPE_t.hpp:166-188) with the table of
+// mat_RoPE_t::init (:99-134).  In the reference's table the block of position m
+// uses column 2m for its first column and 2m+1 for its second, i.e. A and B are
+// two different angles; "standard" mode sets A = B = m / theta^(2i/d).
+// The table is computed on the host with the reference's roundings (double pow,
+// double quotient narrowed to float, float cos/sin) and uploaded.
+#include "common.cuh"
+#include <cmath>
+#include <vector>
+
+namespace jsm {
+
+template <typename T>
+__global__ void rope_apply_kernel(const T* __restrict__ x, T* __restrict__ out, const float4* __restrict__ table, int d,
+                                  int n_heads, const int32_t* __restrict__ positions, int T_tokens) {
+    const int half = d / 2;
+    const long long total = (long long)T_tokens * n_heads * half;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int pair = (int)(i % half);
+        const long long th = i / half;  // token * n_heads + head
+        const int t = (int)(th / n_heads);
+        const int m = positions ? positions[t] : t;
+        const float4 e = table[(long long)m * half + pair];
+        const long long base = th * d + 2 * pair;
+        float x0, x1;
+        if constexpr (sizeof(T) == 4) {
+            float2 v = *reinterpret_cast<const float2*>(x + base);
+            x0 = v.x; x1 = v.y;
+        } else {
+            uint32_t w = *reinterpret_cast<const uint32_t*>(x + base);
+            x0 = bf16lo(w); x1 = bf16hi(w);
+        }
+        // (0 + cosA*x0) + (-sinB)*x1 and (0 + sinA*x0) + cosB*x1, each product rounded on its own
+        const float o0 = __fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1));
+        const float o1 = __fadd_rn(__fmul_rn(e.y, x0), __fmul_rn(e.z, x1));
+        if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float2*>(out + base) = make_float2(o0, o1);
+        } else {
+            *reinterpret_cast<uint32_t*>(out + base) = pack_bf16x2(o0, o1);
+        }
+    }
+}
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" jsm_status jsm_rope_table(float* d_table, int mode, int d, float theta, int max_pos, void* stream) {
+    if (!d_table) JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_table: null table");
+    if (d <= 0 || d % 2 || max_pos <= 0 || (mode != 0 && mode != 1))
+        JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_table: d %d, max_pos %d, mode %d", d, max_pos, mode);
+    const int half = d / 2;
+    std::vector<float> h((size_t)max_pos * half * 4);
+    std::vector<double> p(half);
+    for (int i = 0; i < half; ++i)
+        p[i] = std::pow((double)theta, (double)((mode == 0 ? (float)i : (float)(2 * i)) / (float)d));
+    for (int m = 0; m < max_pos; ++m)
+        for (int i = 0; i < half; ++i) {
+            float a, b;
+            if (mode == 0) {
+                a = (float)((2 * m) / p[i]);
+                b = (float)((2 * m + 1) / p[i]);
+            } else {
+                a = b = (float)(m / p[i]);
+            }
+            float* e = &h[((size_t)m * half + i) * 4];
+            e[0] = std::cos(a); e[1] = std::sin(a); e[2] = std::cos(b); e[3] = std::sin(b);
+        }
+    JSM_CUDA_CHECK(cudaMemcpyAsync(d_table, h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice, as_stream(stream)));
+    JSM_CUDA_CHECK(cudaStreamSynchronize(as_stream(stream)));
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_rope_apply(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
+                                     const int32_t* d_positions, int T, void* stream) {
+    if (T == 0) return JSM_OK;
+    if (!d_x || !d_out || !d_table) JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_apply: null pointer");
+    if (d <= 0 || d % 2 || n_heads <= 0 || T < 0) JSM_FAIL(JSM_SHAPE, "Input dimension does not match RoPE dimension (d %d)", d);
+    if (dtype != JSM_F32 && dtype != JSM_BF16) JSM_FAIL(JSM_UNSUPPORTED, "jsm_rope_apply: dtype %d", (int)dtype);
+    const long long total = (long long)T * n_heads * (d / 2);
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
+    if (dtype == JSM_F32)
+        rope_apply_kernel<float><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(
+            reinterpret_cast<const float*>(d_x), reinterpret_cast<float*>(d_out), reinterpret_cast<const float4*>(d_table), d,
+            n_heads, d_positions, T);
+    else
+        rope_apply_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(
+            reinterpret_cast<const __nv_bfloat16*>(d_x), reinterpret_cast<__nv_bfloat16*>(d_out),
+            reinterpret_cast<const float4*>(d_table), d, n_heads, d_positions, T);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}

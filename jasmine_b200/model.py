@@ -1,0 +1,73 @@
+"""Host-side handle of the decoder-only model of libjasmine_b200.so (jsm_llama_*), for tests and bench.py."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import ALLREDUCE_FN, BF16, F32, ModelConfig, check, lib, stream_ptr
+
+
+class Llama:
+    def __init__(self, n_layers, d_model, n_heads, n_kv_heads, d_ffn, vocab, max_batch, max_context, head_dim=128,
+                 norm_eps=1e-5, rope_theta=10000.0, seed=4, tp_rank=0, tp_size=1):
+        self.cfg = ModelConfig(n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ffn, vocab, max_batch, max_context,
+                               norm_eps, rope_theta, tp_rank, tp_size)
+        self._h = C.c_void_p()
+        check(lib().jsm_llama_create(C.byref(self.cfg), seed, C.byref(self._h)))
+        self._cb = None
+
+    def close(self):
+        if self._h:
+            check(lib().jsm_llama_destroy(self._h))
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_allreduce(self, fn):
+        """fn(ptr, count, dtype, stream) sums in place across the tensor-parallel group."""
+        def tramp(ptr, count, dtype, stream, _user):
+            try:
+                fn(ptr, count, dtype, stream)
+                return 0
+            except Exception:  # the library reports JSM_NCCL
+                import traceback
+                traceback.print_exc()
+                return 1
+        self._cb = ALLREDUCE_FN(tramp)
+        check(lib().jsm_llama_set_allreduce(self._h, self._cb, None))
+
+    def weight(self, name: str) -> np.ndarray:
+        """A weight of this rank's shard as float32 (bf16 tensors are widened)."""
+        p, n = C.c_void_p(), C.c_size_t()
+        check(lib().jsm_llama_weight(self._h, name.encode(), C.byref(p), C.byref(n)))
+        is_f32 = name.endswith(("g1", "g2", "gf"))
+        buf = np.empty(n.value, np.float32 if is_f32 else np.uint16)
+        check(lib().jsm_download(buf.ctypes.data, p, buf.nbytes, stream_ptr()))
+        if is_f32:
+            return buf
+        return (buf.astype(np.uint32) << 16).view(np.float32)
+
+    def prefill(self, ids, seq: int, next_tokens=None, logits_last=None):
+        check(lib().jsm_llama_prefill(self._h, ids.data_ptr(), seq, ids.numel(),
+                                      next_tokens.data_ptr() if next_tokens is not None else None,
+                                      logits_last.data_ptr() if logits_last is not None else None, stream_ptr()))
+
+    def decode_step(self, ids, next_tokens, logits=None):
+        check(lib().jsm_llama_decode_step(self._h, ids.data_ptr(), ids.numel(), next_tokens.data_ptr(),
+                                          logits.data_ptr() if logits is not None else None, stream_ptr()))
+
+    def set_context(self, seq: int, n: int):
+        check(lib().jsm_llama_set_context(self._h, seq, n))
+
+    def reset(self):
+        check(lib().jsm_llama_reset(self._h))
+
+    def step_bytes(self):
+        w, k = C.c_uint64(), C.c_uint64()
+        check(lib().jsm_llama_step_bytes(self._h, C.byref(w), C.byref(k)))
+        return w.value, k.value

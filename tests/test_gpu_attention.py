@@ -1,0 +1,121 @@
+"""GPU parity of RoPE and attention against the reference's golden vectors and the CPU oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import jasmine_b200 as jb
+import oracle_lib as ol
+from gpu_util import BF16_RTOL, FP32_RTOL, assert_close, dev, host
+
+pytestmark = pytest.mark.gpu
+OPS = np.load(Path(__file__).resolve().parent / "golden" / "ops.npz")
+port = ol.port_oracle()
+
+
+def test_rope_reference_mode_matches_reference():
+    """RoPE_net_t::forward over the whole feature vector, the reference's own table (two angles per block)."""
+    x = cases.rope_input()
+    T, d = x.shape
+    table = jb.rope_table(0, d, 10000.0, T)
+    assert np.array_equal(host(table), ol.rope_table(0, d, 10000.0, T))
+    y = jb.rope_apply(dev(x), table, d, 1)
+    assert np.array_equal(host(y), OPS["rope"])
+
+
+def test_rope_standard_mode_matches_oracle():
+    T, H, D = 37, 3, 128
+    x = cases.normal((T, H * D), 620, 0)
+    pos = np.arange(T, dtype=np.int32)[::-1].copy() * 3
+    table = jb.rope_table(1, D, 10000.0, 128)
+    tab_h = ol.rope_table(1, D, 10000.0, 128)
+    assert np.array_equal(host(table), tab_h)
+    y = jb.rope_apply(dev(x), table, D, H, positions=torch.from_numpy(pos).cuda())
+    assert np.array_equal(host(y), ol.rope_apply(x, tab_h, D, H, pos))
+    yb = jb.rope_apply(dev(x, torch.bfloat16), table, D, H, positions=torch.from_numpy(pos).cuda())
+    xb = dev(x, torch.bfloat16).float().cpu().numpy()
+    assert_close(host(yb), ol.rope_apply(xb, tab_h, D, H, pos), 8e-3, "bf16 rope")
+
+
+def mha_device(w, x, H, causal):
+    """mat_mha_t::forward (mat_mha_t.hpp:265-291) from C-ABI calls: block-diagonal per-head projections
+    (each head sees its own slice, :199-215), attention, concatenation, output projection."""
+    T, d = x.shape
+    dh = d // H
+    xd = dev(x)
+    q = torch.empty(T, d, device="cuda"); k = torch.empty_like(q); v = torch.empty_like(q)
+    o = 0
+    for h in range(H):
+        for dst in (q, k, v):
+            W = dev(w[o:o + dh * dh].reshape(dh, dh)); o += dh * dh
+            b = dev(w[o:o + dh].reshape(1, dh)); o += dh
+            # token-major: Y[T,dh] = X_h[T,dh] . W^T + b, same k-ascending sums as W . X
+            jb.dot_f32(xd[:, h * dh:(h + 1) * dh], W.t(), dst[:, h * dh:(h + 1) * dh], bias=b)
+    att = jb.attn_prefill(q, k, v, 1, H, H, dh, causal=causal, impl=1)
+    Wo = dev(w[o:o + d * d].reshape(d, d)); o += d * d
+    bo = dev(w[o:o + d].reshape(1, d))
+    out = torch.empty(T, d, device="cuda")
+    jb.dot_f32(att, Wo.t(), out, bias=bo)
+    return out
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_mha_forward_matches_reference(causal):
+    w, x = cases.mha_inputs()
+    out = mha_device(w, x, cases.MHA["H"], causal)
+    assert_close(host(out), OPS["mha_causal" if causal else "mha_full"], FP32_RTOL, "mat_mha_t::forward")
+
+
+def test_causal_prefix_property_on_device():
+    """test_sequence_mha (transformer_test.hpp:246-282): the outputs of a prefix do not change when
+    later tokens are appended."""
+    w, x = cases.mha_inputs()
+    H = cases.MHA["H"]
+    full = host(mha_device(w, x, H, True))
+    for s1 in (1, 5):
+        part = host(mha_device(w, x[:s1], H, True))
+        assert_close(part, full[:s1], 1e-6, f"prefix {s1}")
+
+
+@pytest.mark.parametrize("batch,Tq,Tk,Hq,Hkv,D", [(1, 1, 1, 1, 1, 2), (2, 9, 9, 4, 2, 32), (1, 70, 70, 2, 2, 128), (3, 5, 33, 8, 2, 64),
+                                                  (1, 1, 100, 4, 4, 128), (2, 40, 40, 3, 1, 30)])
+def test_attention_fp32_shapes(batch, Tq, Tk, Hq, Hkv, D):
+    q = cases.normal((batch * Tq, Hq * D), 630, 0)
+    k = cases.normal((batch * Tk, Hkv * D), 630, 1)
+    v = cases.normal((batch * Tk, Hkv * D), 630, 2)
+    for causal in (True, False):
+        got = jb.attn_prefill(dev(q), dev(k), dev(v), batch, Hq, Hkv, D, causal=causal, impl=1)
+        want = ol.attention(q, k, v, batch, Hq, Hkv, D, causal)
+        assert_close(host(got), want, FP32_RTOL, f"attention causal={causal}")
+
+
+def test_attention_with_fused_rope_fp32():
+    batch, T, Hq, Hkv, D = 2, 19, 4, 2, 64
+    q = cases.normal((batch * T, Hq * D), 640, 0)
+    k = cases.normal((batch * T, Hkv * D), 640, 1)
+    v = cases.normal((batch * T, Hkv * D), 640, 2)
+    table = jb.rope_table(1, D, 10000.0, T)
+    tab_h = ol.rope_table(1, D, 10000.0, T)
+    pos = np.tile(np.arange(T, dtype=np.int32), batch)
+    want = ol.attention(ol.rope_apply(q, tab_h, D, Hq, pos), ol.rope_apply(k, tab_h, D, Hkv, pos), v, batch, Hq, Hkv, D, True)
+    got = jb.attn_prefill(dev(q), dev(k), dev(v), batch, Hq, Hkv, D, causal=True, rope=table, impl=1)
+    assert_close(host(got), want, FP32_RTOL, "attention with RoPE on load")
+
+
+def test_attention_bf16_cuda_core_matches_oracle():
+    batch, T, Hq, Hkv, D = 1, 150, 4, 2, 128
+    q = dev(cases.normal((batch * T, Hq * D), 650, 0), torch.bfloat16)
+    k = dev(cases.normal((batch * T, Hkv * D), 650, 1), torch.bfloat16)
+    v = dev(cases.normal((batch * T, Hkv * D), 650, 2), torch.bfloat16)
+    got = jb.attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=True, impl=1)
+    want = ol.attention(host(q), host(k), host(v), batch, Hq, Hkv, D, True)
+    assert_close(host(got), want, BF16_RTOL / 2, "bf16 attention")
+
+
+def test_attention_argument_errors():
+    z = torch.zeros(4, 6, device="cuda")
+    with pytest.raises(jb.JsmError) as e:
+        jb.attn_prefill(z, z, z, 1, 3, 2, 2)  # 3 query heads over 2 kv heads
+    assert e.value.status == jb.SHAPE

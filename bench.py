@@ -181,6 +181,9 @@ def main():
     ap.add_argument("--impl", default="jasmine_b200")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="run this many eager decode steps between cudaProfilerStart/Stop and exit (for ncu "
+                         "--profile-from-start off); prints no bench line")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -235,6 +238,15 @@ def main():
         ids.copy_(nxt)
     torch.cuda.synchronize()
     launches_per_step = (jb.launch_count() - launches0) // W
+    if args.profile_steps > 0:
+        torch.cuda.profiler.start()
+        for _ in range(args.profile_steps):
+            model.decode_step(ids, nxt)
+            ids.copy_(nxt)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(f"# profiled {args.profile_steps} eager decode steps, {launches_per_step} launches per step", file=sys.stderr)
+        return
     graph = None
     try:
         side = torch.cuda.Stream()

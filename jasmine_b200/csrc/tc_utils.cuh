@@ -1,5 +1,5 @@
 // Blackwell (sm_100a) primitives used by the tensor-core kernels: mbarriers with
-// bounded waits, TMA tile loads (never multicast), tcgen05 MMA / TMEM access and
+// bounded waits, TMA tile loads (each CTA fetches its own tiles), tcgen05 MMA / TMEM access and
 // the shared-memory / instruction descriptors they take.
 #pragma once
 #include <cuda.h>

@@ -1,0 +1,246 @@
+// Attention of the jasmine API, forward halves (reference: mat_mha_t.hpp): mat_head_gen_t (one head),
+// vconcat / vsplit, mat_mha_t (multi-head self and cross attention) and mat_mhca_t.
+//
+// Inputs and outputs are [d_model, seq_len] like in the reference.  Internally q, k and v are produced
+// token-major ([seq_len, d_model], a head = a column slice) straight from the per-head projections, which are
+// d_head x d_head on the head's own row slice of the input (the reference's block-diagonal projections,
+// mat_mha_t.hpp:199-215, 278-282); one attention kernel then covers all heads and the output projection
+// reads the result through a transposed window.  No split / concat copies are made.
+#ifndef JASMINE_B200_MAT_MHA_T_HPP_
+#define JASMINE_B200_MAT_MHA_T_HPP_
+#include <cmath>
+#include <stdexcept>
+#include <vector>
+
+#include "mat_express_t.hpp"
+#include "mat_net_t.hpp"
+#include "mat_t.hpp"
+#include "mat_view_t.hpp"
+
+namespace jsm_attn {
+
+// rows [r0, r0+n) of a [features, tokens] window, seen token-major: [tokens, n]
+inline jsm_mat token_major_rows(const jsm_mat& x, int r0, int n) {
+    jsm_mat t = x;
+    t.data = static_cast<char*>(x.data) + (int64_t)r0 * x.row_stride * (int64_t)sizeof(float);
+    t.rows = x.cols; t.cols = n;
+    t.row_stride = x.col_stride; t.col_stride = x.row_stride;
+    return t;
+}
+inline jsm_mat columns(const jsm_mat& x, int c0, int n) {
+    jsm_mat t = x;
+    t.data = static_cast<char*>(x.data) + (int64_t)c0 * x.col_stride * (int64_t)sizeof(float);
+    t.cols = n;
+    return t;
+}
+inline jsm_mat transposed(const jsm_mat& x) {
+    jsm_mat t = x;
+    t.rows = x.cols; t.cols = x.rows; t.row_stride = x.col_stride; t.col_stride = x.row_stride;
+    return t;
+}
+// Y[tokens, out] = X_tm . W^T + b^T for a weight_net_t: the same k-ascending sums as W . X + b
+template <typename net>
+void project(const net& w, const jsm_mat& x_tm, const jsm_mat& out) {
+    jsm_mat W = transposed(w.jsm_weight().jsm_device());
+    jsm_mat B = transposed(w.jsm_bias().jsm_device());
+    jsm_rt::check(jsm_dot_f32(x_tm, W, &B, 0, nullptr, out, jsm_rt::stream()));
+}
+
+}  // namespace jsm_attn
+
+template <typename input_type, template <typename> class updator_type>
+class mat_head_gen_t {
+public:
+    using val_type = typename input_type::ele_type;
+    using ele_type = typename input_type::ele_type;
+
+private:
+    using ffn_type = weight_net_t<input_type, updator_type>;
+    ffn_type m_q_net, m_k_net, m_v_net;
+    bool m_mask;
+    int m_d;
+
+public:
+    mat_head_gen_t(int const& d_model = 1, bool const& mask = false, int const& = 1)
+        : m_q_net(d_model, d_model), m_k_net(d_model, d_model), m_v_net(d_model, d_model), m_mask(mask), m_d(d_model) {}
+
+    void set_param(int const& d_model, bool const& mask = false, int const& = 1) {
+        m_q_net.reinit(std::vector<int>{d_model, d_model});
+        m_k_net.reinit(std::vector<int>{d_model, d_model});
+        m_v_net.reinit(std::vector<int>{d_model, d_model});
+        m_mask = mask;
+        m_d = d_model;
+    }
+    bool mask() const { return m_mask; }
+    const ffn_type& q_net() const { return m_q_net; }
+    const ffn_type& k_net() const { return m_k_net; }
+    const ffn_type& v_net() const { return m_v_net; }
+
+    // softmax(mask(Q^T K / sqrt(d))) applied to V (reference: mat_mha_t.hpp:45-74); input: [d, S]
+    template <typename any_input>
+    mat_t<val_type> forward(const any_input& input) { return forward(input, input, m_mask); }
+    // cross attention: queries from the first argument, keys and values from the second (:76-90), no mask
+    template <typename any_q, typename any_kv>
+    mat_t<val_type> forward(const any_q& decoder_input, const any_kv& encoder_input) { return forward(decoder_input, encoder_input, false); }
+
+    template <typename... upr_arg_types>
+    void set_updator(upr_arg_types&&... args) {
+        m_q_net.set_updator(args...); m_k_net.set_updator(args...); m_v_net.set_updator(args...);
+    }
+    template <typename init_type>
+    void init_weight() {
+        m_q_net.template init_weight<init_type>();
+        m_k_net.template init_weight<init_type>();
+        m_v_net.template init_weight<init_type>();
+    }
+    std::string net_type(int const& indent = 0) const { return print_indent(indent) + "mat_head_gen_t"; }
+    void step() {}
+
+private:
+    template <typename any_q, typename any_kv>
+    mat_t<val_type> forward(const any_q& xq, const any_kv& xkv, bool mask) {
+        std::vector<std::shared_ptr<void>> keep;
+        const jsm_mat Xq = jsm_expr::operand(xq, keep), Xkv = jsm_expr::operand(xkv, keep);
+        const int Sq = Xq.cols, Sk = Xkv.cols, d = m_d;
+        if (Xq.rows != d || Xkv.rows != d) throw std::invalid_argument("mat_dot_t: inner dimensions do not match for dot product");
+        mat_t<val_type> q(Sq, d), k(Sk, d), v(Sk, d), o(Sq, d);
+        jsm_attn::project(m_q_net, jsm_attn::token_major_rows(Xq, 0, d), q.jsm_device_out());
+        jsm_attn::project(m_k_net, jsm_attn::token_major_rows(Xkv, 0, d), k.jsm_device_out());
+        jsm_attn::project(m_v_net, jsm_attn::token_major_rows(Xkv, 0, d), v.jsm_device_out());
+        jsm_rt::check(jsm_attn_prefill(q.jsm_device().data, k.jsm_device().data, v.jsm_device().data, o.jsm_device_out().data, JSM_F32,
+                                       1, Sq, Sk, 1, 1, d, mask ? 1 : 0, 1.0f / std::sqrt((float)d), nullptr, 1, jsm_rt::stream()));
+        return o.t().clone();  // back to [d, S]
+    }
+};
+
+// row-wise concatenation (reference: mat_mha_t.hpp:164-196)
+template <typename val_type>
+mat_t<val_type> vconcat(const std::vector<mat_t<val_type>>& mats) {
+    if (mats.empty()) throw std::runtime_error("Cannot concatenate empty vector");
+    const int cols = mats[0].col_num();
+    int total_rows = 0;
+    for (const auto& m : mats) {
+        if (m.col_num() != cols) throw std::runtime_error("All matrices must have the same number of columns");
+        total_rows += m.row_num();
+    }
+    mat_t<val_type> result(total_rows, cols);
+    int row_offset = 0;
+    for (const auto& m : mats) {
+        if (m.row_num() > 0) result.view(row_offset, 0, m.row_num(), cols).assign(m);
+        row_offset += m.row_num();
+    }
+    return result;
+}
+
+// equal row slices as views (reference: mat_mha_t.hpp:199-215)
+template <typename mat_type>
+std::vector<mat_view_t<mat_type>> vsplit(mat_type& mat, int num_splits) {
+    if (num_splits <= 0 || mat.row_num() % num_splits != 0) throw std::runtime_error("Invalid number of splits or row count mismatch");
+    const int rows = mat.row_num() / num_splits;
+    std::vector<mat_view_t<mat_type>> views;
+    for (int i = 0; i < num_splits; ++i) views.emplace_back(mat, i * rows, 0, rows, mat.col_num());
+    return views;
+}
+
+template <typename input_type, template <typename> class updator_type>
+class mat_mha_t {
+public:
+    using val_type = typename input_type::ele_type;
+
+private:
+    std::vector<mat_head_gen_t<input_type, updator_type>> m_heads;
+    weight_net_t<mat_t<val_type>, updator_type> m_output_proj;
+    int m_num_heads, m_d_model, m_d_head;
+    bool m_mask;
+
+public:
+    mat_mha_t(int num_heads = 1, int d_model = 1, bool mask = false, int seq_len = 1)
+        : m_output_proj(d_model, d_model), m_num_heads(num_heads), m_d_model(d_model), m_d_head(d_model / num_heads), m_mask(mask) {
+        if (d_model % num_heads != 0) throw std::runtime_error("d_model must be divisible by num_heads");
+        for (int i = 0; i < num_heads; ++i) m_heads.emplace_back(m_d_head, mask, seq_len);
+    }
+
+    void set_param(int num_heads, int d_model, bool mask = false, int seq_len = 1) {
+        if (d_model % num_heads != 0) throw std::runtime_error("d_model must be divisible by num_heads");
+        m_num_heads = num_heads; m_d_model = d_model; m_d_head = d_model / num_heads; m_mask = mask;
+        m_heads.resize(num_heads);
+        for (auto& h : m_heads) h.set_param(m_d_head, mask, seq_len);
+        m_output_proj.reinit(std::vector<int>{d_model, d_model});
+    }
+
+    // self attention (reference: mat_mha_t.hpp:265-291)
+    mat_t<val_type> forward(const input_type& input) {
+        if (input.row_num() != m_d_model) throw std::runtime_error("Input row dimension must match d_model");
+        return attend(input, input, m_mask);
+    }
+    // cross attention (reference: :293-322)
+    mat_t<val_type> forward(const input_type& input, const input_type& encoder_input) {
+        if (input.row_num() != m_d_model) throw std::runtime_error("Input row dimension must match d_model");
+        if (encoder_input.row_num() != m_d_model) throw std::runtime_error("Encoder input row dimension must match d_model");
+        return attend(input, encoder_input, false);
+    }
+
+    template <typename... upr_arg_types>
+    void set_updator(upr_arg_types&&... args) {
+        for (auto& h : m_heads) h.set_updator(args...);
+        m_output_proj.set_updator(args...);
+    }
+    // order: every head q(W,b) k(W,b) v(W,b), then the output projection (reference: :384-392)
+    template <typename init_type>
+    void init_weight() {
+        for (auto& h : m_heads) h.template init_weight<init_type>();
+        m_output_proj.template init_weight<init_type>();
+    }
+    std::string net_type(int const& indent = 0) const {
+        std::stringstream ss;
+        ss << print_indent(indent) << "mat_mha_t:(heads:" << m_num_heads << ", d_model:" << m_d_model << ")";
+        return ss.str();
+    }
+    void step() {}
+
+private:
+    mat_t<val_type> attend(const input_type& xq, const input_type& xkv, bool mask) {
+        const jsm_mat Xq = xq.jsm_device(), Xkv = xkv.jsm_device();
+        const int Sq = Xq.cols, Sk = Xkv.cols, d = m_d_model, dh = m_d_head;
+        mat_t<val_type> q(Sq, d), k(Sk, d), v(Sk, d), att(Sq, d);
+        const jsm_mat Q = q.jsm_device_out(), K = k.jsm_device_out(), V = v.jsm_device_out();
+        for (int h = 0; h < m_num_heads; ++h) {
+            jsm_attn::project(m_heads[h].q_net(), jsm_attn::token_major_rows(Xq, h * dh, dh), jsm_attn::columns(Q, h * dh, dh));
+            jsm_attn::project(m_heads[h].k_net(), jsm_attn::token_major_rows(Xkv, h * dh, dh), jsm_attn::columns(K, h * dh, dh));
+            jsm_attn::project(m_heads[h].v_net(), jsm_attn::token_major_rows(Xkv, h * dh, dh), jsm_attn::columns(V, h * dh, dh));
+        }
+        jsm_rt::check(jsm_attn_prefill(Q.data, K.data, V.data, att.jsm_device_out().data, JSM_F32, 1, Sq, Sk, m_num_heads, m_num_heads, dh,
+                                       mask ? 1 : 0, 1.0f / std::sqrt((float)dh), nullptr, 1, jsm_rt::stream()));
+        // out[d, S] = Wo . concat + bo, the concatenated heads being att^T
+        mat_t<val_type> out(d, Sq);
+        jsm_mat Wo = m_output_proj.jsm_weight().jsm_device(), Bo = m_output_proj.jsm_bias().jsm_device();
+        jsm_rt::check(jsm_dot_f32(Wo, jsm_attn::transposed(att.jsm_device()), &Bo, 0, nullptr, out.jsm_device_out(), jsm_rt::stream()));
+        return out;
+    }
+};
+
+// cross-attention holder: keys and values come from a stored encoder output (reference: mat_mha_t.hpp:410-453)
+template <typename input_type, template <typename> class updator_type>
+class mat_mhca_t : public mat_mha_t<input_type, updator_type> {
+public:
+    using base_type = mat_mha_t<input_type, updator_type>;
+    using val_type = typename input_type::ele_type;
+
+private:
+    mat_t<val_type>* m_encoder_output = nullptr;
+    mat_t<val_type>* m_encoder_delta = nullptr;
+
+public:
+    mat_mhca_t(int num_heads = 1, int d_model = 1, bool mask = false, int seq_len = 1) : base_type(num_heads, d_model, mask, seq_len) {}
+    void set_encoder_param(mat_t<val_type>& encoder_output, mat_t<val_type>& encoder_delta) {
+        m_encoder_output = &encoder_output;
+        m_encoder_delta = &encoder_delta;
+    }
+    mat_t<val_type> forward(const input_type& input) {
+        if (m_encoder_output == nullptr) throw std::runtime_error("Encoder output not set for cross attention");
+        return base_type::forward(input, *m_encoder_output);
+    }
+    void step() {}
+};
+
+#endif

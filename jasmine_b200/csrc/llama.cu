@@ -283,19 +283,24 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         if (s != JSM_OK) return s;
         const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
         const __nv_bfloat16* vv = kk + (long long)m->Hkv_l * D;
-        s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
-        if (s != JSM_OK) return s;
         if (decode) {
+            // the new token: K is rotated on its way into the cache, q inside the attention kernel
+            s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
+            if (s != JSM_OK) return s;
             s = jsm_attn_decode(m->qkv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch, m->Hq_l, m->Hkv_l, D, scale,
                                 m->rope, c.max_context, m->dec_scratch, m->attn, st);
         } else {
-            // prompt of one sequence starting at position 0: attention over the fresh q, k, v with RoPE applied on load
-            const bool flash = flash_available() && T >= 128;
-            if (flash)
-                s = flash_prefill_launch(m->qkv, kk, vv, m->attn, 1, T, T, m->Hq_l, m->Hkv_l, 1, scale, m->rope, st, m->qkv_dim,
+            // prompt of one sequence starting at position 0: rotate q and k in place (the first Hq + Hkv heads of every
+            // fused row), cache K and V, then causal attention over the fresh q, k, v
+            s = rope_apply_strided(m->qkv, m->qkv, JSM_BF16, m->rope, D, m->Hq_l + m->Hkv_l, m->pos, T, m->qkv_dim, st);
+            if (s != JSM_OK) return s;
+            s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, nullptr, st);
+            if (s != JSM_OK) return s;
+            if (flash_available() && T >= 128)
+                s = flash_prefill_launch(m->qkv, kk, vv, m->attn, 1, T, T, m->Hq_l, m->Hkv_l, 1, scale, nullptr, st, m->qkv_dim,
                                          m->qkv_dim, (long long)m->Hq_l * D);
             else
-                s = attn_simt_launch(m->qkv, kk, vv, m->attn, JSM_BF16, 1, T, T, m->Hq_l, m->Hkv_l, D, 1, scale, m->rope, st,
+                s = attn_simt_launch(m->qkv, kk, vv, m->attn, JSM_BF16, 1, T, T, m->Hq_l, m->Hkv_l, D, 1, scale, nullptr, st,
                                      m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
         }
         if (s != JSM_OK) return s;

@@ -8,6 +8,7 @@
 // The table is computed on the host with the reference's roundings (double pow,
 // double quotient narrowed to float, float cos/sin) and uploaded.
 #include "common.cuh"
+#include "attn.cuh"
 #include <cmath>
 #include <vector>
 
@@ -15,7 +16,7 @@ namespace jsm {
 
 template <typename T>
 __global__ void rope_apply_kernel(const T* __restrict__ x, T* __restrict__ out, const float4* __restrict__ table, int d,
-                                  int n_heads, const int32_t* __restrict__ positions, int T_tokens) {
+                                  int n_heads, const int32_t* __restrict__ positions, int T_tokens, long long row_stride) {
     const int half = d / 2;
     const long long total = (long long)T_tokens * n_heads * half;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -24,7 +25,7 @@ __global__ void rope_apply_kernel(const T* __restrict__ x, T* __restrict__ out, 
         const int t = (int)(th / n_heads);
         const int m = positions ? positions[t] : t;
         const float4 e = table[(long long)m * half + pair];
-        const long long base = th * d + 2 * pair;
+        const long long base = (long long)t * row_stride + (long long)(th % n_heads) * d + 2 * pair;
         float x0, x1;
         if constexpr (sizeof(T) == 4) {
             float2 v = *reinterpret_cast<const float2*>(x + base);
@@ -76,6 +77,12 @@ extern "C" jsm_status jsm_rope_table(float* d_table, int mode, int d, float thet
 
 extern "C" jsm_status jsm_rope_apply(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
                                      const int32_t* d_positions, int T, void* stream) {
+    return jsm::rope_apply_strided(d_x, d_out, dtype, d_table, d, n_heads, d_positions, T, (long long)n_heads * d, stream);
+}
+
+// rows of `row_stride` elements whose first n_heads * d entries are rotated (in place when d_out == d_x)
+jsm_status jsm::rope_apply_strided(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
+                                   const int32_t* d_positions, int T, long long row_stride, void* stream) {
     if (T == 0) return JSM_OK;
     if (!d_x || !d_out || !d_table) JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_apply: null pointer");
     if (d <= 0 || d % 2 || n_heads <= 0 || T < 0) JSM_FAIL(JSM_SHAPE, "Input dimension does not match RoPE dimension (d %d)", d);
@@ -86,11 +93,11 @@ extern "C" jsm_status jsm_rope_apply(const void* d_x, void* d_out, jsm_dtype dty
     if (dtype == JSM_F32)
         rope_apply_kernel<float><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(
             reinterpret_cast<const float*>(d_x), reinterpret_cast<float*>(d_out), reinterpret_cast<const float4*>(d_table), d,
-            n_heads, d_positions, T);
+            n_heads, d_positions, T, row_stride);
     else
         rope_apply_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(
             reinterpret_cast<const __nv_bfloat16*>(d_x), reinterpret_cast<__nv_bfloat16*>(d_out),
-            reinterpret_cast<const float4*>(d_table), d, n_heads, d_positions, T);
+            reinterpret_cast<const float4*>(d_table), d, n_heads, d_positions, T, row_stride);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }

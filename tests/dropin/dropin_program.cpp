@@ -1,0 +1,167 @@
+// A program written against the jasmine API only (inference side).  The SAME source is compiled twice:
+//   g++ -std=c++20 -I<jasmine reference>               -> CPU, the reference's own headers (expected output)
+//   g++ -std=c++20 -Iinclude/jasmine -Iinclude -ljasmine_b200   -> this library, every operation on the GPU
+// and the two outputs are compared value by value (tests/test_gpu_dropin.py).
+#include <cstdio>
+#include <stdexcept>
+#include <vector>
+
+#include "mat_t.hpp"
+#include "mat_express_t.hpp"
+#include "mat_view_t.hpp"
+#include "mat_net_t.hpp"
+#include "mat_init_t.hpp"
+#include "mat_mha_t.hpp"
+#include "mat_transformer_kernel_t.hpp"
+#include "mat_RoPE_t.hpp"
+#include "mat_transformer_t.hpp"
+
+using F = float;
+using M = mat_t<F>;
+
+// deterministic values in [-1, 1)
+static unsigned g_state = 12345u;
+static F next_value() {
+    g_state = g_state * 1664525u + 1013904223u;
+    return (F)((g_state >> 8) & 0xFFFF) / 32768.0f - 1.0f;
+}
+// every weight of a net, in the API's fixed order, through the init_t customisation point
+struct seeded_t;
+template <>
+struct init_t<seeded_t> {
+    template <typename mat_type>
+    requires is_matrix<mat_type>
+    static void cal(mat_type& m) {
+        for (int i = 0; i < m.row_num(); ++i)
+            for (int j = 0; j < m.col_num(); ++j) m(i, j) = 0.4f * next_value();
+    }
+};
+static M make(int r, int c, F scale = 1.0f, F shift = 0.0f) {
+    M m(r, c);
+    for (int i = 0; i < r; ++i)
+        for (int j = 0; j < c; ++j) m(i, j) = scale * next_value() + shift;
+    return m;
+}
+template <typename T>
+static void dump(const char* name, const T& m) {
+    std::printf("%s %d %d", name, (int)m.row_num(), (int)m.col_num());
+    for (int i = 0; i < m.row_num(); ++i)
+        for (int j = 0; j < m.col_num(); ++j) std::printf(" %.9g", (double)m(i, j));
+    std::printf("\n");
+}
+static void dump_scalar(const char* name, double v) { std::printf("%s 1 1 %.9g\n", name, v); }
+
+int main() {
+    // ---- expression operators, broadcast, materialisation ----
+    M a = make(4, 6), b = make(4, 6), colv = make(4, 1), rowv = make(1, 6), pos = make(4, 6, 0.5f, 1.0f);
+    dump("add", (a + b).clone());
+    dump("chain", ((a + b - a) * b / pos).clone());
+    dump("axpb", (a * 0.125f + b).clone());
+    dump("bcast_col", (a - colv).clone());
+    dump("bcast_row", (a * rowv).clone());
+    dump("scalar_left", (2.0f - a).clone());
+    dump("greater", (a > b).clone());
+    dump("less", (a < 0.25f).clone());
+    dump("relu_expr", ((a > 0) * a).clone());
+    dump("exp", exp(a).clone());
+    dump("sigmoid", sigmoid(a).clone());
+    M acc = a;
+    acc += b;
+    acc += 1.5f;
+    dump("plus_assign", acc);
+    M conv = a + b;  // conversion operator
+    dump("convert", conv);
+    dump_scalar("elem_of_expr", (a + b)(2, 3));
+    // ---- reductions ----
+    dump("hsum", hsum(a)); dump("vsum", vsum(a)); dump("hmean", hmean(a)); dump("vmean", vmean(a)); dump("hmax", hmax(a));
+    dump_scalar("sum", sum(a)); dump_scalar("mean", mean(a)); dump_scalar("max", max(a));
+    dump("pow2", pow(a, 2.0)); dump("sqrt", sqrt(pos));
+    dump("hsoftmax", hsoftmax(a * 0.125f + b));
+    dump("softmax", softmax(a).clone());
+    dump("hsum_of_expr", hsum(a * b));
+    // ---- views ----
+    dump("view", a.view(1, 2, 2, 3).clone());
+    dump("transpose", a.t().clone());
+    dump("back_col", a.back_col().clone());
+    dump("row", a.row(2).clone());
+    dump("view_expr", (a.view(0, 0, 2, 2) + b.view(2, 4, 2, 2)).clone());
+    M target(4, 6);
+    target.view(1, 1, 2, 3).assign(a.view(0, 0, 2, 3));
+    dump("assign", target);
+    // ---- dot ----
+    M c = make(6, 3);
+    dump("dot", a.dot(c).clone());
+    dump("dot_t", a.t().dot(b).clone());
+    dump("dot_chain", a.dot(c).dot(c.t()).clone());
+    dump("dot_plus", (a.dot(c) + colv).clone());
+    try {
+        auto bad = a.dot(b).clone();
+        std::printf("dot_error 1 1 0\n");
+    } catch (const std::invalid_argument&) {
+        std::printf("dot_error 1 1 1\n");
+    }
+    // ---- nets ----
+    weight_net_t<M, sgd_t> lin(6, 5);
+    lin.init_weight<seeded_t>();
+    M x = make(6, 7);
+    dump("weight_net", lin.forward(x));
+    relu_net_t<M> relu;
+    dump("relu_net", relu.forward(x));
+    sigmoid_net_t<M> sig;
+    dump("sigmoid_net", sig.forward(x));
+    layer_norm_net_t<M, sgd_t> ln;
+    dump("layer_norm", ln.forward(x));
+    hsoftmax_net_t<M> hs;
+    dump("hsoftmax_net", hs.forward(x));
+    using mlp_t = complex_net_builder_t<F>::push_back_updatable<weight_net_t, sgd_t>::push_back_staticnet<relu_net_t>::
+        push_back_updatable<weight_net_t, sgd_t>::type;
+    mlp_t mlp;
+    mlp.reinit(std::vector<int>{6, 9, 4});
+    mlp.init_weight<seeded_t>();
+    dump("mlp", mlp.forward(x));
+    dump("mlp_fold", x >> mlp);
+    residual_net_t<complex_net_t<weight_net_t<M, sgd_t>, relu_net_t<M>>> res;
+    res.base_net().reinit(std::vector<int>{6, 6});
+    res.init_weight<seeded_t>();
+    dump("residual", res.forward(x));
+    // ---- attention ----
+    mat_mha_t<M, sgd_t> mha(4, 16, true, 9);
+    mha.init_weight<seeded_t>();
+    M seq = make(16, 9);
+    M att = mha.forward(seq);
+    dump("mha_causal", att);
+    M prefix(16, 4);
+    for (int i = 0; i < 16; ++i)
+        for (int j = 0; j < 4; ++j) prefix(i, j) = seq(i, j);
+    dump("mha_prefix", mha.forward(prefix));  // equals the first 4 columns of mha_causal
+    mat_mha_t<M, sgd_t> mha_full(2, 16, false, 9);
+    mha_full.init_weight<seeded_t>();
+    dump("mha_full", mha_full.forward(seq));
+    M enc_in = make(16, 5);
+    dump("mha_cross", mha_full.forward(seq, enc_in));
+    try {
+        mha.forward(make(8, 3));
+        std::printf("mha_error 1 1 0\n");
+    } catch (const std::runtime_error&) {
+        std::printf("mha_error 1 1 1\n");
+    }
+    mat_head_gen_t<M, sgd_t> head(8, true, 6);
+    head.init_weight<seeded_t>();
+    M hx = make(8, 6);
+    dump("head", head.forward(hx.view(0, 0, 8, 6)));
+    // ---- RoPE ----
+    RoPE_net_t<M> rope(16);
+    dump("rope", rope.forward(seq));
+    // ---- stacks ----
+    encoder_t<F, sgd_t> enc(2, 2, 8, 5);
+    for (int i = 0; i < 2; ++i) enc.get_mha(i).set_param(2, 8, true, 5);  // decoder-only causal stack
+    enc.init_weight<seeded_t>();
+    M ex = make(8, 5);
+    dump("encoder_causal", enc.forward(ex));
+    transformer_base_t<M, sgd_t> tf(1, 1, 2, 8);
+    tf.init_weight<seeded_t>();
+    tf.encoder_forward(ex);
+    M dx = make(8, 3);
+    dump("transformer", tf.forward(dx));
+    return 0;
+}

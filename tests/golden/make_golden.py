@@ -58,5 +58,22 @@ def main():
     print("wrote", HERE / "ops.npz", HERE / "gpt_tiny.npz")
 
 
+
+
+def make_dropin_expected(reference_root="/root/reference"):
+    """Expected output of tests/dropin/dropin_program.cpp: the program compiled against the reference's headers."""
+    import subprocess
+    import tempfile
+    src = HERE.parent / "dropin" / "dropin_program.cpp"
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = Path(tmp) / "dropin_ref"
+        subprocess.run(["g++", "-std=c++20", "-O2", "-w", "-ffp-contract=off", f"-I{reference_root}", str(src), "-o", str(exe)],
+                       check=True)
+        out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    (HERE / "dropin_expected.txt").write_text(out)
+    print("wrote", HERE / "dropin_expected.txt")
+
+
 if __name__ == "__main__":
     main()
+    make_dropin_expected()

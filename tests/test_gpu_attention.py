@@ -119,3 +119,52 @@ def test_attention_argument_errors():
     with pytest.raises(jb.JsmError) as e:
         jb.attn_prefill(z, z, z, 1, 3, 2, 2)  # 3 query heads over 2 kv heads
     assert e.value.status == jb.SHAPE
+
+
+# ---- tcgen05 flash-attention prefill (bf16, head_dim 128) ------------------------------------------
+@pytest.mark.parametrize("batch,Tq,Tk,Hq,Hkv,causal", [(1, 128, 128, 1, 1, True), (1, 256, 256, 2, 2, True), (2, 300, 300, 4, 2, True),
+                                                      (1, 1000, 1000, 2, 1, True), (1, 384, 384, 2, 2, False), (2, 200, 456, 2, 2, True),
+                                                      (1, 130, 515, 4, 4, False)])
+def test_flash_prefill_matches_oracle(batch, Tq, Tk, Hq, Hkv, causal):
+    D = 128
+    q = dev(cases.normal((batch * Tq, Hq * D), 660, 0), torch.bfloat16)
+    k = dev(cases.normal((batch * Tk, Hkv * D), 660, 1), torch.bfloat16)
+    v = dev(cases.normal((batch * Tk, Hkv * D), 660, 2), torch.bfloat16)
+    got = jb.attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=causal, impl=2)
+    torch.cuda.synchronize()
+    want = ol.attention(host(q), host(k), host(v), batch, Hq, Hkv, D, causal, exact_div=False)
+    assert_close(host(got), want, 1e-2, f"flash B{batch} Tq{Tq} Tk{Tk} Hq{Hq} Hkv{Hkv} causal={causal}")
+
+
+def test_flash_prefill_with_rope_matches_cuda_core_kernel():
+    batch, T, Hq, Hkv, D = 2, 640, 4, 2, 128
+    q = dev(cases.normal((batch * T, Hq * D), 670, 0), torch.bfloat16)
+    k = dev(cases.normal((batch * T, Hkv * D), 670, 1), torch.bfloat16)
+    v = dev(cases.normal((batch * T, Hkv * D), 670, 2), torch.bfloat16)
+    table = jb.rope_table(1, D, 10000.0, T)
+    a = jb.attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=True, rope=table, impl=2)
+    b = jb.attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=True, rope=table, impl=1)
+    assert_close(host(a), host(b), 1e-2, "flash vs CUDA-core kernel with RoPE")
+
+
+def test_config3_full_size():
+    """Configuration 3: batch 4, 32 heads, head_dim 128, seq 4096, causal, RoPE theta 10000, bf16 ~N(0,1) (seed 2):
+    the tcgen05 kernel against the fp32 CUDA-core kernel on every row, and against the CPU oracle on two heads."""
+    batch, T, H, D = 4, 4096, 32, 128
+    q = torch.empty(batch * T, H * D, device="cuda", dtype=torch.bfloat16)
+    k = torch.empty_like(q); v = torch.empty_like(q)
+    jb.fill(q, 2, 0, 0, 0.0, 1.0); jb.fill(k, 2, 1, 0, 0.0, 1.0); jb.fill(v, 2, 2, 0, 0.0, 1.0)
+    table = jb.rope_table(1, D, 10000.0, T)
+    pos = torch.arange(T, dtype=torch.int32, device="cuda").repeat(batch)
+    qr, kr = jb.rope_apply(q, table, D, H, positions=pos), jb.rope_apply(k, table, D, H, positions=pos)
+    a = jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2)
+    b = jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=1)
+    torch.cuda.synchronize()
+    assert float((a.float() - b.float()).abs().max()) <= 1e-2 * float(b.float().abs().max())
+    # causal row 0 attends only to key 0: the output is v[0]
+    assert torch.equal(a[0], v[0])
+    for (bb, hh) in ((0, 0), (3, 31)):
+        rows = slice(bb * T, bb * T + 512)  # the first 512 queries only need the first 512 keys
+        cols = slice(hh * D, (hh + 1) * D)
+        want = ol.attention(host(qr[rows, cols]), host(kr[rows, cols]), host(v[rows, cols]), 1, 1, 1, D, True, exact_div=False)
+        assert_close(host(a[rows, cols]), want, 1e-2, f"cfg3 oracle (batch {bb}, head {hh})")

@@ -213,6 +213,29 @@ jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_
                            int n_seqs, int Hq, int Hkv, int D, float scale, const float* d_rope_table,
                            int max_context, void* d_scratch, void* d_out, void* stream);
 
+/* Decode attention for hosts that must not allocate.
+ * No counterpart in the reference (it has neither a KV cache nor device memory).
+ * Same arithmetic and arguments as jsm_attn_decode, but the per-chunk partial results live in a
+ * fixed array that is part of the library image instead of a caller-supplied buffer, and the call
+ * performs no cudaMalloc / cudaFree or any other allocating routine.  Meant for embedders whose
+ * device-memory budget is fixed before the first request - a serving process that has handed all
+ * remaining HBM to its KV page pool, or a plugin that is only given input and output buffers by
+ * its host - where an allocation would fail, fragment the pool or stall the device.
+ *  - Limit: jsm_attn_decode_scratch_bytes(n_seqs, Hq, D, max_context) must not exceed
+ *    JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES (8 MiB, held by every GPU that loads the library until
+ *    the process exits); larger problems are rejected with JSM_UNSUPPORTED.
+ *  - The first call on each device looks up the device address of the array; make that first call
+ *    outside any stream capture.
+ *  - All calls on a device share the array and it keeps the contents of the last call.  Nothing in
+ *    it has to start at zero (every slot that is read is written first by the same call), but two
+ *    calls that overlap on the GPU (different streams) race on it: serialise them. */
+#define JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+jsm_status jsm_attn_decode_static_scratch(const void* d_q, int64_t q_row_stride, const void* d_pool,
+                                          const int32_t* d_block_table, int max_pages,
+                                          const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D,
+                                          float scale, const float* d_rope_table, int max_context, void* d_out,
+                                          void* stream);
+
 /* ---- token-level helpers (not in the reference) ------------------------- */
 /* out[t, :] = table[ids[t], :] (+ pos_table[positions[t], :]) */
 jsm_status jsm_embedding(const void* d_table, const void* d_pos_table, const int32_t* d_ids,

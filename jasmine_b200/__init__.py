@@ -79,6 +79,7 @@ SYMBOLS = {
     "jsm_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "jsm_attn_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "jsm_attn_decode": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp]),
+    "jsm_attn_decode_static_scratch": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp]),
     "jsm_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "jsm_add_norm": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _f, _i, _i, _vp]),
     "jsm_llama_create": (_i, [C.POINTER(ModelConfig), _u64, C.POINTER(_vp)]),
@@ -243,6 +244,24 @@ def attn_decode(q, pool, block_table, context_lens, Hq, Hkv, D, max_context, sca
                                 block_table.shape[1], context_lens.data_ptr(), n, Hq, Hkv, D, scale,
                                 rope.data_ptr() if rope is not None else None, max_context, scratch.data_ptr(),
                                 out.data_ptr(), stream_ptr()))
+    return out
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def attn_decode_static_scratch(q, pool, block_table, context_lens, Hq, Hkv, D, max_context, scale=None, rope=None,
+                               out=None):
+    """jsm_attn_decode_static_scratch: decode attention whose partials live in the library's built-in array
+    (no allocation inside the call; `out` must be supplied by callers that may not allocate either)."""
+    torch = _torch()
+    n = q.shape[0]
+    out = torch.empty(n, Hq * D, dtype=q.dtype, device=q.device) if out is None else out
+    scale = float(D) ** -0.5 if scale is None else scale
+    check(lib().jsm_attn_decode_static_scratch(q.data_ptr(), q.stride(0), pool.data_ptr(), block_table.data_ptr(),
+                                               block_table.shape[1], context_lens.data_ptr(), n, Hq, Hkv, D, scale,
+                                               rope.data_ptr() if rope is not None else None, max_context,
+                                               out.data_ptr(), stream_ptr()))
     return out
 
 

@@ -16,6 +16,7 @@
 // partials of a sequence.
 #include "common.cuh"
 #include <math.h>
+#include <mutex>
 
 namespace jsm {
 
@@ -287,4 +288,41 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
                                                                (__nv_bfloat16*)d_out);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
+}
+
+// ---- decode attention that allocates nothing ---------------------------------------------------------
+// The chunk partials go to a fixed array in the library image.  In host code the array's name is only a
+// stand-in for the symbol: the address a kernel can use is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached.
+static __device__ __align__(256) float g_decode_static_scratch[JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+extern "C" jsm_status jsm_attn_decode_static_scratch(const void* d_q, int64_t q_row_stride, const void* d_pool,
+                                                     const int32_t* d_block_table, int max_pages, const int32_t* d_context_lens,
+                                                     int n_seqs, int Hq, int Hkv, int D, float scale, const float* d_rope_table,
+                                                     int max_context, void* d_out, void* stream) {
+    if (n_seqs == 0) return JSM_OK;
+    const size_t need = jsm_attn_decode_scratch_bytes(n_seqs, Hq, D, max_context);
+    if (need == 0) JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode_static_scratch: n_seqs %d, Hq %d, D %d, max_context %d", n_seqs, Hq, D, max_context);
+    if (need > (size_t)JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES)
+        JSM_FAIL(JSM_UNSUPPORTED,
+                 "jsm_attn_decode_static_scratch: %d sequences x %d heads x context %d need %zu bytes of partials, the built-in array "
+                 "holds %u; use jsm_attn_decode with a caller-supplied buffer",
+                 n_seqs, Hq, max_context, need, (unsigned)JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES);
+    static std::mutex mu;
+    static float* addr[64] = {nullptr};
+    int dev = -1;
+    JSM_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_decode_static_scratch: device index %d", dev);
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!addr[dev]) {
+            void* p = nullptr;
+            JSM_CUDA_CHECK(cudaGetSymbolAddress(&p, g_decode_static_scratch));
+            addr[dev] = reinterpret_cast<float*>(p);
+        }
+        scratch = addr[dev];
+    }
+    return jsm_attn_decode(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D, scale,
+                           d_rope_table, max_context, scratch, d_out, stream);
 }

@@ -171,6 +171,97 @@ def workload_config(args, n):
             "parallelism": f"tp{n}", "l2": "inputs larger than L2 (13.2 GB of weights per step)"}
 
 
+# ---- kernel-level workloads: configurations 2, 3 and 4 of the baseline ------------------------------------
+def run_kernel_workload(args):
+    import torch
+    import jasmine_b200 as jb
+    torch.cuda.set_device(0)
+    hbm, peak_kind = measured_peaks()
+    p = ROOT / "MEASURED_PEAKS.json"
+    tf_peak = float(json.loads(p.read_text())["bf16_tflops"]) if p.exists() else 1590.0
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+
+    def timed(fn, sets=1):
+        """Mean milliseconds per call over K calls; `sets` rotating input sets keep the operands out of L2."""
+        for i in range(W):
+            fn(i % sets)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            fn(i % sets)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / K
+
+    def emit(name, ms, bound, work, peak, unit, config):
+        ach = work / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+        print(json.dumps({"metric": name, "value": ach, "unit": unit, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic", "config": config,
+                          "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                                       "traffic": None, "peak_source": f"{peak_kind}"}}), flush=True)
+
+    L0, L1 = (jb.OP_LEAF, 0), (jb.OP_LEAF, 1)
+    if args.workload == "expr":
+        n, sets = 4096, 4  # 4 sets x 192 MiB of operands: every launch reads from HBM, not from the 126 MB L2
+        A = [torch.empty(n, n, device="cuda") for _ in range(sets)]
+        B = [torch.empty(n, n, device="cuda") for _ in range(sets)]
+        Y = [torch.empty(n, n, device="cuda") for _ in range(sets)]
+        for i in range(sets):
+            jb.fill(A[i], 1, 2 * i, 0, 0.0, 1.0); jb.fill(B[i], 1, 2 * i + 1, 0, 0.0, 1.0)
+        g = torch.empty(n, device="cuda"); b = torch.empty(n, device="cuda"); r = torch.empty(n, 1, device="cuda")
+        jb.fill(g, 1, 100, 1, 0.5, 1.5); jb.fill(b, 1, 101, 0, 0.0, 0.1)
+        axpb = [L0, (jb.OP_IMM, 0.125), (jb.OP_MUL,), L1, (jb.OP_ADD,)]
+        cfg = {"workload": "expr_4096x4096_f32", "l2": f"{sets} rotating operand sets (768 MiB) > L2"}
+        full = n * n * 4
+        emit("hsoftmax(A*0.125+B)_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_SOFTMAX, 1, axpb, [A[i], B[i]], Y[i]), sets), "hbm", 3 * full, hbm, "GB/s", cfg)
+        emit("LayerNorm_rows(A+B)*g+b_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_LAYERNORM, 1, [L0, L1, (jb.OP_ADD,)], [A[i], B[i]], Y[i], gain=g, bias=b, eps=1e-5), sets),
+             "hbm", 3 * full + 2 * n * 4, hbm, "GB/s", cfg)
+        emit("RMSNorm_rows(A)*g_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_RMSNORM, 1, [L0], [A[i]], Y[i], gain=g, eps=1e-5), sets), "hbm", 2 * full + n * 4, hbm, "GB/s", cfg)
+        emit("row_sum_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_SUM, 1, [L0], [A[i]], r), sets), "hbm", full + n * 4, hbm, "GB/s", cfg)
+        emit("row_max_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_MAX, 1, [L0], [B[i]], r), sets), "hbm", full + n * 4, hbm, "GB/s", cfg)
+        emit("elementwise_A*0.125+B_GBps", timed(lambda i: jb.eval_elementwise(axpb, [A[i], B[i]], Y[i]), sets), "hbm", 3 * full, hbm, "GB/s", cfg)
+    elif args.workload == "flash":
+        batch, T, H, D = 4, 4096, 32, 128
+        q = torch.empty(batch * T, H * D, device="cuda", dtype=torch.bfloat16)
+        k = torch.empty_like(q); v = torch.empty_like(q); o = torch.empty_like(q)
+        jb.fill(q, 2, 0, 0, 0.0, 1.0); jb.fill(k, 2, 1, 0, 0.0, 1.0); jb.fill(v, 2, 2, 0, 0.0, 1.0)
+        table = jb.rope_table(1, D, 10000.0, T)
+        pos = torch.arange(T, dtype=torch.int32, device="cuda").repeat(batch)
+        qr, kr = torch.empty_like(q), torch.empty_like(k)
+        flops = 4.0 * batch * H * T * T * D / 2  # causal convention: half of the S x S scores
+        cfg = {"workload": "flash_prefill_b4_h32_s4096_d128_causal_bf16", "l2": "512 MiB of q, k, v, out > L2"}
+
+        def attn_only(_):
+            jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2, out=o)
+
+        def with_rope(_):
+            jb.rope_apply(q, table, D, H, positions=pos, out=qr)
+            jb.rope_apply(k, table, D, H, positions=pos, out=kr)
+            jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2, out=o)
+        with_rope(0)
+        jb.check_device_errors()  # a kernel that gave up on a wait must not be timed
+        emit("flash_prefill_TFLOPs", timed(attn_only), "tensor", flops, tf_peak, "TFLOP/s", cfg)
+        emit("flash_prefill_with_rope_TFLOPs", timed(with_rope), "tensor", flops, tf_peak, "TFLOP/s", cfg)
+    else:
+        sys.path.insert(0, str(ROOT))
+        Hq, Hkv, D, n = 32, 8, 128, 64
+        lens_t = torch.empty(n, dtype=torch.int32)
+        jb.fill(lens_t, 3, 0, 2, 512, 8193)
+        lens = lens_t.tolist()
+        max_ctx, max_pages = 8192, 8192 // jb.PAGE_SIZE
+        pool = torch.empty(n * max_pages, 2, Hkv, jb.PAGE_SIZE, D, device="cuda", dtype=torch.bfloat16)
+        jb.fill(pool, 3, 1, 0, 0.0, 1.0)
+        bt = torch.arange(n * max_pages, dtype=torch.int32, device="cuda").reshape(n, max_pages)
+        q = torch.empty(n, Hq * D, device="cuda", dtype=torch.bfloat16); jb.fill(q, 3, 2, 0, 0.0, 1.0)
+        ctx = lens_t.cuda()
+        out = torch.empty(n, Hq * D, device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(jb.lib().jsm_attn_decode_scratch_bytes(n, Hq, D, max_ctx) // 4, device="cuda")
+        kv_bytes = sum(lens) * Hkv * D * 2 * 2
+        cfg = {"workload": "kv_decode_b64_q32_kv8_d128_ctx512-8192", "sum_context": sum(lens), "l2": f"{kv_bytes / 2**20:.0f} MiB of K/V > L2"}
+        emit("kv_decode_attention_GBps", timed(lambda _: jb.attn_decode(q, pool, bt, ctx, Hq, Hkv, D, max_ctx, scratch=scratch, out=out)), "hbm", kv_bytes, hbm, "GB/s", cfg)
+
+
 # ---- the GPU arm --------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -181,6 +272,9 @@ def main():
     ap.add_argument("--impl", default="jasmine_b200")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode"],
+                    help="decode = the headline; expr / flash / kvdecode = configurations 2 / 3 / 4 of the baseline "
+                         "(kernel-level lines, one JSON line per kernel)")
     ap.add_argument("--profile-steps", type=int, default=0,
                     help="run this many eager decode steps between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no bench line")
@@ -188,6 +282,8 @@ def main():
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.workload != "decode":
+        return run_kernel_workload(args)
 
     import torch
     import torch.distributed as dist

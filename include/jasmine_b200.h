@@ -52,6 +52,10 @@ jsm_status jsm_device_count(int* count);
 /* Count of kernels launched by this library in this process (all threads). */
 uint64_t jsm_launch_count(void);
 
+/* Synchronises `stream` and reports (then clears) the error word of the tensor-core kernels: JSM_TIMEOUT when a
+ * bounded device-side wait ran out since the last check (the kernel unwound and its result is invalid). */
+jsm_status jsm_check_device_errors(void* stream);
+
 /* ---- device memory (mat_t storage: mat_t.hpp:30-69 new[]/memset/delete[]) */
 jsm_status jsm_malloc(void** d_ptr, size_t bytes); /* zero-filled like init_matrix */
 jsm_status jsm_free(void* d_ptr);

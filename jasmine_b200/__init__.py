@@ -59,6 +59,7 @@ SYMBOLS = {
     "jsm_version": (_i, []),
     "jsm_device_count": (_i, [C.POINTER(_i)]),
     "jsm_launch_count": (_u64, []),
+    "jsm_check_device_errors": (_i, [_vp]),
     "jsm_malloc": (_i, [C.POINTER(_vp), _sz]),
     "jsm_free": (_i, [_vp]),
     "jsm_upload": (_i, [_vp, _vp, _sz, _vp]),
@@ -294,6 +295,11 @@ def fill(t, seed: int, tensor_id: int, dist: int, a: float, b: float):
     else:
         check(lib().jsm_fill_host(t.data_ptr(), dtype_of(t), t.numel(), seed, tensor_id, dist, a, b))
     return t
+
+
+def check_device_errors():
+    """Synchronise and raise JsmError(TIMEOUT) if a tensor-core kernel gave up on a wait since the last check."""
+    check(lib().jsm_check_device_errors(stream_ptr()))
 
 
 def launch_count() -> int:

@@ -200,9 +200,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             float mx = sv[0];
 #pragma unroll
             for (int i = 1; i < FA_BN; ++i) mx = fmaxf(mx, sv[i]);
-            if (mx > m_ref + FA_RESCALE_THRESHOLD) {
+            // tcgen05.ld / st are warp-collective: the decision to touch the accumulator is taken per warp,
+            // each lane then applies its own factor (1 for the rows whose maximum did not move)
+            const bool grow = mx > m_ref + FA_RESCALE_THRESHOLD;
+            if (__any_sync(0xffffffffu, grow)) {
                 // raise the reference maximum; the accumulated O and l shrink by 2^(old - new)
-                const float alpha = exp2f(m_ref - mx);
+                const float alpha = grow ? exp2f(m_ref - mx) : 1.0f;
                 if (j > 0) {
 #pragma unroll
                     for (int c = 0; c < FA_D; c += 32) {
@@ -218,8 +221,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                         }
                     }
                 }
-                l *= alpha;
-                m_ref = mx;
+                if (grow) {
+                    l *= alpha;
+                    m_ref = mx;
+                }
             }
             // p = 2^(s - m_ref), packed to bf16 pairs, written over the first 64 columns of S
             float lsum = 0.0f;
@@ -242,22 +247,25 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         // epilogue: O / l -> bf16 -> global
         if (ok && n_tiles[t] > 0) ok = mbar_wait(&o_done, 0, &abort_flag, P.err, TC_TIMEOUT_ACC);
         tc_fence_after();
-        if (ok && n_tiles[t] > 0 && qi < P.Tq) {
+        if (ok && n_tiles[t] > 0) {  // warp-uniform: the TMEM loads are collective, only the stores are per row
             const float inv = 1.0f / l;
-            __nv_bfloat16* dst = P.out + (long long)(b * P.Tq + qi) * P.out_rs + (long long)h * FA_D;
+            const bool store = qi < P.Tq;
+            __nv_bfloat16* dst = P.out + (long long)(b * P.Tq + (store ? qi : 0)) * P.out_rs + (long long)h * FA_D;
 #pragma unroll
             for (int c = 0; c < FA_D; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(o_addr + c, r);
                 tmem_ld_wait();
+                if (store) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 o;
-                    o.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                    o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                    o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                    o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c + i) = o;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + i) = o;
+                    }
                 }
             }
         }

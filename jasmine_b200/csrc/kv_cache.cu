@@ -20,10 +20,17 @@
 
 namespace jsm {
 
-constexpr int DEC_CHUNK = 512;   // context positions per CTA
+constexpr int DEC_CHUNK_MAX = 512;  // context positions per CTA at large batch
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_UNROLL = 4;    // warp loads of K (and V) in flight per step: 8 keys
 constexpr float LOG2E = 1.4426950408889634f;
+
+// Context positions per CTA: small batches get short chunks so that the grid still fills the GPU
+// (chunks x kv heads x sequences CTAs); always a multiple of the 32 positions a CTA covers per step.
+__host__ __device__ inline int decode_chunk(int n_seqs, int Hq) {
+    const int work = n_seqs * Hq;
+    return work >= 512 ? DEC_CHUNK_MAX : work >= 128 ? 256 : work >= 32 ? 128 : 64;
+}
 
 __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
     f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
@@ -64,13 +71,13 @@ template <int G>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ pool,
     const int32_t* __restrict__ block_table, int max_pages, const int32_t* __restrict__ context_lens, int Hq, int Hkv,
-    float scale_log2, const float4* __restrict__ rope, int n_chunks, float* __restrict__ scratch) {
+    float scale_log2, const float4* __restrict__ rope, int n_chunks, int chunk_len, float* __restrict__ scratch) {
     constexpr int D = 128;
     const int chunk = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int ctx = context_lens[seq];
-    const int c_begin = chunk * DEC_CHUNK;
+    const int c_begin = chunk * chunk_len;
     if (c_begin >= ctx) return;
-    const int c_end = min(ctx, c_begin + DEC_CHUNK);
+    const int c_end = min(ctx, c_begin + chunk_len);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ks = lane >> 4;          // which of the two keys of a warp load
     const int dsub = (lane & 15) * 8;  // this lane's 8 dims
@@ -217,10 +224,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
 // merge the chunk partials of one (sequence, query head): 128 threads, one per dim
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ scratch,
                                                                 const int32_t* __restrict__ context_lens, int Hq, int n_chunks,
-                                                                __nv_bfloat16* __restrict__ out) {
+                                                                int chunk_len, __nv_bfloat16* __restrict__ out) {
     constexpr int D = 128;
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
-    const int n = (context_lens[seq] + DEC_CHUNK - 1) / DEC_CHUNK;
+    const int n = (context_lens[seq] + chunk_len - 1) / chunk_len;
     const float* src = scratch + ((long long)seq * Hq + h) * n_chunks * (D + 2);
     float M = -INFINITY;
     for (int c = 0; c < n; ++c) M = fmaxf(M, src[c * (D + 2) + D]);
@@ -253,7 +260,8 @@ extern "C" jsm_status jsm_kv_append(void* d_pool, const int32_t* d_block_table, 
 
 extern "C" size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int max_context) {
     if (n_seqs <= 0 || Hq <= 0 || D <= 0 || max_context <= 0) return 0;
-    const size_t n_chunks = (size_t)(max_context + DEC_CHUNK - 1) / DEC_CHUNK;
+    const int chunk = decode_chunk(n_seqs, Hq);
+    const size_t n_chunks = (size_t)(max_context + chunk - 1) / chunk;
     return (size_t)n_seqs * Hq * n_chunks * (D + 2) * sizeof(float);
 }
 
@@ -267,14 +275,15 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) JSM_FAIL(JSM_SHAPE, "d_model must be divisible by num_heads (Hq %d, Hkv %d)", Hq, Hkv);
     if (max_context <= 0 || (q_row_stride % 8)) JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode: max_context %d, q stride %lld", max_context, (long long)q_row_stride);
     const int G = Hq / Hkv;
-    const int n_chunks = (max_context + DEC_CHUNK - 1) / DEC_CHUNK;
+    const int chunk = decode_chunk(n_seqs, Hq);
+    const int n_chunks = (max_context + chunk - 1) / chunk;
     dim3 grid(n_chunks, Hkv, n_seqs);
     cudaStream_t st = as_stream(stream);
     const float sl2 = scale * LOG2E;
 #define JSM_DEC(GG)                                                                                                            \
     attn_decode_kernel<GG><<<grid, DEC_WARPS * 32, 0, st>>>((const __nv_bfloat16*)d_q, q_row_stride, (const __nv_bfloat16*)d_pool, \
                                                             d_block_table, max_pages, d_context_lens, Hq, Hkv, sl2,               \
-                                                            (const float4*)d_rope_table, n_chunks, (float*)d_scratch)
+                                                            (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch)
     switch (G) {
         case 1: JSM_DEC(1); break;
         case 2: JSM_DEC(2); break;
@@ -284,7 +293,7 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
     }
 #undef JSM_DEC
     JSM_LAUNCH_CHECK();
-    attn_decode_merge_kernel<<<dim3(Hq, n_seqs), 128, 0, st>>>((const float*)d_scratch, d_context_lens, Hq, n_chunks,
+    attn_decode_merge_kernel<<<dim3(Hq, n_seqs), 128, 0, st>>>((const float*)d_scratch, d_context_lens, Hq, n_chunks, chunk,
                                                                (__nv_bfloat16*)d_out);
     JSM_LAUNCH_CHECK();
     return JSM_OK;

@@ -105,6 +105,8 @@ struct TcParams {
     const __nv_bfloat16* R;
     void* Y;
     int* err;
+    float* ws;            // split-K with in-kernel fix-up: partials [split][T][ldw]
+    int* counters;        // one arrival counter per output tile, zero between launches
 };
 
 template <int BN, bool GATEUP>
@@ -212,7 +214,60 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         bool ok = n_kb > 0;
         if (ok) ok = mbar_wait(&acc_bar, 0, &abort_flag, P.err, TC_TIMEOUT_ACC);
         tc_fence_after();
-        if (ok) {
+        if (ok && P.ws && gridDim.z > 1) {
+            // ---- split-K with in-kernel fix-up: every CTA of a tile stores its raw partial; the one that arrives last
+            // adds the partials in split order (so the result does not depend on who is last) and runs the epilogue
+            __shared__ int is_last;
+            const int ldw = GATEUP ? 2 * P.N : P.N;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= P.T) break;
+                uint32_t r[16], u[16];
+                tmem_ld16(lane_addr + c0, r);
+                if (GATEUP) tmem_ld16(lane_addr + BN + c0, u);
+                tmem_ld_wait();
+                if (feat < P.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < P.T) {
+                            float* w = P.ws + ((size_t)blockIdx.z * P.T + t) * ldw + feat;
+                            __stcg(w, __uint_as_float(r[j]));
+                            if (GATEUP) __stcg(w + P.N, __uint_as_float(u[j]));
+                        }
+                    }
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+            if (threadIdx.x == 64) {
+                const int old = atomicAdd(&P.counters[tile_id], 1);
+                is_last = (old == (int)gridDim.z - 1);
+                if (is_last) P.counters[tile_id] = 0;  // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (is_last && feat < P.N) {
+                __threadfence();
+                const float bias = P.bias ? P.bias[feat] : 0.0f;
+                for (int t = t0; t < min(P.T, t0 + BN); ++t) {
+                    float v = 0.0f, up = 0.0f;
+                    for (int z = 0; z < (int)gridDim.z; ++z) {
+                        const float* w = P.ws + ((size_t)z * P.T + t) * ldw + feat;
+                        v += __ldcg(w);
+                        if (GATEUP) up += __ldcg(w + P.N);
+                    }
+                    v += bias;
+                    if (GATEUP) v = silu_f(v) * up;
+                    else if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
+                    else if (P.epilogue == LIN_GELU) v = gelu_f(v);
+                    else if (P.epilogue == LIN_RESIDUAL) v += __bfloat162float(P.R[(size_t)t * P.N + feat]);
+                    if (P.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + feat] = __float2bfloat16_rn(v);
+                    else reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + feat] = v;
+                }
+            }
+        } else if (ok) {
             const float bias = (P.bias && feat < P.N && (P.out_mode != 2 || blockIdx.z == 0)) ? P.bias[feat] : 0.0f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -269,11 +324,10 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x) {
 }
 
 // Each warp owns ROWS output rows (GATEUP: ROWS/2 gate rows and the matching up rows).
-template <int TOK, bool GATEUP>
+template <int TOK, bool GATEUP, int ROWS>
 __global__ void __launch_bounds__(256) gemv_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                                                    const float* __restrict__ bias, int epilogue, const __nv_bfloat16* __restrict__ R,
                                                    void* __restrict__ Y, int out_f32, int N, int K) {
-    constexpr int ROWS = 4;
     constexpr int OUTS = GATEUP ? ROWS / 2 : ROWS;
     const int warp = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int o0 = warp * OUTS;  // first output of this warp
@@ -333,22 +387,31 @@ template <int TOK>
 static void launch_gemv(const void* X, const void* W, const float* bias, int epi, const void* R, void* Y, int out_f32, int N, int K,
                         cudaStream_t st) {
     const bool gu = epi == LIN_SILU_MUL;
-    const int outs_per_warp = gu ? 2 : 4;
+    // enough warps for two CTAs on every SM: narrow outputs use two rows per warp instead of four
+    const bool narrow = !gu && (N / 4 + 7) / 8 < 2 * sm_count();
+    const int outs_per_warp = gu ? 2 : (narrow ? 2 : 4);
     const int warps = (N + outs_per_warp - 1) / outs_per_warp;
     const int blocks = (warps + 7) / 8;
     if (gu)
-        gemv_kernel<TOK, true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
-                                                       (const __nv_bfloat16*)R, Y, out_f32, N, K);
+        gemv_kernel<TOK, true, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                                                          (const __nv_bfloat16*)R, Y, out_f32, N, K);
+    else if (narrow)
+        gemv_kernel<TOK, false, 2><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                                                           (const __nv_bfloat16*)R, Y, out_f32, N, K);
     else
-        gemv_kernel<TOK, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
-                                                        (const __nv_bfloat16*)R, Y, out_f32, N, K);
+        gemv_kernel<TOK, false, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                                                           (const __nv_bfloat16*)R, Y, out_f32, N, K);
 }
 
 template <int BN, bool GATEUP>
 static jsm_status launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& P, int splits, cudaStream_t st) {
     constexpr int A_BYTES = BM * BK * 2 * (GATEUP ? 2 : 1);
     constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
-    int stages = (200 * 1024) / STAGE_BYTES;
+    // a weight stream split along K runs two CTAs per SM (about 100 KB of stages each) so that a grid of about twice
+    // the SM count is resident at once; a single-wave grid takes the whole shared memory for one deep ring
+    const int n_ctas = ((P.N + BM - 1) / BM) * ((P.T + BN - 1) / BN) * splits;
+    const bool two_per_sm = n_ctas > sm_count() && 2 * (GATEUP ? 2 * BN : BN) <= 512;
+    int stages = ((two_per_sm ? 104 : 200) * 1024) / STAGE_BYTES;
     if (stages > 8) stages = 8;
     if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
@@ -369,9 +432,11 @@ jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st) {
     if (a.K <= 0 || a.K % 8) JSM_FAIL(JSM_UNSUPPORTED, "linear_bf16: K (%d) must be a positive multiple of 8", a.K);
     if (a.epilogue < LIN_NONE || a.epilogue > LIN_RESIDUAL) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: epilogue %d", a.epilogue);
     if (a.epilogue == LIN_RESIDUAL && !a.R) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: residual epilogue without R");
-    if (a.splits > 1 && (a.out_mode != 2 || a.epilogue != LIN_NONE))
-        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K writes raw f32 partials only");
-    const bool use_gemv = a.impl == 1 || (a.impl == 0 && a.T <= 4 && a.splits <= 1 && a.out_mode != 2);
+    if (a.splits > 1 && !a.ws && (a.out_mode != 2 || a.epilogue != LIN_NONE))
+        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K without a workspace writes raw f32 partials only");
+    if (a.splits > 1 && a.ws && (a.out_mode == 2 || !a.counters))
+        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K with in-kernel fix-up needs arrival counters and a final output");
+    const bool use_gemv = a.impl == 1 || (a.impl == 0 && a.T <= 4 && a.out_mode != 2);
     if (use_gemv) {
         if (a.T > 4) JSM_FAIL(JSM_UNSUPPORTED, "linear_bf16: the CUDA-core kernel takes at most 4 tokens");
         const int f32 = a.out_mode == 1;
@@ -394,11 +459,13 @@ jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st) {
     TcParams P;
     P.T = a.T; P.N = a.N; P.K = a.K;
     const int kb_total = (a.K + BK - 1) / BK;
-    const int splits = a.splits < 1 ? 1 : (a.splits > kb_total ? kb_total : a.splits);
+    int splits = a.splits < 1 ? 1 : (a.splits > kb_total ? kb_total : a.splits);
     P.kb_per_split = (kb_total + splits - 1) / splits;
+    splits = (kb_total + P.kb_per_split - 1) / P.kb_per_split;  // no empty slice: every CTA of a tile must arrive
     P.epilogue = a.epilogue; P.out_mode = a.out_mode; P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y;
     P.err = tc_error_word();
-    const int grid_z = a.out_mode == 2 ? (a.splits < 1 ? 1 : a.splits) : 1;
+    P.ws = a.ws; P.counters = a.counters;
+    const int grid_z = a.out_mode == 2 ? (a.splits < 1 ? 1 : a.splits) : (a.ws ? splits : 1);
     if (gu) {
         switch (bn) {
             case 16: return launch_tc<16, true>(mw, mx, P, grid_z, st);
@@ -432,12 +499,14 @@ jsm_status tc_check_error(cudaStream_t st, const char* who) {
 
 using namespace jsm;
 
+extern "C" jsm_status jsm_check_device_errors(void* stream) { return tc_check_error(as_stream(stream), "jsm_check_device_errors"); }
+
 extern "C" jsm_status jsm_linear_bf16(const void* d_X, const void* d_W, const float* d_bias, int epilogue, const void* d_R,
                                       void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
     if (out_dtype != JSM_BF16 && out_dtype != JSM_F32) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16: out dtype %d", out_dtype);
     LinearArgs a;
     a.X = d_X; a.W = d_W; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.Y = d_Y;
     a.out_mode = out_dtype == JSM_F32 ? 1 : 0;
-    a.T = T; a.N = N; a.K = K; a.splits = 1; a.impl = 0;
+    a.T = T; a.N = N; a.K = K; a.splits = 1; a.impl = 0; a.ws = nullptr; a.counters = nullptr;
     return linear_bf16_launch(a, as_stream(stream));
 }

@@ -15,8 +15,10 @@ struct LinearArgs {
     void* Y;            // out_mode 0: bf16 [T,N]; 1: f32 [T,N]; 2: f32 partials [splits][T][N]
     int out_mode;
     int T, N, K;
-    int splits;         // grid split along K (out_mode 2 only)
+    int splits;         // grid split along K: out_mode 2 writes the raw partials; with a workspace the kernel folds them itself
     int impl;           // 0 auto, 1 CUDA-core stream (T <= 4), 2 tcgen05
+    float* ws = nullptr;      // workspace of splits * T * (N or 2N) floats for the in-kernel fix-up
+    int* counters = nullptr;  // ceil(N/128) * ceil(T/BN) arrival counters, zero before the first launch
 };
 
 jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st);

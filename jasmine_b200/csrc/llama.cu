@@ -48,6 +48,7 @@ struct jsm_model {
     float* partial = nullptr;
     float* logits = nullptr;
     float* dec_scratch = nullptr;
+    int* counters = nullptr;     // arrival counters of the split-K projections (self-resetting)
     std::vector<void*> allocs;
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
@@ -109,9 +110,10 @@ __global__ void __launch_bounds__(256) fold_add_norm_kernel(__nv_bfloat16* __res
             const uint4 w = *reinterpret_cast<const uint4*>(h + base + c);
             v[i][0] = bf16lo(w.x); v[i][1] = bf16hi(w.x); v[i][2] = bf16lo(w.y); v[i][3] = bf16hi(w.y);
             v[i][4] = bf16lo(w.z); v[i][5] = bf16hi(w.z); v[i][6] = bf16lo(w.w); v[i][7] = bf16hi(w.w);
+#pragma unroll 4
             for (int s = 0; s < splits; ++s) {
-                const float4 a = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c);
-                const float4 b = *reinterpret_cast<const float4*>(partial + s * split_stride + base + c + 4);
+                const float4 a = __ldcs(reinterpret_cast<const float4*>(partial + s * split_stride + base + c));
+                const float4 b = __ldcs(reinterpret_cast<const float4*>(partial + s * split_stride + base + c + 4));
                 v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
                 v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
             }
@@ -211,12 +213,15 @@ static void fill_shard(__nv_bfloat16* dst, long long rows, long long cols, long 
 }
 
 static int pick_splits(int T, int N, int K) {
-    // enough CTAs to pull from every SM: tiles * splits >= ~SM count, each split at least 4 k-blocks
+    // a weight stream wants about two CTAs per SM in flight; the fp32 partials (written and read once per split)
+    // must stay small next to the weights: splits * T * N * 8 bytes <= a quarter of N * K * 2 bytes
     const int tiles = ((N + 127) / 128) * ((T + 127) / 128);
     const int kb = (K + 63) / 64;
-    int s = (sm_count() + tiles - 1) / tiles;
-    if (s > 8) s = 8;
-    while (s > 1 && kb / s < 4) --s;
+    int s = (2 * sm_count() + tiles / 2) / tiles;
+    const int cap = K / (16 * (T < 1 ? 1 : T));
+    if (s > cap) s = cap;
+    if (s > 16) s = 16;
+    while (s > 1 && kb / s < 2) --s;
     return s < 1 ? 1 : s;
 }
 
@@ -242,21 +247,25 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
         jsm_status s = linear_bf16_launch(a, st);
         if (s != JSM_OK) return s;
     } else {
-        const int splits = pick_splits(T, N, K);
-        a.epilogue = LIN_NONE; a.Y = m->partial; a.out_mode = 2; a.splits = splits;
-        jsm_status s = linear_bf16_launch(a, st);
-        if (s != JSM_OK) return s;
+        // weight stream split along K; the CTA that finishes a tile last folds the partials and writes the result:
+        // straight into the residual stream on one GPU, into the all-reduce buffer under tensor parallelism
+        a.splits = pick_splits(T, N, K);
+        a.ws = a.splits > 1 ? m->partial : nullptr;
+        a.counters = m->counters;
+        a.out_mode = 0;
         if (!tp) {
-            fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, m->partial, splits, (long long)T * N, nullptr, next_gain, m->c.norm_eps,
-                                                       next_gain ? m->xn : nullptr, d);
-            JSM_LAUNCH_CHECK();
+            a.epilogue = LIN_RESIDUAL; a.R = m->h; a.Y = m->h;
+            jsm_status s = linear_bf16_launch(a, st);
+            if (s != JSM_OK) return s;
+            if (next_gain) {
+                fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d);
+                JSM_LAUNCH_CHECK();
+            }
             return JSM_OK;
         }
-        const long long n = (long long)T * N;
-        long long blocks = (n / 4 + 255) / 256;
-        if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
-        fold_partials_kernel<<<(unsigned)blocks, 256, 0, st>>>(m->partial, splits, n, m->red, n);
-        JSM_LAUNCH_CHECK();
+        a.epilogue = LIN_NONE; a.Y = m->red;
+        jsm_status s = linear_bf16_launch(a, st);
+        if (s != JSM_OK) return s;
     }
     // tensor parallel: sum the rank-local outputs, then add into the residual stream
     if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
@@ -278,7 +287,10 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         LayerW& L = m->layers[l];
         LinearArgs a;
         a.X = m->xn; a.W = L.wqkv; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = m->qkv; a.out_mode = 0;
-        a.T = T; a.N = m->qkv_dim; a.K = d; a.splits = 1; a.impl = 0;
+        a.T = T; a.N = m->qkv_dim; a.K = d; a.impl = 0;
+        a.splits = T > 4 ? pick_splits(T, a.N, d) : 1;
+        a.ws = a.splits > 1 ? m->partial : nullptr;
+        a.counters = m->counters;
         s = linear_bf16_launch(a, st);
         if (s != JSM_OK) return s;
         const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
@@ -307,6 +319,8 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, L.g2, st);
         if (s != JSM_OK) return s;
         a.X = m->xn; a.W = L.wgu; a.epilogue = LIN_SILU_MUL; a.Y = m->act; a.N = m->ffn_l; a.K = d;
+        a.splits = T > 4 ? pick_splits(T, a.N, d) : 1;
+        a.ws = a.splits > 1 ? m->partial : nullptr;
         s = linear_bf16_launch(a, st);
         if (s != JSM_OK) return s;
         const float* next_gain = (l + 1 < c.n_layers) ? m->layers[l + 1].g1 : m->gf;
@@ -365,7 +379,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     m->qkv_dim = (m->Hq_l + 2 * m->Hkv_l) * D;
     m->pages_per_seq = (c.max_context + JSM_PAGE_SIZE - 1) / JSM_PAGE_SIZE;
     m->max_tokens = c.max_batch > 512 ? c.max_batch : 512;
-    m->max_splits = 8;
+    m->max_splits = 16;
     m->layers.resize(c.n_layers);
     cudaStream_t st = nullptr;
     const float std = 0.02f;
@@ -431,6 +445,11 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->attn, Tm * m->Hq_l * D));
     JSM_TRY(dev_alloc(m, &m->act, Tm * m->ffn_l));
     JSM_TRY(dev_alloc(m, &m->partial, (size_t)m->max_splits * Tm * d));
+    JSM_TRY(dev_alloc(m, &m->counters, (size_t)8192));
+    {
+        cudaError_t e0 = cudaMemset(m->counters, 0, 8192 * sizeof(int));
+        if (e0 != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: %s", cudaGetErrorString(e0)); }
+    }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
     JSM_TRY(dev_alloc(m, &m->dec_scratch, jsm_attn_decode_scratch_bytes(c.max_batch, m->Hq_l, D, c.max_context) / sizeof(float) + 4));
     cudaError_t e = cudaMemset(m->ctx, 0, sizeof(int32_t) * c.max_batch);

@@ -10,9 +10,9 @@ namespace tc {
 
 // ---- error word ----------------------------------------------------------------
 // A kernel that gives up on a wait stores a code here and unwinds; the host reads it
-// after the stream has been synchronised (jsm_tc_status).
+// after the stream has been synchronised (jsm_check_device_errors).
 enum TcError : int { TC_OK = 0, TC_TIMEOUT_FULL = 1, TC_TIMEOUT_EMPTY = 2, TC_TIMEOUT_ACC = 3, TC_TIMEOUT_MISC = 4 };
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // about two seconds
+constexpr long long WAIT_LIMIT_CYCLES = 400000000ll;  // about 0.2 s: a healthy wait ends within microseconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

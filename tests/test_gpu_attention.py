@@ -131,7 +131,7 @@ def test_flash_prefill_matches_oracle(batch, Tq, Tk, Hq, Hkv, causal):
     k = dev(cases.normal((batch * Tk, Hkv * D), 660, 1), torch.bfloat16)
     v = dev(cases.normal((batch * Tk, Hkv * D), 660, 2), torch.bfloat16)
     got = jb.attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=causal, impl=2)
-    torch.cuda.synchronize()
+    jb.check_device_errors()
     want = ol.attention(host(q), host(k), host(v), batch, Hq, Hkv, D, causal, exact_div=False)
     assert_close(host(got), want, 1e-2, f"flash B{batch} Tq{Tq} Tk{Tk} Hq{Hq} Hkv{Hkv} causal={causal}")
 
@@ -158,6 +158,7 @@ def test_config3_full_size():
     pos = torch.arange(T, dtype=torch.int32, device="cuda").repeat(batch)
     qr, kr = jb.rope_apply(q, table, D, H, positions=pos), jb.rope_apply(k, table, D, H, positions=pos)
     a = jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2)
+    jb.check_device_errors()
     b = jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=1)
     torch.cuda.synchronize()
     assert float((a.float() - b.float()).abs().max()) <= 1e-2 * float(b.float().abs().max())

@@ -221,6 +221,22 @@ def run_kernel_workload(args):
         emit("row_sum_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_SUM, 1, [L0], [A[i]], r), sets), "hbm", full + n * 4, hbm, "GB/s", cfg)
         emit("row_max_GBps", timed(lambda i: jb.eval_rows(jb.ROWS_MAX, 1, [L0], [B[i]], r), sets), "hbm", full + n * 4, hbm, "GB/s", cfg)
         emit("elementwise_A*0.125+B_GBps", timed(lambda i: jb.eval_elementwise(axpb, [A[i], B[i]], Y[i]), sets), "hbm", 3 * full, hbm, "GB/s", cfg)
+    elif args.workload == "gateup":
+        # one SwiGLU gate/up projection of the 7B shape, alone: [2 x 11008, 4096] bf16 weights (180 MB) streamed once per
+        # launch against B tokens; 4 rotating weight sets keep every launch out of L2
+        d, ffn, Bt, sets = 4096, 11008, args.batch, 4
+        Ws = [torch.empty(2 * ffn, d, device="cuda", dtype=torch.bfloat16) for _ in range(sets)]
+        for i, w in enumerate(Ws):
+            jb.fill(w, SEED, 9000 + i, 0, 0.0, 0.02)
+        x = torch.empty(Bt, d, device="cuda", dtype=torch.bfloat16); jb.fill(x, SEED, 7000, 0, 0.0, 1.0)
+        y = torch.empty(Bt, ffn, device="cuda", dtype=torch.bfloat16)
+        cfg = {"workload": f"gate_up_projection_11008x4096_b{Bt}", "l2": f"{sets} rotating weight sets (720 MB) > L2"}
+        work = 2 * ffn * d * 2 + Bt * d * 2 + Bt * ffn * 2
+
+        def once(i):
+            jb.check(jb.lib().jsm_linear_bf16(x.data_ptr(), Ws[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16, Bt, ffn, d,
+                                              jb.stream_ptr()))
+        emit("gate_up_projection_GBps", timed(once, sets), "hbm", work, hbm, "GB/s", cfg)
     elif args.workload == "flash":
         batch, T, H, D = 4, 4096, 32, 128
         q = torch.empty(batch * T, H * D, device="cuda", dtype=torch.bfloat16)
@@ -272,7 +288,7 @@ def main():
     ap.add_argument("--impl", default="jasmine_b200")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode", "gateup"],
                     help="decode = the headline; expr / flash / kvdecode = configurations 2 / 3 / 4 of the baseline "
                          "(kernel-level lines, one JSON line per kernel)")
     ap.add_argument("--profile-steps", type=int, default=0,
@@ -295,6 +311,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
+        # in-switch (NVLS) reductions bind every rank's buffers to one multicast object; plain peer transfers are used
+        # instead so that a rank that leaves abnormally cannot fault the others' GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     B, K, W = args.batch, args.steps, args.warmup
     max_ctx = PROMPT + W + 2 * K + 8
@@ -411,8 +430,7 @@ def main():
     e2e_tok_s = B * Ke / e2e_s
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        shutdown(graph)
         return
 
     # roofline of the dominant kernel, timed alone: the SwiGLU gate/up weight stream of one layer
@@ -470,8 +488,30 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {type(e).__name__}: {e}"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown(graph)
+
+
+def shutdown(graph):
+    """Leaves a multi-rank run without waiting on the communicator: tearing down a process group whose collectives
+    live in a captured graph has blocked forever here, so the graph is dropped first and the process then exits
+    by the regular tear-down; if that still blocks, the process exits after 20 s (all ranks are past their last
+    collective and a final barrier by then)."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    del graph
+    torch.cuda.synchronize()
+    dist.barrier()  # every rank has finished its work: nobody leaves while another still computes
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+
+    def give_up():
+        time.sleep(20.0)
+        os._exit(0)
+    threading.Thread(target=give_up, daemon=True).start()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

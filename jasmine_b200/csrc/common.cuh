@@ -41,6 +41,32 @@ extern std::atomic<uint64_t> g_launches;
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 int sm_count();
 
+// ---- programmatic dependent launch ------------------------------------------------
+// The kernels of a decode step are chained with programmatic stream serialisation: a kernel may become
+// resident while its predecessor still runs, do the work that does not depend on it (barrier set-up, TMEM
+// allocation, streaming or prefetching its WEIGHTS, which no kernel writes) and only then wait for the
+// predecessor's results.  Rules every kernel launched through launch_chained keeps:
+//   * chain_trigger() first, so that its own successor can be made resident early;
+//   * chain_wait() before the first access (read or write) to anything another kernel of the stream
+//     produces or consumes; it returns once the predecessor grid has completed and its writes are visible.
+// Both are no-ops for a kernel launched without the attribute.
+bool chained_launch_enabled();  // JSM_PDL=0 in the environment turns the attribute off (plain stream order)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- counter-based generator (bit-identical on host and device) ------------
 __host__ __device__ inline uint64_t splitmix64(uint64_t x) {
     x += 0x9E3779B97F4A7C15ull;
@@ -116,6 +142,9 @@ __host__ __device__ inline float bf16_bits_to_f32(uint16_t b) {
 }
 
 #ifdef __CUDACC__
+__device__ __forceinline__ void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

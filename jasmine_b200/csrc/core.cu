@@ -1,6 +1,7 @@
 // Library plumbing of the C ABI: error strings, device memory, seeded fills, dtype conversion.
 #include "common.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 namespace jsm {
 
@@ -12,6 +13,15 @@ void set_error(const char* fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(t_error, sizeof(t_error), fmt, ap);
     va_end(ap);
+}
+
+bool chained_launch_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("JSM_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
 }
 
 int sm_count() {

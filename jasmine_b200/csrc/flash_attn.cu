@@ -30,6 +30,12 @@ constexpr int FA_KV_STAGES = 2;
 constexpr uint32_t FA_TILE_BYTES = FA_BM * FA_D * 2;  // 32 KB: two 16 KB halves of 64 columns
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;          // log2 domain
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct FlashParams {
     int Tq, Tk, Hq, Hkv, causal;
     float scale_log2;
@@ -128,42 +134,60 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             constexpr uint32_t idesc_qk = instr_desc_bf16(FA_BM, FA_BN, 0, 0);  // both operands K-major (head_dim contiguous)
             constexpr uint32_t idesc_pv = instr_desc_bf16(FA_BM, FA_D, 0, 1);   // V is N-contiguous: MN-major B
             bool ok = mbar_wait(&q_full, 0, &abort_flag, P.err, TC_TIMEOUT_FULL);
-            for (int j = 0; j < n_max && ok; ++j) {
-                const int s = j % FA_KV_STAGES;
-                const uint32_t ph = (j / FA_KV_STAGES) & 1;
-                if (!mbar_wait(&k_full[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(k_smem + s * FA_TILE_BYTES);
+            // S_t(j) = Q_t . K(j)^T into the S columns of tile t (overwrites P_t(j-1): the tensor pipe runs the MMAs of
+            // this thread in issue order, so the P.V product issued before it has read P by then)
+            auto issue_s = [&](int t, uint32_t k_addr) {
+                const uint32_t q_addr = smem_u32(q_smem + t * FA_TILE_BYTES);
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (j >= n_tiles[t]) continue;
-                    const uint32_t q_addr = smem_u32(q_smem + t * FA_TILE_BYTES);
-#pragma unroll
-                    for (int kk = 0; kk < FA_D / 16; ++kk) {
-                        const uint32_t off = (kk / 4) * (FA_TILE_BYTES / 2);
-                        mma_ss(tmem_base + S_COL[t], smem_desc_sw128(q_addr + off) + (uint64_t)((kk % 4) * 2),
-                               smem_desc_sw128(k_addr + off) + (uint64_t)((kk % 4) * 2), idesc_qk, kk > 0 ? 1u : 0u);
-                    }
-                    mma_commit(&s_full[t]);
+                for (int kk = 0; kk < FA_D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * (FA_TILE_BYTES / 2);
+                    mma_ss(tmem_base + S_COL[t], smem_desc_sw128(q_addr + off) + (uint64_t)((kk % 4) * 2),
+                           smem_desc_sw128(k_addr + off) + (uint64_t)((kk % 4) * 2), idesc_qk, kk > 0 ? 1u : 0u);
                 }
-                mma_commit(&k_empty[s]);
+                mma_commit(&s_full[t]);
+            };
+            // The scores run one key tile ahead of the P.V products: S_t(j+1) is issued right after O_t += P_t(j).V(j),
+            // so the softmax of one query tile overlaps the softmax of the other instead of alternating with it.
+            if (ok && n_max > 0) {
+                ok = mbar_wait(&k_full[0], 0, &abort_flag, P.err, TC_TIMEOUT_FULL);
+                tc_fence_after();
+                if (ok) {
+                    const uint32_t k_addr = smem_u32(k_smem);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                        if (n_tiles[t] > 0) issue_s(t, k_addr);
+                    mma_commit(&k_empty[0]);
+                }
+            }
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int s = j % FA_KV_STAGES, s1 = (j + 1) % FA_KV_STAGES;
+                const uint32_t ph = (j / FA_KV_STAGES) & 1, ph1 = ((j + 1) / FA_KV_STAGES) & 1;
+                const bool more = j + 1 < n_max;
                 if (!mbar_wait(&v_full[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(v_smem + s * FA_TILE_BYTES);
+                const uint32_t k_addr = smem_u32(k_smem + s1 * FA_TILE_BYTES);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                    if (j >= n_tiles[t]) continue;
-                    if (!mbar_wait(&p_ready[t], j & 1, &abort_flag, P.err, TC_TIMEOUT_MISC)) { ok = false; break; }
-                    tc_fence_after();
+                    if (j < n_tiles[t]) {
+                        if (!mbar_wait(&p_ready[t], j & 1, &abort_flag, P.err, TC_TIMEOUT_MISC)) { ok = false; break; }
+                        tc_fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < FA_BN / 16; ++kk) {
-                        // 16 keys = two 8-row groups of 1024 bytes; the two 64-column halves of V are 16 KB apart
-                        const uint64_t v_desc = smem_desc_sw128_mn(v_addr + kk * 2048, FA_TILE_BYTES / 2);
-                        mma_ts(tmem_base + O_COL[t], tmem_base + S_COL[t] + kk * 8, v_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+                            // 16 keys = two 8-row groups of 1024 bytes; the two 64-column halves of V are 16 KB apart
+                            const uint64_t v_desc = smem_desc_sw128_mn(v_addr + kk * 2048, FA_TILE_BYTES / 2);
+                            mma_ts(tmem_base + O_COL[t], tmem_base + S_COL[t] + kk * 8, v_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
+                    if (t == 0 && more) {
+                        if (!mbar_wait(&k_full[s1], ph1, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
+                        tc_fence_after();
+                    }
+                    if (j + 1 < n_tiles[t]) issue_s(t, k_addr);
                 }
                 if (!ok) break;
                 mma_commit(&v_empty[s]);
+                if (more) mma_commit(&k_empty[s1]);
             }
             if (ok) mma_commit(&o_done);
         }
@@ -188,7 +212,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 tmem_ld32(s_addr + c, r);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]) * P.scale_log2;
+                for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]);
             }
             const int key0 = j * FA_BN;
             const bool needs_mask = (P.causal && key0 + FA_BN - 1 > q0 + t * FA_BM + shift) || key0 + FA_BN > P.Tk;
@@ -197,15 +221,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 for (int i = 0; i < FA_BN; ++i)
                     if ((P.causal && key0 + i > qpos) || key0 + i >= P.Tk) sv[i] = -INFINITY;
             }
+            // scores stay unscaled in registers; the scale (> 0, log2 domain) is applied inside the exponent's FMA
             float mx = sv[0];
 #pragma unroll
             for (int i = 1; i < FA_BN; ++i) mx = fmaxf(mx, sv[i]);
+            mx *= P.scale_log2;
             // tcgen05.ld / st are warp-collective: the decision to touch the accumulator is taken per warp,
             // each lane then applies its own factor (1 for the rows whose maximum did not move)
             const bool grow = mx > m_ref + FA_RESCALE_THRESHOLD;
             if (__any_sync(0xffffffffu, grow)) {
                 // raise the reference maximum; the accumulated O and l shrink by 2^(old - new)
-                const float alpha = grow ? exp2f(m_ref - mx) : 1.0f;
+                const float alpha = grow ? ex2_approx(m_ref - mx) : 1.0f;
                 if (j > 0) {
 #pragma unroll
                     for (int c = 0; c < FA_D; c += 32) {
@@ -228,12 +254,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
             }
             // p = 2^(s - m_ref), packed to bf16 pairs, written over the first 64 columns of S
             float lsum = 0.0f;
+            const float neg_m = -m_ref, sc = P.scale_log2;
 #pragma unroll
             for (int c = 0; c < FA_BN / 2; c += 16) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = exp2f(sv[2 * (c + i)] - m_ref), p1 = exp2f(sv[2 * (c + i) + 1] - m_ref);
+                    const float p0 = ex2_approx(fmaf(sv[2 * (c + i)], sc, neg_m)), p1 = ex2_approx(fmaf(sv[2 * (c + i) + 1], sc, neg_m));
                     lsum += p0 + p1;
                     w[i] = pack_bf16x2(p0, p1);
                 }
@@ -284,6 +311,7 @@ jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, voi
                                 int causal, float scale, const float* rope, cudaStream_t st, long long q_rs, long long kv_rs,
                                 long long o_rs) {
     if (rope) JSM_FAIL(JSM_UNSUPPORTED, "flash_prefill: q and k must already be rotated");
+    if (!(scale > 0.0f)) JSM_FAIL(JSM_UNSUPPORTED, "flash_prefill: the softmax scale (%g) must be positive", (double)scale);
     if (q_rs <= 0) q_rs = (long long)Hq * FA_D;
     if (kv_rs <= 0) kv_rs = (long long)Hkv * FA_D;
     if (o_rs <= 0) o_rs = (long long)Hq * FA_D;

@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(128) kv_append_kernel(__nv_bfloat16* __restric
                                                         const __nv_bfloat16* __restrict__ v, long long row_stride,
                                                         const int32_t* __restrict__ seq_ids, const int32_t* __restrict__ positions,
                                                         int Hkv, int D, const float4* __restrict__ rope) {
+    chain_trigger();
+    chain_wait();
     const int t = blockIdx.x, hk = blockIdx.y;
     const int seq = seq_ids ? seq_ids[t] : 0;
     const int pos = positions[t];
@@ -73,6 +75,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     const int32_t* __restrict__ block_table, int max_pages, const int32_t* __restrict__ context_lens, int Hq, int Hkv,
     float scale_log2, const float4* __restrict__ rope, int n_chunks, int chunk_len, float* __restrict__ scratch) {
     constexpr int D = 128;
+    chain_trigger();
+    chain_wait();
     const int chunk = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int ctx = context_lens[seq];
     const int c_begin = chunk * chunk_len;
@@ -226,6 +230,8 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
                                                                 const int32_t* __restrict__ context_lens, int Hq, int n_chunks,
                                                                 int chunk_len, __nv_bfloat16* __restrict__ out) {
     constexpr int D = 128;
+    chain_trigger();
+    chain_wait();
     const int h = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
     const int n = (context_lens[seq] + chunk_len - 1) / chunk_len;
     const float* src = scratch + ((long long)seq * Hq + h) * n_chunks * (D + 2);
@@ -251,9 +257,9 @@ extern "C" jsm_status jsm_kv_append(void* d_pool, const int32_t* d_block_table, 
     if (!d_pool || !d_block_table || !d_k || !d_v || !d_positions) JSM_FAIL(JSM_INVALID_ARG, "jsm_kv_append: null pointer");
     if (D <= 0 || D % 2 || Hkv <= 0 || max_pages <= 0) JSM_FAIL(JSM_SHAPE, "jsm_kv_append: Hkv %d D %d max_pages %d", Hkv, D, max_pages);
     dim3 grid(T, Hkv);
-    kv_append_kernel<<<grid, 64, 0, as_stream(stream)>>>((__nv_bfloat16*)d_pool, d_block_table, max_pages, (const __nv_bfloat16*)d_k,
-                                                         (const __nv_bfloat16*)d_v, kv_row_stride, d_seq_ids, d_positions, Hkv, D,
-                                                         (const float4*)d_rope_table);
+    JSM_CUDA_CHECK(launch_chained(kv_append_kernel, grid, dim3(64), 0, as_stream(stream), (__nv_bfloat16*)d_pool, d_block_table, max_pages,
+                                  (const __nv_bfloat16*)d_k, (const __nv_bfloat16*)d_v, (long long)kv_row_stride, d_seq_ids, d_positions,
+                                  Hkv, D, (const float4*)d_rope_table));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -281,9 +287,9 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
     cudaStream_t st = as_stream(stream);
     const float sl2 = scale * LOG2E;
 #define JSM_DEC(GG)                                                                                                            \
-    attn_decode_kernel<GG><<<grid, DEC_WARPS * 32, 0, st>>>((const __nv_bfloat16*)d_q, q_row_stride, (const __nv_bfloat16*)d_pool, \
-                                                            d_block_table, max_pages, d_context_lens, Hq, Hkv, sl2,               \
-                                                            (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch)
+    JSM_CUDA_CHECK(launch_chained(attn_decode_kernel<GG>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)d_q,          \
+                                  (long long)q_row_stride, (const __nv_bfloat16*)d_pool, d_block_table, max_pages, d_context_lens, \
+                                  Hq, Hkv, sl2, (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch))
     switch (G) {
         case 1: JSM_DEC(1); break;
         case 2: JSM_DEC(2); break;
@@ -293,8 +299,8 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
     }
 #undef JSM_DEC
     JSM_LAUNCH_CHECK();
-    attn_decode_merge_kernel<<<dim3(Hq, n_seqs), 128, 0, st>>>((const float*)d_scratch, d_context_lens, Hq, n_chunks, chunk,
-                                                               (__nv_bfloat16*)d_out);
+    JSM_CUDA_CHECK(launch_chained(attn_decode_merge_kernel, dim3(Hq, n_seqs), dim3(128), 0, st, (const float*)d_scratch, d_context_lens,
+                                  Hq, n_chunks, chunk, (__nv_bfloat16*)d_out));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }

@@ -107,6 +107,8 @@ struct TcParams {
     int* err;
     float* ws;            // split-K with in-kernel fix-up: partials [split][T][ldw]
     int* counters;        // one arrival counter per output tile, zero between launches
+    int w_early;          // W is constant for the whole stream: its tiles may be fetched before the predecessor kernel ends
+    int pf_kb;            // with w_early: k-blocks of W beyond the ring that are prefetched into L2 up front
 };
 
 template <int BN, bool GATEUP>
@@ -128,6 +130,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
 
+    chain_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BM;   // first output feature of the tile
     const int t0 = blockIdx.y * BN;   // first token of the tile
@@ -160,7 +163,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // ---- producer: one thread streams W and X tiles into the ring
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < n_kb; ++i) {
+            // weights never change while the stream runs: the first ring of W tiles is requested (and further tiles are
+            // pulled into L2) before the predecessor kernel has finished; the tokens X are its output and wait for it
+            const int pre = P.w_early ? min(n_kb, stages) : 0;
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* st = tiles + (size_t)i * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                const int kx = (kb_begin + i) * BK;
+                tma_load_2d(st, &tmap_w, kx, n0, &full_bar[i]);
+                if (GATEUP) tma_load_2d(st + BM * BK * 2, &tmap_w, kx, P.N + n0, &full_bar[i]);
+            }
+            if (P.w_early) {
+                const int pf_end = min(n_kb, pre + P.pf_kb);
+                for (int i = pre; i < pf_end; ++i) {
+                    const int kx = (kb_begin + i) * BK;
+                    tma_prefetch_2d(&tmap_w, kx, n0);
+                    if (GATEUP) tma_prefetch_2d(&tmap_w, kx, P.N + n0);
+                }
+            }
+            chain_wait();
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + A_BYTES, &tmap_x, (kb_begin + i) * BK, t0, &full_bar[i]);
+            issued = pre;
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % stages;
                 const uint32_t ph = (i / stages) & 1;
                 if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
@@ -214,6 +239,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         bool ok = n_kb > 0;
         if (ok) ok = mbar_wait(&acc_bar, 0, &abort_flag, P.err, TC_TIMEOUT_ACC);
         tc_fence_after();
+        chain_wait();  // the residual input, the output and the workspace belong to the stream's other kernels
         if (ok && P.ws && gridDim.z > 1) {
             // ---- split-K with in-kernel fix-up: every CTA of a tile stores its raw partial; the one that arrives last
             // adds the partials in split order (so the result does not depend on who is last) and runs the epilogue
@@ -248,23 +274,60 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if (is_last) P.counters[tile_id] = 0;  // ready for the next launch
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (is_last && feat < P.N) {
+            if (is_last) {
+                // 128 threads fold the tile: a thread owns 4 consecutive features of every fourth token, the partials of
+                // four tokens are in flight at once and are added in split order (the result does not depend on who came last)
                 __threadfence();
-                const float bias = P.bias ? P.bias[feat] : 0.0f;
-                for (int t = t0; t < min(P.T, t0 + BN); ++t) {
-                    float v = 0.0f, up = 0.0f;
-                    for (int z = 0; z < (int)gridDim.z; ++z) {
-                        const float* w = P.ws + ((size_t)z * P.T + t) * ldw + feat;
-                        v += __ldcg(w);
-                        if (GATEUP) up += __ldcg(w + P.N);
+                const int tid = threadIdx.x - 64;
+                const int n = n0 + (tid & 31) * 4, tsub = tid >> 5;
+                const int t_end = min(P.T, t0 + BN);
+                if (n < P.N) {
+                    const float4 bias4 = P.bias ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int tb = t0 + tsub; tb < t_end; tb += 16) {
+                        float4 g[4], u[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { g[i] = make_float4(0.f, 0.f, 0.f, 0.f); u[i] = g[i]; }
+#pragma unroll 2
+                        for (int z = 0; z < (int)gridDim.z; ++z) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int t = tb + 4 * i;
+                                if (t < t_end) {
+                                    const float* w = P.ws + ((size_t)z * P.T + t) * ldw + n;
+                                    const float4 a = __ldcg(reinterpret_cast<const float4*>(w));
+                                    g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
+                                    if (GATEUP) {
+                                        const float4 c = __ldcg(reinterpret_cast<const float4*>(w + P.N));
+                                        u[i].x += c.x; u[i].y += c.y; u[i].z += c.z; u[i].w += c.w;
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int t = tb + 4 * i;
+                            if (t >= t_end) break;
+                            float v[4] = {g[i].x + bias4.x, g[i].y + bias4.y, g[i].z + bias4.z, g[i].w + bias4.w};
+                            const float uu[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+                            if (P.epilogue == LIN_RESIDUAL) {
+                                const uint2 r = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                                v[0] += bf16lo(r.x); v[1] += bf16hi(r.x); v[2] += bf16lo(r.y); v[3] += bf16hi(r.y);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (GATEUP) v[j] = silu_f(v[j]) * uu[j];
+                                else if (P.epilogue == LIN_RELU) v[j] = fmaxf(v[j], 0.0f);
+                                else if (P.epilogue == LIN_GELU) v[j] = gelu_f(v[j]);
+                            }
+                            if (P.out_mode == 0) {
+                                uint2 o;
+                                o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+                                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
+                            } else {
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.Y) + (size_t)t * P.N + n) = make_float4(v[0], v[1], v[2], v[3]);
+                            }
+                        }
                     }
-                    v += bias;
-                    if (GATEUP) v = silu_f(v) * up;
-                    else if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
-                    else if (P.epilogue == LIN_GELU) v = gelu_f(v);
-                    else if (P.epilogue == LIN_RESIDUAL) v += __bfloat162float(P.R[(size_t)t * P.N + feat]);
-                    if (P.out_mode == 0) reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + feat] = __float2bfloat16_rn(v);
-                    else reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + feat] = v;
                 }
             }
         } else if (ok) {
@@ -327,8 +390,9 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x) {
 template <int TOK, bool GATEUP, int ROWS>
 __global__ void __launch_bounds__(256) gemv_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                                                    const float* __restrict__ bias, int epilogue, const __nv_bfloat16* __restrict__ R,
-                                                   void* __restrict__ Y, int out_f32, int N, int K) {
+                                                   void* __restrict__ Y, int out_f32, int N, int K, int w_early) {
     constexpr int OUTS = GATEUP ? ROWS / 2 : ROWS;
+    chain_trigger();
     const int warp = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int o0 = warp * OUTS;  // first output of this warp
     if (o0 >= N) return;
@@ -348,6 +412,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __nv_bfloat16* __restri
 #pragma unroll
         for (int t = 0; t < TOK; ++t) acc[r][t] = 0.0f;
     const int nvec = K / 8;
+    chain_wait();
 #pragma unroll 4
     for (int v = lane; v < nvec; v += 32) {
         uint4 w[ROWS];
@@ -385,22 +450,25 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __nv_bfloat16* __restri
 
 template <int TOK>
 static void launch_gemv(const void* X, const void* W, const float* bias, int epi, const void* R, void* Y, int out_f32, int N, int K,
-                        cudaStream_t st) {
+                        bool chained, cudaStream_t st) {
     const bool gu = epi == LIN_SILU_MUL;
     // enough warps for two CTAs on every SM: narrow outputs use two rows per warp instead of four
     const bool narrow = !gu && (N / 4 + 7) / 8 < 2 * sm_count();
     const int outs_per_warp = gu ? 2 : (narrow ? 2 : 4);
     const int warps = (N + outs_per_warp - 1) / outs_per_warp;
     const int blocks = (warps + 7) / 8;
-    if (gu)
-        gemv_kernel<TOK, true, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
-                                                          (const __nv_bfloat16*)R, Y, out_f32, N, K);
-    else if (narrow)
-        gemv_kernel<TOK, false, 2><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
-                                                           (const __nv_bfloat16*)R, Y, out_f32, N, K);
-    else
-        gemv_kernel<TOK, false, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
-                                                           (const __nv_bfloat16*)R, Y, out_f32, N, K);
+    const int early = chained ? 1 : 0;
+    auto go = [&](auto kernel) {
+        if (chained)
+            launch_chained(kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi,
+                           (const __nv_bfloat16*)R, Y, out_f32, N, K, early);
+        else
+            kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, epi, (const __nv_bfloat16*)R, Y,
+                                           out_f32, N, K, early);
+    };
+    if (gu) go(gemv_kernel<TOK, true, 4>);
+    else if (narrow) go(gemv_kernel<TOK, false, 2>);
+    else go(gemv_kernel<TOK, false, 4>);
 }
 
 template <int BN, bool GATEUP>
@@ -421,7 +489,17 @@ static jsm_status launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const 
         attr_done = true;
     }
     dim3 grid((P.N + BM - 1) / BM, (P.T + BN - 1) / BN, splits);
-    linear_tc_kernel<BN, GATEUP><<<grid, TC_THREADS, smem, st>>>(mw, mx, P, stages);
+    TcParams Q = P;
+    if (Q.w_early) {
+        // L2 prefetch beyond the ring: at most about 48 MB per launch over all CTAs
+        const long long per_kb = (long long)A_BYTES * n_ctas;
+        long long pf = per_kb > 0 ? (48ll << 20) / per_kb : 0;
+        Q.pf_kb = (int)(pf > 64 ? 64 : pf);
+        JSM_CUDA_CHECK(launch_chained(linear_tc_kernel<BN, GATEUP>, grid, dim3(TC_THREADS), smem, st, mw, mx, Q, stages));
+        g_launches.fetch_add(1);
+        return JSM_OK;
+    }
+    linear_tc_kernel<BN, GATEUP><<<grid, TC_THREADS, smem, st>>>(mw, mx, Q, stages);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -434,17 +512,17 @@ jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st) {
     if (a.epilogue == LIN_RESIDUAL && !a.R) JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: residual epilogue without R");
     if (a.splits > 1 && !a.ws && (a.out_mode != 2 || a.epilogue != LIN_NONE))
         JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K without a workspace writes raw f32 partials only");
-    if (a.splits > 1 && a.ws && (a.out_mode == 2 || !a.counters))
-        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K with in-kernel fix-up needs arrival counters and a final output");
+    if (a.splits > 1 && a.ws && (a.out_mode == 2 || !a.counters || a.N % 4))
+        JSM_FAIL(JSM_INVALID_ARG, "linear_bf16: split-K with in-kernel fix-up needs arrival counters, a final output and N %% 4 == 0");
     const bool use_gemv = a.impl == 1 || (a.impl == 0 && a.T <= 4 && a.out_mode != 2);
     if (use_gemv) {
         if (a.T > 4) JSM_FAIL(JSM_UNSUPPORTED, "linear_bf16: the CUDA-core kernel takes at most 4 tokens");
         const int f32 = a.out_mode == 1;
         switch (a.T) {
-            case 1: launch_gemv<1>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
-            case 2: launch_gemv<2>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
-            case 3: launch_gemv<3>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
-            default: launch_gemv<4>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, st); break;
+            case 1: launch_gemv<1>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, a.chained, st); break;
+            case 2: launch_gemv<2>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, a.chained, st); break;
+            case 3: launch_gemv<3>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, a.chained, st); break;
+            default: launch_gemv<4>(a.X, a.W, a.bias, a.epilogue, a.R, a.Y, f32, a.N, a.K, a.chained, st); break;
         }
         JSM_LAUNCH_CHECK();
         return JSM_OK;
@@ -465,6 +543,7 @@ jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st) {
     P.epilogue = a.epilogue; P.out_mode = a.out_mode; P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y;
     P.err = tc_error_word();
     P.ws = a.ws; P.counters = a.counters;
+    P.w_early = a.chained ? 1 : 0; P.pf_kb = 0;
     const int grid_z = a.out_mode == 2 ? (a.splits < 1 ? 1 : a.splits) : (a.ws ? splits : 1);
     if (gu) {
         switch (bn) {

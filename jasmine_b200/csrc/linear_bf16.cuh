@@ -18,6 +18,8 @@ struct LinearArgs {
     int splits;         // grid split along K: out_mode 2 writes the raw partials; with a workspace the kernel folds them itself
     int impl;           // 0 auto, 1 CUDA-core stream (T <= 4), 2 tcgen05
     float* ws = nullptr;      // workspace of splits * T * (N or 2N) floats for the in-kernel fix-up
+    bool chained = false;     // launched as a link of a kernel chain whose weights are constant: W may be fetched before the
+                              // predecessor kernel has finished (programmatic dependent launch)
     int* counters = nullptr;  // ceil(N/128) * ceil(T/BN) arrival counters, zero before the first launch
 };
 

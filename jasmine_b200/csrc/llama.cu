@@ -48,6 +48,7 @@ struct jsm_model {
     float* partial = nullptr;
     float* logits = nullptr;
     float* dec_scratch = nullptr;
+    size_t ws_floats = 0;        // capacity of `partial`
     int* counters = nullptr;     // arrival counters of the split-K projections (self-resetting)
     std::vector<void*> allocs;
     jsm_allreduce_fn allreduce = nullptr;
@@ -78,6 +79,8 @@ __global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = va
 // decode bookkeeping on the device so that a captured step can be replayed: the new token of
 // sequence b goes to position ctx[b], then the context grows by one
 __global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch) {
+    chain_trigger();
+    chain_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch) { pos[b] = ctx[b]; seq_ids[b] = b; ctx[b] = ctx[b] + 1; }
 }
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(256) fold_add_norm_kernel(__nv_bfloat16* __res
                                                             long long split_stride, const __nv_bfloat16* __restrict__ delta,
                                                             const float* __restrict__ gain, float eps, __nv_bfloat16* __restrict__ y, int d) {
     __shared__ float smem[8];
+    chain_trigger();
+    chain_wait();
     const long long base = (long long)blockIdx.x * d;
     float v[MAXV][8];
     float q = 0.0f;
@@ -168,6 +173,8 @@ __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restr
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n) {
     __shared__ float sv[8];
     __shared__ int si[8];
+    chain_trigger();
+    chain_wait();
     const float* row = x + (long long)blockIdx.x * n;
     float m = -INFINITY;
     int mi = 0x7fffffff;
@@ -212,7 +219,7 @@ static void fill_shard(__nv_bfloat16* dst, long long rows, long long cols, long 
     g_launches.fetch_add(1);
 }
 
-static int pick_splits(int T, int N, int K) {
+static int pick_splits_raw(int T, int N, int K) {
     // a weight stream wants about two CTAs per SM in flight; the fp32 partials (written and read once per split)
     // must stay small next to the weights: splits * T * N * 8 bytes <= a quarter of N * K * 2 bytes
     const int tiles = ((N + 127) / 128) * ((T + 127) / 128);
@@ -225,11 +232,20 @@ static int pick_splits(int T, int N, int K) {
     return s < 1 ? 1 : s;
 }
 
+// never more splits than the workspace of fp32 partials holds (ld = N, or 2N for the fused gate/up projection)
+static int pick_splits(const jsm_model* m, int T, int N, int K, int ld) {
+    int s = pick_splits_raw(T, N, K);
+    const size_t per_split = (size_t)T * ld;
+    while (s > 1 && (size_t)s * per_split > m->ws_floats) --s;
+    return s;
+}
+
 // Y_partial = X . W^T into the residual stream h, then xn = RMSNorm(h) * gain (gain may be null: no norm)
 static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
                                         const float* next_gain, cudaStream_t st) {
     const bool tp = m->c.tp_size > 1;
     LinearArgs a;
+    a.chained = true;  // the model's weights are constant while its stream runs
     a.X = X; a.W = W; a.bias = nullptr; a.R = nullptr; a.T = T; a.N = N; a.K = K; a.impl = 0;
     const int d = m->c.d_model;
     if (T <= 4) {
@@ -238,7 +254,7 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
             jsm_status s = linear_bf16_launch(a, st);
             if (s != JSM_OK) return s;
             if (next_gain) {
-                fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d);
+                JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d));
                 JSM_LAUNCH_CHECK();
             }
             return JSM_OK;
@@ -249,7 +265,7 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
     } else {
         // weight stream split along K; the CTA that finishes a tile last folds the partials and writes the result:
         // straight into the residual stream on one GPU, into the all-reduce buffer under tensor parallelism
-        a.splits = pick_splits(T, N, K);
+        a.splits = pick_splits(m, T, N, K, N);
         a.ws = a.splits > 1 ? m->partial : nullptr;
         a.counters = m->counters;
         a.out_mode = 0;
@@ -258,7 +274,7 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
             jsm_status s = linear_bf16_launch(a, st);
             if (s != JSM_OK) return s;
             if (next_gain) {
-                fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d);
+                JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d));
                 JSM_LAUNCH_CHECK();
             }
             return JSM_OK;
@@ -270,7 +286,7 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
     // tensor parallel: sum the rank-local outputs, then add into the residual stream
     if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
     if (m->allreduce(m->red, (size_t)T * N, JSM_BF16, st, m->allreduce_user) != 0) JSM_FAIL(JSM_NCCL, "all-reduce callback failed");
-    fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, m->red, next_gain, m->c.norm_eps, next_gain ? m->xn : nullptr, d);
+    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, next_gain, m->c.norm_eps, next_gain ? m->xn : nullptr, d));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -280,15 +296,16 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
     const int d = c.d_model, D = c.head_dim;
     jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
     if (s != JSM_OK) return s;
-    fold_add_norm_kernel<2><<<T, 256, 0, st>>>(m->h, nullptr, 0, 0, nullptr, m->layers[0].g1, c.norm_eps, m->xn, d);
+    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, m->layers[0].g1, c.norm_eps, m->xn, d));
     JSM_LAUNCH_CHECK();
     const float scale = 1.0f / sqrtf((float)D);
     for (int l = 0; l < c.n_layers; ++l) {
         LayerW& L = m->layers[l];
         LinearArgs a;
+    a.chained = true;  // the model's weights are constant while its stream runs
         a.X = m->xn; a.W = L.wqkv; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = m->qkv; a.out_mode = 0;
         a.T = T; a.N = m->qkv_dim; a.K = d; a.impl = 0;
-        a.splits = T > 4 ? pick_splits(T, a.N, d) : 1;
+        a.splits = T > 4 ? pick_splits(m, T, a.N, d, a.N) : 1;
         a.ws = a.splits > 1 ? m->partial : nullptr;
         a.counters = m->counters;
         s = linear_bf16_launch(a, st);
@@ -319,7 +336,7 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, L.g2, st);
         if (s != JSM_OK) return s;
         a.X = m->xn; a.W = L.wgu; a.epilogue = LIN_SILU_MUL; a.Y = m->act; a.N = m->ffn_l; a.K = d;
-        a.splits = T > 4 ? pick_splits(T, a.N, d) : 1;
+        a.splits = T > 4 ? pick_splits(m, T, a.N, d, 2 * a.N) : 1;
         a.ws = a.splits > 1 ? m->partial : nullptr;
         s = linear_bf16_launch(a, st);
         if (s != JSM_OK) return s;
@@ -335,12 +352,13 @@ static jsm_status logits_and_argmax(jsm_model* m, const __nv_bfloat16* xn_rows, 
                                     cudaStream_t st) {
     float* lg = d_logits ? d_logits : m->logits;
     LinearArgs a;
+    a.chained = true;  // the model's weights are constant while its stream runs
     a.X = xn_rows; a.W = m->lm_head; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = lg; a.out_mode = 1;
     a.T = rows; a.N = m->c.vocab; a.K = m->c.d_model; a.splits = 1; a.impl = 0;
     jsm_status s = linear_bf16_launch(a, st);
     if (s != JSM_OK) return s;
     if (d_next) {
-        argmax_rows_kernel<<<rows, 256, 0, st>>>(lg, d_next, m->c.vocab);
+        JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
         JSM_LAUNCH_CHECK();
     }
     return JSM_OK;
@@ -444,7 +462,8 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->qkv, Tm * m->qkv_dim));
     JSM_TRY(dev_alloc(m, &m->attn, Tm * m->Hq_l * D));
     JSM_TRY(dev_alloc(m, &m->act, Tm * m->ffn_l));
-    JSM_TRY(dev_alloc(m, &m->partial, (size_t)m->max_splits * Tm * d));
+    m->ws_floats = (size_t)m->max_splits * Tm * d;
+    JSM_TRY(dev_alloc(m, &m->partial, m->ws_floats));
     JSM_TRY(dev_alloc(m, &m->counters, (size_t)8192));
     {
         cudaError_t e0 = cudaMemset(m->counters, 0, 8192 * sizeof(int));
@@ -516,7 +535,7 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step: null argument");
     if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step: batch %d (1..%d)", batch, m->c.max_batch);
     cudaStream_t st = as_stream(stream);
-    advance_kernel<<<(batch + 255) / 256, 256, 0, st>>>(m->ctx, m->pos, m->seq_ids, batch);
+    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch));
     JSM_LAUNCH_CHECK();
     jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
     if (s != JSM_OK) return s;

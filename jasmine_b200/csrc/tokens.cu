@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(256) embedding_kernel(const T* __restrict__ ta
                                                         const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
                                                         T* __restrict__ out, int d) {
     constexpr int N = VecIO<T>::N;
+    chain_trigger();
+    chain_wait();
     const int t = blockIdx.x;
     const long long row = ids[t];
     const long long prow = pos_table ? (positions ? positions[t] : t) : 0;
@@ -145,12 +147,12 @@ extern "C" jsm_status jsm_embedding(const void* d_table, const void* d_pos_table
     if (T == 0) return JSM_OK;
     if (!d_table || !d_ids || !d_out) JSM_FAIL(JSM_INVALID_ARG, "jsm_embedding: null pointer");
     if (dtype == JSM_F32 && d % 4 == 0)
-        embedding_kernel<float><<<T, 256, 0, as_stream(stream)>>>((const float*)d_table, (const float*)d_pos_table, d_ids,
-                                                                 d_positions, (float*)d_out, d);
+        JSM_CUDA_CHECK(launch_chained(embedding_kernel<float>, dim3(T), dim3(256), 0, as_stream(stream), (const float*)d_table,
+                                      (const float*)d_pos_table, d_ids, d_positions, (float*)d_out, d));
     else if (dtype == JSM_BF16 && d % 8 == 0)
-        embedding_kernel<__nv_bfloat16><<<T, 256, 0, as_stream(stream)>>>((const __nv_bfloat16*)d_table,
-                                                                         (const __nv_bfloat16*)d_pos_table, d_ids, d_positions,
-                                                                         (__nv_bfloat16*)d_out, d);
+        JSM_CUDA_CHECK(launch_chained(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, as_stream(stream),
+                                      (const __nv_bfloat16*)d_table, (const __nv_bfloat16*)d_pos_table, d_ids, d_positions,
+                                      (__nv_bfloat16*)d_out, d));
     else
         JSM_FAIL(JSM_UNSUPPORTED, "jsm_embedding: dtype %d with d %d (d must be a multiple of 16 bytes)", (int)dtype, d);
     JSM_LAUNCH_CHECK();

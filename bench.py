@@ -237,6 +237,15 @@ def run_kernel_workload(args):
             jb.check(jb.lib().jsm_linear_bf16(x.data_ptr(), Ws[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16, Bt, ffn, d,
                                               jb.stream_ptr()))
         emit("gate_up_projection_GBps", timed(once, sets), "hbm", work, hbm, "GB/s", cfg)
+        # the same projection over packed weights (contiguous 16 KB tiles, stream-K split over all SMs)
+        Wp = [jb.linear_pack(w, ffn, paired=True) for w in Ws]
+
+        def once_packed(i):
+            jb.check(jb.lib().jsm_linear_bf16_packed(x.data_ptr(), Wp[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16, Bt,
+                                                     ffn, d, jb.stream_ptr()))
+        once_packed(0)
+        jb.check_device_errors()
+        emit("gate_up_projection_packed_GBps", timed(once_packed, sets), "hbm", work, hbm, "GB/s", cfg)
     elif args.workload == "flash":
         batch, T, H, D = 4, 4096, 32, 128
         q = torch.empty(batch * T, H * D, device="cuda", dtype=torch.bfloat16)
@@ -434,29 +443,30 @@ def main():
         return
 
     # roofline of the dominant kernel, timed alone: the SwiGLU gate/up weight stream of one layer
-    # (2 x 11008 x 4096 bf16 = 180 MB per launch, a different layer every launch: larger than L2)
+    # (2 x 11008 x 4096 bf16 = 180 MB per launch over packed weights, 4 rotating weight sets: larger than L2)
     peak, peak_kind = measured_peaks()
     d, ffn_l = cfg["d_model"], cfg["d_ffn"] // world
     x = torch.empty(B, d, device="cuda", dtype=torch.bfloat16)
     jb.fill(x, SEED, 7000, 0, 0.0, 1.0)
     y = torch.empty(B, ffn_l, device="cuda", dtype=torch.bfloat16)
-    wptrs = []
-    for l in range(cfg["n_layers"]):
-        p, n = C.c_void_p(), C.c_size_t()
-        jb.check(jb.lib().jsm_llama_weight(model._h, f"layers.{l}.wgu".encode(), C.byref(p), C.byref(n)))
-        wptrs.append(p.value)
+    packed_sets = []
+    for i in range(4):
+        w = torch.empty(2 * ffn_l, d, device="cuda", dtype=torch.bfloat16)
+        jb.fill(w, SEED, 9000 + i, 0, 0.0, 0.02)
+        packed_sets.append(jb.linear_pack(w, ffn_l, paired=True))
+        del w
 
-    def stream_once(l):
-        jb.check(jb.lib().jsm_linear_bf16(x.data_ptr(), wptrs[l], None, 3, None, y.data_ptr(), jb.BF16, B, ffn_l, d,
-                                          jb.stream_ptr()))
-    for l in range(min(4, len(wptrs))):
-        stream_once(l)
+    def stream_once(i):
+        jb.check(jb.lib().jsm_linear_bf16_packed(x.data_ptr(), packed_sets[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16,
+                                                 B, ffn_l, d, jb.stream_ptr()))
+    for i in range(4):
+        stream_once(i)
     torch.cuda.synchronize()
-    reps = 3 * len(wptrs)
+    reps = 96
     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     r0.record()
     for i in range(reps):
-        stream_once(i % len(wptrs))
+        stream_once(i % 4)
     r1.record()
     torch.cuda.synchronize()
     k_ms = r0.elapsed_time(r1) / reps
@@ -471,7 +481,7 @@ def main():
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "gate/up projection weight stream (jsm_linear_bf16, silu*up epilogue)",
+                     "traffic": None, "kernel": "linear_packed_kernel: gate/up projection weight stream (jsm_linear_bf16_packed, silu*up epilogue)",
                      "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes},
         "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_gbs, "frac": step_gbs / peak,
                           "note": "all weights + cached K/V of the step over the measured step time"},

@@ -172,6 +172,32 @@ jsm_status jsm_dot_f32(jsm_mat A, jsm_mat B, const jsm_mat* bias, int epilogue, 
 jsm_status jsm_linear_bf16(const void* d_X, const void* d_W, const float* d_bias, int epilogue, const void* d_R,
                            void* d_Y, int out_dtype, int T, int N, int K, void* stream);
 
+/* The same projection over weights that were packed once (inference: weight_net_t's W does not change between
+ * forwards).  The packed image stores every 128-feature x 64-k tile as one contiguous 16 KB block in the
+ * shared-memory layout of the tensor cores, tiles in stream order, so that the kernel reads the matrix as one linear
+ * stream split evenly over all SMs.  paired != 0 packs a [2N, K] matrix of N gate rows followed by N up rows for
+ * epilogue 3 (silu(gate)*up), N being the number of gate rows.
+ * jsm_linear_packed_bytes: size of the packed image.  jsm_linear_pack / jsm_linear_unpack convert between the
+ * reference's [out, in] layout and the packed image.  jsm_linear_bf16_packed: any T (chunks of 256 tokens);
+ * N % 4 == 0, K % 8 == 0; it keeps a grow-only per-device workspace (first call of a shape allocates: make it
+ * outside stream capture) that overlapping calls on different streams would share. */
+size_t jsm_linear_packed_bytes(int N, int K, int paired);
+/* The work split of a packed projection: tiles of 128 packed rows, k-blocks of 64 per tile, CTAs in the grid
+ * (CTA c streams units [c*U/G, (c+1)*U/G) of the U = n_tiles*kbt units) and the most CTAs that share one tile. */
+jsm_status jsm_linear_packed_plan(int N, int K, int paired, int* n_tiles, int* kbt, int* grid, int* max_slots);
+jsm_status jsm_linear_pack(const void* d_W, int N, int K, int paired, void* d_packed, void* stream);
+jsm_status jsm_linear_unpack(const void* d_packed, int N, int K, int paired, void* d_W, void* stream);
+jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_packed, const float* d_bias, int epilogue,
+                                  const void* d_R, void* d_Y, int out_dtype, int T, int N, int K, void* stream);
+
+/* Timeline of the packed projections (profiling aid, off by default; the reference has no tracing).  Between
+ * jsm_trace_begin and jsm_trace_end every launch of the packed projection kernel (up to max_launches, eager launches
+ * only: not inside a replayed graph) records 8 device time stamps in ns per CTA: resident, first weights requested,
+ * predecessor complete, first stage landed, last MMA issued, first / last epilogue done, CTA done.
+ * h_stamps: [n_launches][ctas_per_launch][8] uint64, zero where a CTA did not exist. */
+jsm_status jsm_trace_begin(int max_launches);
+jsm_status jsm_trace_end(uint64_t* h_stamps, int max_launches, int* n_launches, int* ctas_per_launch);
+
 /* ---- RoPE (mat_RoPE_t::init mat_RoPE_t.hpp:99-134, RoPE_net_t::forward :166-188)
  * Table entry for (pair i, position m): (cos A, sin A, cos B, sin B);
  *   out0 = cosA*x0 - sinB*x1 ; out1 = sinA*x0 + cosB*x1.

@@ -74,6 +74,13 @@ SYMBOLS = {
     "jsm_eval_full": (_i, [_i, C.POINTER(Instr), _i, C.POINTER(Mat), _i, Mat, _vp]),
     "jsm_dot_f32": (_i, [Mat, Mat, C.POINTER(Mat), _i, C.POINTER(Mat), Mat, _vp]),
     "jsm_linear_bf16": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "jsm_linear_packed_bytes": (_sz, [_i, _i, _i]),
+    "jsm_linear_packed_plan": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "jsm_trace_begin": (_i, [_i]),
+    "jsm_trace_end": (_i, [_vp, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "jsm_linear_pack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "jsm_linear_unpack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "jsm_linear_bf16_packed": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "jsm_rope_table": (_i, [_vp, _i, _i, _f, _i, _vp]),
     "jsm_rope_apply": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp]),
     "jsm_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
@@ -196,6 +203,31 @@ def linear_bf16(X, W, out, bias=None, epilogue=0, residual=None):
     check(lib().jsm_linear_bf16(X.data_ptr(), W.data_ptr(), bias.data_ptr() if bias is not None else None, epilogue,
                                 residual.data_ptr() if residual is not None else None, out.data_ptr(), dtype_of(out),
                                 T, N, K, stream_ptr()))
+    return out
+
+
+def linear_pack(W, N: int, paired: bool = False):
+    """Packs a row-major bf16 weight matrix ([N, K], or [2N, K] gate rows then up rows when paired) once."""
+    torch = _torch()
+    K = W.shape[1]
+    packed = torch.empty(lib().jsm_linear_packed_bytes(N, K, int(paired)), dtype=torch.uint8, device=W.device)
+    check(lib().jsm_linear_pack(W.data_ptr(), N, K, int(paired), packed.data_ptr(), stream_ptr()))
+    return packed
+
+
+def linear_unpack(packed, N: int, K: int, paired: bool = False):
+    torch = _torch()
+    W = torch.zeros((2 * N if paired else N), K, dtype=torch.bfloat16, device=packed.device)
+    check(lib().jsm_linear_unpack(packed.data_ptr(), N, K, int(paired), W.data_ptr(), stream_ptr()))
+    return W
+
+
+def linear_bf16_packed(X, packed, out, bias=None, epilogue=0, residual=None):
+    T, K = X.shape
+    N = out.shape[1]
+    check(lib().jsm_linear_bf16_packed(X.data_ptr(), packed.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       epilogue, residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                       dtype_of(out), T, N, K, stream_ptr()))
     return out
 
 

@@ -24,6 +24,45 @@ struct LinearArgs {
 };
 
 jsm_status linear_bf16_launch(const LinearArgs& a, cudaStream_t st);
+
+// ---- projections over packed weights (linear_packed.cu) ----
+struct PackedArgs {
+    const void* X;            // [T, K] bf16, row pitch x_row_stride elements (0 = K)
+    const void* Wp;           // packed weights (linear_pack_launch)
+    const float* bias;        // [N] or null (16-byte aligned)
+    int epilogue;             // LIN_*; LIN_SILU_MUL = weights packed as gate/up pairs, N = gate features
+    const void* R;            // [T, N] bf16 residual or null
+    void* Y;                  // [T, N] bf16 or f32
+    bool out_f32 = false;
+    int T = 0, N = 0, K = 0;  // T <= 256 per launch
+    long long x_row_stride = 0;
+    float* ws = nullptr;      // fp32 partials of the tiles shared between CTAs (linear_packed_ws_floats)
+    size_t ws_floats = 0;
+    int* counters = nullptr;  // one per tile, zero before the first launch (the kernel leaves them zero)
+    int n_counters = 0;
+    bool chained = false;     // link of a kernel chain: W may be fetched before the predecessor kernel ends
+};
+// Row of the logical (stacked) weight matrix that packed row r of tile j holds; -1 = padding.
+// plain : rows j*128 .. j*128+127 of an [N, K] matrix.
+// paired: the matrix is [2*N, K] = N gate rows then N up rows; tile j holds gate rows j*64..+63 in its first 64
+//         packed rows and the matching up rows in its last 64, so that silu(gate)*up needs one tile only.
+__host__ __device__ inline long long pk_source_row(int paired, int N, int j, int r) {
+    if (!paired) {
+        const long long row = (long long)j * 128 + r;
+        return row < N ? row : -1;
+    }
+    const long long f = (long long)j * 64 + (r & 63);
+    if (f >= N) return -1;
+    return r < 64 ? f : (long long)N + f;
+}
+
+size_t linear_packed_bytes(int N, int K, int paired);
+size_t linear_packed_ws_floats(int T, int N, int K, int paired);
+// packs (or, with unpack, rebuilds) a row-major [N, K] matrix ([2N, K] gate rows then up rows when paired)
+jsm_status linear_pack_launch(const void* W, int N, int K, int paired, void* packed, bool unpack, cudaStream_t st);
+jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st);
+// dimensions of the packed image
+void pk_dims(int N, int K, int paired, int* n_tiles, int* kbt);
 // reads (and clears) the device error word of the tensor-core kernels; synchronises the stream
 jsm_status tc_check_error(cudaStream_t st, const char* who);
 

@@ -1,0 +1,659 @@
+// bf16 projections over PACKED weights: Y[t,n] = sum_k X[t,k] * W[n,k] with fp32 accumulation, the device form of
+// weight_net_t::forward (mat_net_t.hpp:38-49, Y = W.X + b with W stored [out, in]) for weights that stay constant
+// between calls (inference).
+//
+// Why a packed layout.  A [out, in] row-major weight matrix read in 128 x 64 tiles touches 128 different rows per
+// tile, 128 bytes each, 2*K bytes apart: every DRAM page is opened for 128 bytes.  Packed once at load time, a tile
+// (128 output features x 64 k, 16 KB) is ONE contiguous block that already has the shared-memory image the tensor
+// core wants (128-byte swizzle), the k-blocks of a tile follow each other, and the tiles follow each other.  The whole
+// matrix is then a single linear stream and a CTA's share of it is one contiguous byte range fetched with plain bulk
+// copies (cp.async.bulk), 16 KB per request.
+//
+// Work split ("stream-K").  The matrix is n_tiles * kbt units (tile, k-block) in stream order; CTA c of G owns units
+// [c*U/G, (c+1)*U/G).  A CTA therefore finishes the tail of one tile, possibly some whole tiles, and the head of
+// another.  Whole tiles are written straight from the accumulator; a tile shared by several CTAs is reduced through
+// fp32 partials in a workspace: every contributor stores its partial in its own slot, the one that arrives last
+// (a counter per tile) adds the slots in slot order, so the sum does not depend on the arrival order, and runs the
+// epilogue.  All SMs stream the same number of bytes whatever the shape.
+//
+// Kernel roles (192 threads): warp 0 producer (bulk copies of W, TMA tiles of X), warp 1 MMA issuer
+// (tcgen05.mma 128 x BN x 16, accumulators in TMEM, two accumulator buffers so that the epilogue of one segment
+// overlaps the MMAs of the next), warps 2-5 epilogue (tcgen05.ld, one TMEM lane = one packed row per thread).
+// Chained launches: the W stream does not depend on the predecessor kernel, so the first ring of W tiles is
+// requested (and more is prefetched into L2) before griddepcontrol.wait; X, R, Y and the workspace come after it.
+#include "tc_utils.cuh"
+#include "linear_bf16.cuh"
+#include <math.h>
+#include <mutex>
+
+namespace jsm {
+
+using namespace tc;
+
+constexpr int PK_TILE_BYTES = 128 * 64 * 2;  // one packed unit: 128 rows x 64 k, bf16
+constexpr int PK_THREADS = 192;
+constexpr int PK_MAX_STAGES = 12;
+
+__device__ __forceinline__ float pk_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float pk_silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// 1-D bulk copy global -> shared (this CTA), completion counted in bytes on `bar`; both addresses 16-byte aligned
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes) : "memory");
+}
+
+struct PkParams {
+    int T, N, K;          // tokens (<= BN), output features (paired: gate features), reduction length
+    int n_tiles, kbt;     // tiles of 128 packed rows, k-blocks of 64 per tile
+    int paired;           // epilogue silu(gate) * up over a paired tile
+    int epilogue;         // LIN_* (LIN_SILU_MUL exactly when paired)
+    int out_f32;
+    const float* bias;
+    const __nv_bfloat16* R;
+    void* Y;
+    const uint8_t* Wp;
+    float* ws;            // [n_tiles][max_slots][T][128] fp32 partials
+    int* counters;        // [n_tiles], zero between launches
+    int max_slots;
+    int* err;
+    int w_early;          // weights may be fetched before the predecessor kernel has finished
+    int pf_units;         // units beyond the ring that are prefetched into L2 up front
+    int stages;
+    unsigned long long* trace;  // optional timeline: 8 time stamps (globaltimer, ns) per CTA of this launch
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PK_TRACE(slot)                                                              \
+    do {                                                                            \
+        if (P.trace) P.trace[(size_t)blockIdx.x * 8 + (slot)] = global_ns();        \
+    } while (0)
+
+// unit range of CTA c: [c*U/G, (c+1)*U/G)
+__host__ __device__ inline long long pk_begin(long long c, long long U, long long G) { return c * U / G; }
+// CTA that owns unit u: the largest c with c*U/G <= u
+__host__ __device__ inline int pk_owner(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
+
+template <int BN>
+__global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
+    linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, PkParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int B_BYTES = BN * 128;  // BN tokens x 64 k, bf16
+    constexpr int STAGE_BYTES = PK_TILE_BYTES + B_BYTES;
+    constexpr int TMEM_NEED = 2 * BN;  // two accumulator buffers
+    constexpr int TMEM_COLS = TMEM_NEED < 32 ? 32 : TMEM_NEED;
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two, at most 512");
+
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) uint64_t full_bar[PK_MAX_STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[PK_MAX_STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_flag;
+    __shared__ int is_last_smem;
+    __shared__ float pair_smem[64 * 17];  // paired epilogue: up values of 16 token columns, padded rows
+
+    chain_trigger();
+    if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = P.stages;
+    const long long U = (long long)P.n_tiles * P.kbt, G = gridDim.x;
+    const long long u_begin = pk_begin(blockIdx.x, U, G), u_end = pk_begin(blockIdx.x + 1, U, G);
+    const int n_it = (int)(u_end - u_begin);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp == 0) {
+        // ---- producer ------------------------------------------------------------------------------------
+        if (lane == 0) {
+            const uint8_t* wsrc = P.Wp + (size_t)u_begin * PK_TILE_BYTES;
+            const int pre = P.w_early ? min(n_it, stages) : 0;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+                bulk_load(tiles + (size_t)i * STAGE_BYTES, wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES, &full_bar[i]);
+            }
+            if (P.w_early) {
+                const int pf_end = min(n_it, pre + P.pf_units);
+                for (int i = pre; i < pf_end; ++i) bulk_prefetch_l2(wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES);
+            }
+            PK_TRACE(1);  // first ring of W requested
+            chain_wait();
+            PK_TRACE(2);  // predecessor complete
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + PK_TILE_BYTES, &tmap_x, (int)((u_begin + i) % P.kbt) * 64, 0, &full_bar[i]);
+            int issued = pre;
+            for (int i = pre; i < n_it; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
+                uint8_t* st = tiles + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                bulk_load(st, wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES, &full_bar[s]);
+                tma_load_2d(st + PK_TILE_BYTES, &tmap_x, (int)((u_begin + i) % P.kbt) * 64, 0, &full_bar[s]);
+                issued = i + 1;
+            }
+            if (abort_flag) {  // let the copies in flight land before the CTA exits (bounded)
+                const long long t_start = clock64();
+                for (int i = max(0, issued - stages); i < issued; ++i)
+                    while (!mbar_try_wait(&full_bar[i % stages], (i / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ------------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(128, BN);
+            bool ok = true;
+            int it = 0, seg = 0;
+            long long u = u_begin;
+            while (u < u_end && ok) {
+                const int kb0 = (int)(u % P.kbt);
+                const int len = (int)min((long long)(P.kbt - kb0), u_end - u);
+                const int buf = seg & 1;
+                if (seg >= 2) {
+                    // the epilogue must have drained this buffer's previous segment
+                    if (!mbar_wait(&acc_empty[buf], ((seg >> 1) - 1) & 1, &abort_flag, P.err, TC_TIMEOUT_MISC)) { ok = false; break; }
+                    tc_fence_after();
+                }
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int j = 0; j < len; ++j, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1;
+                    if (!mbar_wait(&full_bar[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
+                    if (it == 0) PK_TRACE(3);  // first stage landed
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t a_desc = smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = smem_desc_sw128(a_addr + PK_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (j > 0 || k > 0) ? 1u : 0u);
+                    mma_commit(&empty_bar[s]);
+                }
+                if (!ok) break;
+                mma_commit(&acc_full[buf]);
+                u += len;
+                ++seg;
+            }
+            PK_TRACE(4);  // last MMA issued
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own the TMEM lane quadrants warp % 4 ------------------------------------------
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;  // packed row of the tile = TMEM lane
+        const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
+        bool ok = true, waited = false;
+        int seg = 0;
+        long long u = u_begin;
+        while (u < u_end && ok) {
+            const int tile = (int)(u / P.kbt);
+            const int kb0 = (int)(u % P.kbt);
+            const int len = (int)min((long long)(P.kbt - kb0), u_end - u);
+            const int buf = seg & 1;
+            if (!mbar_wait(&acc_full[buf], (seg >> 1) & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
+            tc_fence_after();
+            if (!waited) {
+                chain_wait();  // R, Y, the workspace and the counters belong to the stream's other kernels
+                waited = true;
+            }
+            const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            const bool whole = (len == P.kbt);
+            if (whole) {
+                // ---- the tile is complete in this CTA: epilogue straight from the accumulator
+                if (!P.paired) {
+                    const int n = tile * 128 + row;
+                    const float bias = (P.bias && n < P.N) ? P.bias[n] : 0.0f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (c0 >= P.T) break;
+                        uint32_t r[16];
+                        tmem_ld16(acc_addr + c0, r);
+                        tmem_ld_wait();
+                        if (n < P.N) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = c0 + j;
+                                if (t < P.T) {
+                                    float v = __uint_as_float(r[j]) + bias;
+                                    if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
+                                    else if (P.epilogue == LIN_GELU) v = pk_gelu(v);
+                                    else if (P.epilogue == LIN_RESIDUAL) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
+                                    if (P.out_f32) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
+                                    else reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = __float2bfloat16_rn(v);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    // lanes 0..63 hold gate, lanes 64..127 the matching up rows: hand the up values over through shared memory
+                    const int f = row & 63;
+                    const int n = tile * 64 + f;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (c0 >= P.T) break;
+                        uint32_t r[16];
+                        tmem_ld16(acc_addr + c0, r);
+                        tmem_ld_wait();
+                        if (row >= 64) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) pair_smem[f * 17 + j] = __uint_as_float(r[j]);
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (row < 64 && n < P.N) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int t = c0 + j;
+                                if (t < P.T) {
+                                    const float v = pk_silu(__uint_as_float(r[j])) * pair_smem[f * 17 + j];
+                                    if (P.out_f32) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
+                                    else reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = __float2bfloat16_rn(v);
+                                }
+                            }
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            } else {
+                // ---- shared tile: store the raw partial in this CTA's slot, the last contributor folds
+                const long long uf = (long long)tile * P.kbt;
+                const int c_first = pk_owner(uf, U, G), c_last = pk_owner(uf + P.kbt - 1, U, G);
+                const int n_contrib = c_last - c_first + 1;
+                const int slot = (int)blockIdx.x - c_first;
+                float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * (size_t)P.T * 128;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= P.T) break;
+                    uint32_t r[16];
+                    tmem_ld16(acc_addr + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < P.T) __stcg(wbase + (size_t)(c0 + j) * 128 + row, __uint_as_float(r[j]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the MMA warp may reuse the buffer while the fold runs
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) {
+                    const int old = atomicAdd(&P.counters[tile], 1);
+                    const int last = (old == n_contrib - 1);
+                    if (last) P.counters[tile] = 0;  // ready for the next launch
+                    is_last_smem = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool is_last = is_last_smem != 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // is_last_smem may be rewritten by the next shared tile
+                if (is_last) {
+                    __threadfence();
+                    // A thread owns 4 consecutive output features of every TS-th token; the partials of four tokens are in
+                    // flight at once and the slots are added in slot order.
+                    const int groups = P.paired ? 16 : 32;  // groups of 4 features per tile
+                    const int f4 = (etid % groups) * 4, tsub = etid / groups, TS = 128 / groups;
+                    const int n = (P.paired ? tile * 64 : tile * 128) + f4;
+                    const float* tbase = P.ws + (size_t)tile * P.max_slots * (size_t)P.T * 128;
+                    const size_t slot_stride = (size_t)P.T * 128;
+                    if (n < P.N) {
+                        const float4 bias4 = (P.bias && !P.paired) ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int tb = tsub; tb < P.T; tb += 4 * TS) {
+                            float4 g[4], up[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { g[i] = make_float4(0.f, 0.f, 0.f, 0.f); up[i] = g[i]; }
+#pragma unroll 2
+                            for (int z = 0; z < n_contrib; ++z) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int t = tb + TS * i;
+                                    if (t < P.T) {
+                                        const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
+                                        const float4 a = __ldcg(reinterpret_cast<const float4*>(w));
+                                        g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
+                                        if (P.paired) {
+                                            const float4 c = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                            up[i].x += c.x; up[i].y += c.y; up[i].z += c.z; up[i].w += c.w;
+                                        }
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int t = tb + TS * i;
+                                if (t >= P.T) break;
+                                float v[4] = {g[i].x + bias4.x, g[i].y + bias4.y, g[i].z + bias4.z, g[i].w + bias4.w};
+                                const float uu[4] = {up[i].x, up[i].y, up[i].z, up[i].w};
+                                if (P.epilogue == LIN_RESIDUAL) {
+                                    const uint2 rr = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                                    v[0] += bf16lo(rr.x); v[1] += bf16hi(rr.x); v[2] += bf16lo(rr.y); v[3] += bf16hi(rr.y);
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    if (P.paired) v[j] = pk_silu(v[j]) * uu[j];
+                                    else if (P.epilogue == LIN_RELU) v[j] = fmaxf(v[j], 0.0f);
+                                    else if (P.epilogue == LIN_GELU) v[j] = pk_gelu(v[j]);
+                                }
+                                if (P.out_f32) {
+                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.Y) + (size_t)t * P.N + n) = make_float4(v[0], v[1], v[2], v[3]);
+                                } else {
+                                    uint2 o;
+                                    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+                                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (etid == 0) PK_TRACE(5 + (seg > 1 ? 1 : seg));  // end of the first / of the last segment's epilogue
+            u += len;
+            ++seg;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0) PK_TRACE(7);  // CTA done
+}
+
+// ---- packing ---------------------------------------------------------------------------------------------
+// One thread per 16-byte chunk of the packed image.  Chunk q of a unit sits at row r = q / 8, position cs = q % 8 of
+// the 128-byte row and holds the logical chunk cs ^ (r % 8): the 128-byte swizzle of the shared-memory tile.
+__global__ void __launch_bounds__(256) pack_weights_kernel(const __nv_bfloat16* __restrict__ src, uint8_t* __restrict__ dst, int N, int K,
+                                                           int n_tiles, int kbt, int paired, int unpack) {
+    const long long total = (long long)n_tiles * kbt * 1024;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(idx % 1024);
+        const long long unit = idx / 1024;
+        const int kb = (int)(unit % kbt), j = (int)(unit / kbt);
+        const int r = q >> 3, cs = q & 7, c = cs ^ (r & 7);
+        const long long row = pk_source_row(paired, N, j, r);
+        const int k = kb * 64 + c * 8;
+        uint4* packed = reinterpret_cast<uint4*>(dst) + idx;
+        if (unpack) {  // dst is the packed image here, src the row-major matrix to rebuild
+            if (row >= 0 && k < K) *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(src) + row * K + k) = *packed;
+        } else {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row >= 0 && k < K) v = *reinterpret_cast<const uint4*>(src + row * K + k);
+            *packed = v;
+        }
+    }
+}
+
+void pk_dims(int N, int K, int paired, int* n_tiles, int* kbt) {
+    *n_tiles = paired ? (N + 63) / 64 : (N + 127) / 128;
+    *kbt = (K + 63) / 64;
+}
+
+size_t linear_packed_bytes(int N, int K, int paired) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    return (size_t)nt * kbt * PK_TILE_BYTES;
+}
+
+jsm_status linear_pack_launch(const void* W, int N, int K, int paired, void* packed, bool unpack, cudaStream_t st) {
+    if (!W || !packed) JSM_FAIL(JSM_INVALID_ARG, "linear_pack: null pointer");
+    if (N <= 0 || K <= 0 || K % 8) JSM_FAIL(JSM_UNSUPPORTED, "linear_pack: N %d, K %d (K must be a positive multiple of 8)", N, K);
+    if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15))
+        JSM_FAIL(JSM_INVALID_ARG, "linear_pack: pointers must be 16-byte aligned");
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    const long long total = (long long)nt * kbt * 1024;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 32) blocks = (long long)sm_count() * 32;
+    pack_weights_kernel<<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)W, (uint8_t*)packed, N, K, nt, kbt, paired, unpack ? 1 : 0);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+int linear_packed_grid(int N, int K, int paired) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    const long long U = (long long)nt * kbt;
+    long long G = sm_count();
+    if (U < 4 * G) G = U / 4;  // at least four units per CTA
+    if (G < 1) G = 1;
+    return (int)G;
+}
+
+int linear_packed_slots(int N, int K, int paired) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    const long long U = (long long)nt * kbt, G = linear_packed_grid(N, K, paired);
+    // a tile of kbt units is covered by at most ceil(kbt / floor(U/G)) + 1 consecutive CTA ranges
+    const long long per = U / G > 0 ? U / G : 1;
+    return (int)((kbt + per - 1) / per + 1);
+}
+
+size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    return (size_t)nt * linear_packed_slots(N, K, paired) * (size_t)T * 128;
+}
+
+// ---- optional timeline of the packed projections (a profiling aid; off unless jsm_trace_begin was called) ----------
+static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
+static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
+
+template <int BN>
+static jsm_status launch_packed(const CUtensorMap& mx, PkParams& P, int grid, bool chained, cudaStream_t st) {
+    constexpr int STAGE_BYTES = PK_TILE_BYTES + BN * 128;
+    // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
+    const int budget = (BN <= 64 ? 106 : 200) * 1024;
+    int stages = budget / STAGE_BYTES;
+    if (stages > PK_MAX_STAGES) stages = PK_MAX_STAGES;
+    if (stages < 2) stages = 2;
+    P.stages = stages;
+    P.trace = nullptr;
+    if (g_trace_buf && g_trace_n < g_trace_cap && grid <= g_trace_ctas) {
+        P.trace = g_trace_buf + (size_t)g_trace_n * g_trace_ctas * 8;
+        ++g_trace_n;
+    }
+    const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+    static bool attr_done = false;  // per instantiation
+    if (!attr_done) {
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_done = true;
+    }
+    if (chained) {
+        // L2 prefetch beyond the ring: about 32 MB per launch over all CTAs
+        long long pf = (32ll << 20) / ((long long)PK_TILE_BYTES * grid);
+        P.pf_units = (int)(pf > 128 ? 128 : pf);
+        P.w_early = 1;
+        JSM_CUDA_CHECK(launch_chained(linear_packed_kernel<BN>, dim3(grid), dim3(PK_THREADS), smem, st, mx, P));
+        g_launches.fetch_add(1);
+        return JSM_OK;
+    }
+    P.w_early = 0;
+    P.pf_units = 0;
+    linear_packed_kernel<BN><<<grid, PK_THREADS, smem, st>>>(mx, P);
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
+    if (a.T <= 0 || a.N <= 0) return JSM_OK;
+    if (!a.X || !a.Wp || !a.Y) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: null pointer");
+    if (a.K <= 0 || a.K % 8) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: K (%d) must be a positive multiple of 8", a.K);
+    if (a.N % 4) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: N (%d) must be a multiple of 4", a.N);
+    if (a.T > 256) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: at most 256 tokens per launch (%d)", a.T);
+    if (a.epilogue < LIN_NONE || a.epilogue > LIN_RESIDUAL) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: epilogue %d", a.epilogue);
+    const int paired = a.epilogue == LIN_SILU_MUL ? 1 : 0;
+    if (paired && a.bias) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: the gate/up projection takes no bias");
+    if (a.epilogue == LIN_RESIDUAL && !a.R) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: residual epilogue without R");
+    if (a.bias && (reinterpret_cast<uintptr_t>(a.bias) & 15)) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: bias must be 16-byte aligned");
+    PkParams P;
+    P.T = a.T; P.N = a.N; P.K = a.K;
+    pk_dims(a.N, a.K, paired, &P.n_tiles, &P.kbt);
+    P.paired = paired; P.epilogue = a.epilogue; P.out_f32 = a.out_f32 ? 1 : 0;
+    P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y; P.Wp = (const uint8_t*)a.Wp;
+    const int grid = linear_packed_grid(a.N, a.K, paired);
+    P.max_slots = linear_packed_slots(a.N, a.K, paired);
+    const long long U = (long long)P.n_tiles * P.kbt;
+    const bool shared_tiles = (U % grid) != 0 || ((U / grid) % P.kbt) != 0;
+    if (shared_tiles) {
+        if (!a.ws || !a.counters) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace and counters are required");
+        if (linear_packed_ws_floats(a.T, a.N, a.K, paired) > a.ws_floats)
+            JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace of %zu floats, %zu needed", a.ws_floats,
+                     linear_packed_ws_floats(a.T, a.N, a.K, paired));
+        if (P.n_tiles > a.n_counters) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: %d tile counters, %d needed", a.n_counters, P.n_tiles);
+    }
+    P.ws = a.ws; P.counters = a.counters;
+    P.err = tc_error_word();
+    const int bn = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : a.T <= 128 ? 128 : 256;
+    CUtensorMap mx;
+    jsm_status s = make_tmap_bf16_2d(&mx, a.X, (uint64_t)a.T, (uint64_t)a.K, (uint64_t)(a.x_row_stride > 0 ? a.x_row_stride : a.K), bn, 64);
+    if (s != JSM_OK) return s;
+    switch (bn) {
+        case 16: return launch_packed<16>(mx, P, grid, a.chained, st);
+        case 32: return launch_packed<32>(mx, P, grid, a.chained, st);
+        case 64: return launch_packed<64>(mx, P, grid, a.chained, st);
+        case 128: return launch_packed<128>(mx, P, grid, a.chained, st);
+        default: return launch_packed<256>(mx, P, grid, a.chained, st);
+    }
+}
+
+// ---- per-device workspace of the public entry point -------------------------------------------------------------
+struct PkWorkspace {
+    float* ws = nullptr;
+    size_t ws_floats = 0;
+    int* counters = nullptr;
+    int n_counters = 0;
+};
+static PkWorkspace g_pk_ws[64];
+static std::mutex g_pk_mu;
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" jsm_status jsm_trace_begin(int max_launches) {
+    if (max_launches <= 0 || max_launches > 100000) JSM_FAIL(JSM_INVALID_ARG, "jsm_trace_begin: %d launches", max_launches);
+    if (g_trace_buf) cudaFree(g_trace_buf);
+    g_trace_buf = nullptr;
+    g_trace_ctas = sm_count();
+    const size_t bytes = (size_t)max_launches * g_trace_ctas * 8 * sizeof(unsigned long long);
+    JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&g_trace_buf), bytes));
+    JSM_CUDA_CHECK(cudaMemset(g_trace_buf, 0, bytes));
+    g_trace_cap = max_launches;
+    g_trace_n = 0;
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_trace_end(uint64_t* h_stamps, int max_launches, int* n_launches, int* ctas_per_launch) {
+    if (!n_launches || !ctas_per_launch) JSM_FAIL(JSM_INVALID_ARG, "jsm_trace_end: null argument");
+    JSM_CUDA_CHECK(cudaDeviceSynchronize());
+    const int n = g_trace_n < max_launches ? g_trace_n : max_launches;
+    *n_launches = n;
+    *ctas_per_launch = g_trace_ctas;
+    if (g_trace_buf && h_stamps && n > 0)
+        JSM_CUDA_CHECK(cudaMemcpy(h_stamps, g_trace_buf, (size_t)n * g_trace_ctas * 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    if (g_trace_buf) cudaFree(g_trace_buf);
+    g_trace_buf = nullptr;
+    g_trace_cap = g_trace_n = 0;
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_linear_packed_plan(int N, int K, int paired, int* n_tiles, int* kbt, int* grid, int* max_slots) {
+    if (N <= 0 || K <= 0 || !n_tiles || !kbt || !grid || !max_slots) JSM_FAIL(JSM_INVALID_ARG, "jsm_linear_packed_plan: bad argument");
+    pk_dims(N, K, paired ? 1 : 0, n_tiles, kbt);
+    *grid = linear_packed_grid(N, K, paired ? 1 : 0);
+    *max_slots = linear_packed_slots(N, K, paired ? 1 : 0);
+    return JSM_OK;
+}
+
+extern "C" size_t jsm_linear_packed_bytes(int N, int K, int paired) {
+    if (N <= 0 || K <= 0) return 0;
+    return linear_packed_bytes(N, K, paired ? 1 : 0);
+}
+
+extern "C" jsm_status jsm_linear_pack(const void* d_W, int N, int K, int paired, void* d_packed, void* stream) {
+    return linear_pack_launch(d_W, N, K, paired ? 1 : 0, d_packed, false, as_stream(stream));
+}
+
+extern "C" jsm_status jsm_linear_unpack(const void* d_packed, int N, int K, int paired, void* d_W, void* stream) {
+    return linear_pack_launch(d_W, N, K, paired ? 1 : 0, const_cast<void*>(d_packed), true, as_stream(stream));
+}
+
+extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_packed, const float* d_bias, int epilogue, const void* d_R,
+                                             void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
+    if (out_dtype != JSM_BF16 && out_dtype != JSM_F32) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16_packed: out dtype %d", out_dtype);
+    if (T <= 0 || N <= 0) return JSM_OK;
+    int dev = -1;
+    JSM_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16_packed: device index %d", dev);
+    cudaStream_t st = as_stream(stream);
+    const int paired = epilogue == LIN_SILU_MUL ? 1 : 0;
+    PackedArgs a;
+    a.X = d_X; a.Wp = d_packed; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.out_f32 = out_dtype == JSM_F32;
+    a.N = N; a.K = K; a.x_row_stride = 0; a.chained = false;
+    {
+        // grow-only workspace shared by the calls on this device (they are ordered by their streams' users; two
+        // calls that overlap on the GPU would race on it, like any scratch buffer)
+        std::lock_guard<std::mutex> lock(g_pk_mu);
+        PkWorkspace& w = g_pk_ws[dev];
+        const size_t need = linear_packed_ws_floats(T < 256 ? T : 256, N, K, paired);
+        int nt, kbt;
+        pk_dims(N, K, paired, &nt, &kbt);
+        if (need > w.ws_floats) {
+            JSM_CUDA_CHECK(cudaDeviceSynchronize());
+            if (w.ws) cudaFree(w.ws);
+            w.ws = nullptr; w.ws_floats = 0;
+            JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.ws), need * sizeof(float)));
+            w.ws_floats = need;
+        }
+        if (nt > w.n_counters) {
+            JSM_CUDA_CHECK(cudaDeviceSynchronize());
+            if (w.counters) cudaFree(w.counters);
+            w.counters = nullptr; w.n_counters = 0;
+            const int n = nt < 1024 ? 1024 : nt;
+            JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.counters), n * sizeof(int)));
+            JSM_CUDA_CHECK(cudaMemset(w.counters, 0, n * sizeof(int)));
+            w.n_counters = n;
+        }
+        a.ws = w.ws; a.ws_floats = w.ws_floats; a.counters = w.counters; a.n_counters = w.n_counters;
+    }
+    // more than 256 tokens: token chunks, each streaming the weights once
+    for (int t0 = 0; t0 < T; t0 += 256) {
+        const int tc = T - t0 < 256 ? T - t0 : 256;
+        a.T = tc;
+        a.X = reinterpret_cast<const __nv_bfloat16*>(d_X) + (size_t)t0 * K;
+        a.R = d_R ? reinterpret_cast<const __nv_bfloat16*>(d_R) + (size_t)t0 * N : nullptr;
+        a.Y = a.out_f32 ? static_cast<void*>(reinterpret_cast<float*>(d_Y) + (size_t)t0 * N)
+                        : static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(d_Y) + (size_t)t0 * N);
+        jsm_status s = linear_packed_launch(a, st);
+        if (s != JSM_OK) return s;
+    }
+    return JSM_OK;
+}

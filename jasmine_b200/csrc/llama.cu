@@ -17,16 +17,19 @@
 #include <string.h>
 #include <string>
 #include <vector>
+#include <algorithm>
 
 namespace jsm {
 
+// The projection weights are kept packed (linear_packed.cu: contiguous 16 KB tiles in stream order); the logical
+// matrices are the reference's [out, in] layout (mat_net_t.hpp:25-26).
 struct LayerW {
     float* g1;
-    __nv_bfloat16* wqkv;  // [(Hq_l + 2 Hkv_l) * D, d]
-    __nv_bfloat16* wo;    // [d, Hq_l * D]
+    uint8_t* wqkv;        // packed [(Hq_l + 2 Hkv_l) * D, d]: q rows, k rows, v rows
+    uint8_t* wo;          // packed [d, Hq_l * D]
     float* g2;
-    __nv_bfloat16* wgu;   // [2 * ffn_l, d]: gate rows, then up rows
-    __nv_bfloat16* wdown; // [d, ffn_l]
+    uint8_t* wgu;         // packed pairs of [2 * ffn_l, d]: gate rows, then up rows
+    uint8_t* wdown;       // packed [d, ffn_l]
     __nv_bfloat16* pool;  // KV pages of this layer
 };
 
@@ -34,10 +37,12 @@ struct LayerW {
 
 struct jsm_model {
     jsm_model_config c;
-    int Hq_l, Hkv_l, ffn_l, qkv_dim, pages_per_seq, max_tokens, max_splits;
+    int Hq_l, Hkv_l, ffn_l, qkv_dim, pages_per_seq, max_tokens;
     std::vector<jsm::LayerW> layers;
     __nv_bfloat16* emb = nullptr;
-    __nv_bfloat16* lm_head = nullptr;
+    uint8_t* lm_head = nullptr;  // packed [vocab, d]
+    __nv_bfloat16* unpack_buf = nullptr;  // row-major copy of the weight last asked for (jsm_llama_weight)
+    size_t unpack_elems = 0;
     float* gf = nullptr;
     float* rope = nullptr;
     int32_t* block_table = nullptr;
@@ -48,8 +53,9 @@ struct jsm_model {
     float* partial = nullptr;
     float* logits = nullptr;
     float* dec_scratch = nullptr;
-    size_t ws_floats = 0;        // capacity of `partial`
-    int* counters = nullptr;     // arrival counters of the split-K projections (self-resetting)
+    size_t ws_floats = 0;        // capacity of `partial`: fp32 partials of the tiles that several CTAs share
+    int* counters = nullptr;     // one arrival counter per tile (self-resetting)
+    int n_counters = 0;
     std::vector<void*> allocs;
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
@@ -58,7 +64,41 @@ struct jsm_model {
 
 namespace jsm {
 
-// value (r, c) of a shard = element ((row0 + r) * full_cols + col0 + c) of the full tensor: all TP layouts agree
+// Rows [start, start + rows) of a stacked logical matrix come from rows row0.. of the full tensor with generator key
+// `key`; value (r, c) of a shard = element ((row0 + r) * full_cols + col0 + c) of the full tensor, so that all TP
+// layouts agree.
+struct RowSeg { long long start, rows, row0; uint64_t key; };
+struct FillSpec { RowSeg seg[3]; int n_seg; long long full_cols, col0; float std; };
+
+// generates a weight matrix straight into its packed image (one thread per 16-byte chunk, see pack_weights_kernel)
+__global__ void __launch_bounds__(256) fill_packed_kernel(uint8_t* __restrict__ dst, int N, int K, int n_tiles, int kbt, int paired,
+                                                          FillSpec spec) {
+    const long long total = (long long)n_tiles * kbt * 1024;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int q = (int)(idx % 1024);
+        const long long unit = idx / 1024;
+        const int kb = (int)(unit % kbt), j = (int)(unit / kbt);
+        const int r = q >> 3, cs = q & 7, c = cs ^ (r & 7);
+        const long long row = pk_source_row(paired, N, j, r);
+        const int k = kb * 64 + c * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row >= 0 && k < K) {
+            int sg = 0;
+            while (sg + 1 < spec.n_seg && row >= spec.seg[sg].start + spec.seg[sg].rows) ++sg;
+            const RowSeg& S = spec.seg[sg];
+            const uint64_t base = (uint64_t)((S.row0 + (row - S.start)) * spec.full_cols + spec.col0 + k);
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = rng_value(S.key, base + 2 * e, 0, 0.0f, spec.std), hi = rng_value(S.key, base + 2 * e + 1, 0, 0.0f, spec.std);
+                w[e] = (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+            }
+            v = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        reinterpret_cast<uint4*>(dst)[idx] = v;
+    }
+}
+// row-major fill of a shard (the embedding table, which is gathered and not streamed)
 __global__ void fill_shard_kernel(__nv_bfloat16* dst, long long rows, long long cols, long long full_cols, long long row0,
                                   long long col0, uint64_t key, float std) {
     const long long n = rows * cols;
@@ -155,21 +195,6 @@ __global__ void __launch_bounds__(256) fold_add_norm_kernel(__nv_bfloat16* __res
     }
 }
 
-// out[t,:] = bf16(sum_s partial[s][t][:]) : the rank-local sum that goes into the all-reduce
-__global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partial, int splits, long long split_stride,
-                                                            __nv_bfloat16* __restrict__ out, long long n) {
-    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
-        float4 a = *reinterpret_cast<const float4*>(partial + i);
-        for (int s = 1; s < splits; ++s) {
-            const float4 b = *reinterpret_cast<const float4*>(partial + s * split_stride + i);
-            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-        }
-        uint2 o;
-        o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
-        *reinterpret_cast<uint2*>(out + i) = o;
-    }
-}
-
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n) {
     __shared__ float sv[8];
     __shared__ int si[8];
@@ -219,74 +244,58 @@ static void fill_shard(__nv_bfloat16* dst, long long rows, long long cols, long 
     g_launches.fetch_add(1);
 }
 
-static int pick_splits_raw(int T, int N, int K) {
-    // a weight stream wants about two CTAs per SM in flight; the fp32 partials (written and read once per split)
-    // must stay small next to the weights: splits * T * N * 8 bytes <= a quarter of N * K * 2 bytes
-    const int tiles = ((N + 127) / 128) * ((T + 127) / 128);
-    const int kb = (K + 63) / 64;
-    int s = (2 * sm_count() + tiles / 2) / tiles;
-    const int cap = K / (16 * (T < 1 ? 1 : T));
-    if (s > cap) s = cap;
-    if (s > 16) s = 16;
-    while (s > 1 && kb / s < 2) --s;
-    return s < 1 ? 1 : s;
+// packed image of a stacked [N (or 2N when paired), K] matrix whose row blocks come from up to three tensors
+static void fill_packed(uint8_t* dst, int N, int K, int paired, const FillSpec& spec, cudaStream_t st) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    const long long total = (long long)nt * kbt * 1024;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
+    fill_packed_kernel<<<(unsigned)blocks, 256, 0, st>>>(dst, N, K, nt, kbt, paired, spec);
+    g_launches.fetch_add(1);
 }
 
-// never more splits than the workspace of fp32 partials holds (ld = N, or 2N for the fused gate/up projection)
-static int pick_splits(const jsm_model* m, int T, int N, int K, int ld) {
-    int s = pick_splits_raw(T, N, K);
-    const size_t per_split = (size_t)T * ld;
-    while (s > 1 && (size_t)s * per_split > m->ws_floats) --s;
-    return s;
-}
-
-// Y_partial = X . W^T into the residual stream h, then xn = RMSNorm(h) * gain (gain may be null: no norm)
-static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
-                                        const float* next_gain, cudaStream_t st) {
-    const bool tp = m->c.tp_size > 1;
-    LinearArgs a;
+// One projection over packed weights for any number of tokens: chunks of 256 tokens, each streaming the weights once.
+static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_stride, const uint8_t* Wp, int N, int K, int epilogue,
+                             const __nv_bfloat16* R, void* Y, bool out_f32, int T, cudaStream_t st) {
+    PackedArgs a;
+    a.Wp = Wp; a.bias = nullptr; a.epilogue = epilogue; a.out_f32 = out_f32; a.N = N; a.K = K; a.x_row_stride = x_stride;
+    a.ws = m->partial; a.ws_floats = m->ws_floats; a.counters = m->counters; a.n_counters = m->n_counters;
     a.chained = true;  // the model's weights are constant while its stream runs
-    a.X = X; a.W = W; a.bias = nullptr; a.R = nullptr; a.T = T; a.N = N; a.K = K; a.impl = 0;
-    const int d = m->c.d_model;
-    if (T <= 4) {
-        if (!tp) {
-            a.epilogue = LIN_RESIDUAL; a.R = m->h; a.Y = m->h; a.out_mode = 0; a.splits = 1;
-            jsm_status s = linear_bf16_launch(a, st);
-            if (s != JSM_OK) return s;
-            if (next_gain) {
-                JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d));
-                JSM_LAUNCH_CHECK();
-            }
-            return JSM_OK;
-        }
-        a.epilogue = LIN_NONE; a.Y = m->red; a.out_mode = 0; a.splits = 1;
-        jsm_status s = linear_bf16_launch(a, st);
-        if (s != JSM_OK) return s;
-    } else {
-        // weight stream split along K; the CTA that finishes a tile last folds the partials and writes the result:
-        // straight into the residual stream on one GPU, into the all-reduce buffer under tensor parallelism
-        a.splits = pick_splits(m, T, N, K, N);
-        a.ws = a.splits > 1 ? m->partial : nullptr;
-        a.counters = m->counters;
-        a.out_mode = 0;
-        if (!tp) {
-            a.epilogue = LIN_RESIDUAL; a.R = m->h; a.Y = m->h;
-            jsm_status s = linear_bf16_launch(a, st);
-            if (s != JSM_OK) return s;
-            if (next_gain) {
-                JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain, m->c.norm_eps, m->xn, d));
-                JSM_LAUNCH_CHECK();
-            }
-            return JSM_OK;
-        }
-        a.epilogue = LIN_NONE; a.Y = m->red;
-        jsm_status s = linear_bf16_launch(a, st);
+    for (int t0 = 0; t0 < T; t0 += 256) {
+        a.T = T - t0 < 256 ? T - t0 : 256;
+        a.X = X + (long long)t0 * x_stride;
+        a.R = R ? R + (long long)t0 * N : nullptr;
+        a.Y = out_f32 ? static_cast<void*>(reinterpret_cast<float*>(Y) + (long long)t0 * N)
+                      : static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(Y) + (long long)t0 * N);
+        jsm_status s = linear_packed_launch(a, st);
         if (s != JSM_OK) return s;
     }
+    return JSM_OK;
+}
+
+// h += X . W^T (the residual stream), then xn = RMSNorm(h) * gain (gain may be null: no norm).  On one GPU the
+// projection adds into h in its epilogue; under tensor parallelism the rank-local product goes through the all-reduce.
+static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K,
+                                        const float* next_gain, cudaStream_t st) {
+    const int d = m->c.d_model;
+    if (m->c.tp_size == 1) {
+        jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_RESIDUAL, m->h, m->h, false, T, st);
+        if (s != JSM_OK) return s;
+        if (next_gain) {
+            JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain,
+                                          m->c.norm_eps, m->xn, d));
+            JSM_LAUNCH_CHECK();
+        }
+        return JSM_OK;
+    }
+    jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->red, false, T, st);
+    if (s != JSM_OK) return s;
     // tensor parallel: sum the rank-local outputs, then add into the residual stream
     if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
     if (m->allreduce(m->red, (size_t)T * N, JSM_BF16, st, m->allreduce_user) != 0) JSM_FAIL(JSM_NCCL, "all-reduce callback failed");
-    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, next_gain, m->c.norm_eps, next_gain ? m->xn : nullptr, d));
+    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, next_gain,
+                                  m->c.norm_eps, next_gain ? m->xn : nullptr, d));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -296,19 +305,13 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
     const int d = c.d_model, D = c.head_dim;
     jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
     if (s != JSM_OK) return s;
-    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, m->layers[0].g1, c.norm_eps, m->xn, d));
+    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, m->layers[0].g1,
+                                  c.norm_eps, m->xn, d));
     JSM_LAUNCH_CHECK();
     const float scale = 1.0f / sqrtf((float)D);
     for (int l = 0; l < c.n_layers; ++l) {
         LayerW& L = m->layers[l];
-        LinearArgs a;
-    a.chained = true;  // the model's weights are constant while its stream runs
-        a.X = m->xn; a.W = L.wqkv; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = m->qkv; a.out_mode = 0;
-        a.T = T; a.N = m->qkv_dim; a.K = d; a.impl = 0;
-        a.splits = T > 4 ? pick_splits(m, T, a.N, d, a.N) : 1;
-        a.ws = a.splits > 1 ? m->partial : nullptr;
-        a.counters = m->counters;
-        s = linear_bf16_launch(a, st);
+        s = run_linear(m, m->xn, d, L.wqkv, m->qkv_dim, d, LIN_NONE, nullptr, m->qkv, false, T, st);
         if (s != JSM_OK) return s;
         const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
         const __nv_bfloat16* vv = kk + (long long)m->Hkv_l * D;
@@ -335,10 +338,7 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         if (s != JSM_OK) return s;
         s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, L.g2, st);
         if (s != JSM_OK) return s;
-        a.X = m->xn; a.W = L.wgu; a.epilogue = LIN_SILU_MUL; a.Y = m->act; a.N = m->ffn_l; a.K = d;
-        a.splits = T > 4 ? pick_splits(m, T, a.N, d, 2 * a.N) : 1;
-        a.ws = a.splits > 1 ? m->partial : nullptr;
-        s = linear_bf16_launch(a, st);
+        s = run_linear(m, m->xn, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st);
         if (s != JSM_OK) return s;
         const float* next_gain = (l + 1 < c.n_layers) ? m->layers[l + 1].g1 : m->gf;
         s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, next_gain, st);
@@ -351,11 +351,7 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
 static jsm_status logits_and_argmax(jsm_model* m, const __nv_bfloat16* xn_rows, int rows, int32_t* d_next, float* d_logits,
                                     cudaStream_t st) {
     float* lg = d_logits ? d_logits : m->logits;
-    LinearArgs a;
-    a.chained = true;  // the model's weights are constant while its stream runs
-    a.X = xn_rows; a.W = m->lm_head; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = lg; a.out_mode = 1;
-    a.T = rows; a.N = m->c.vocab; a.K = m->c.d_model; a.splits = 1; a.impl = 0;
-    jsm_status s = linear_bf16_launch(a, st);
+    jsm_status s = run_linear(m, xn_rows, m->c.d_model, m->lm_head, m->c.vocab, m->c.d_model, LIN_NONE, nullptr, lg, true, rows, st);
     if (s != JSM_OK) return s;
     if (d_next) {
         JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
@@ -397,7 +393,6 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     m->qkv_dim = (m->Hq_l + 2 * m->Hkv_l) * D;
     m->pages_per_seq = (c.max_context + JSM_PAGE_SIZE - 1) / JSM_PAGE_SIZE;
     m->max_tokens = c.max_batch > 512 ? c.max_batch : 512;
-    m->max_splits = 16;
     m->layers.resize(c.n_layers);
     cudaStream_t st = nullptr;
     const float std = 0.02f;
@@ -412,34 +407,54 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     const long long n_pages = (long long)c.max_batch * m->pages_per_seq;
     const size_t page_elems = (size_t)2 * m->Hkv_l * JSM_PAGE_SIZE * D;
     uint64_t wbytes = 0;
+    const int qdim = m->Hq_l * D;  // K of the attention output projection
+    auto spec1 = [&](long long rows, long long row0, uint64_t tid, long long full_cols, long long col0) {
+        FillSpec f{};
+        f.n_seg = 1;
+        f.seg[0] = RowSeg{0, rows, row0, rng_key(seed, tid)};
+        f.full_cols = full_cols; f.col0 = col0; f.std = std;
+        return f;
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         LayerW& L = m->layers[l];
         const uint64_t t0 = (uint64_t)l * 16;
         JSM_TRY(dev_alloc(m, &L.g1, (size_t)d));
         JSM_TRY(dev_alloc(m, &L.g2, (size_t)d));
-        JSM_TRY(dev_alloc(m, &L.wqkv, (size_t)m->qkv_dim * d));
-        JSM_TRY(dev_alloc(m, &L.wo, (size_t)d * m->Hq_l * D));
-        JSM_TRY(dev_alloc(m, &L.wgu, (size_t)2 * m->ffn_l * d));
-        JSM_TRY(dev_alloc(m, &L.wdown, (size_t)d * m->ffn_l));
+        JSM_TRY(dev_alloc(m, &L.wqkv, linear_packed_bytes(m->qkv_dim, d, 0)));
+        JSM_TRY(dev_alloc(m, &L.wo, linear_packed_bytes(d, qdim, 0)));
+        JSM_TRY(dev_alloc(m, &L.wgu, linear_packed_bytes(m->ffn_l, d, 1)));
+        JSM_TRY(dev_alloc(m, &L.wdown, linear_packed_bytes(d, m->ffn_l, 0)));
         JSM_TRY(dev_alloc(m, &L.pool, (size_t)n_pages * page_elems));
         fill_const_kernel<<<16, 256, 0, st>>>(L.g1, d, 1.0f);
         fill_const_kernel<<<16, 256, 0, st>>>(L.g2, d, 1.0f);
         // full tensors: wq [Hq*D, d] (id +0), wk [Hkv*D, d] (+1), wv (+2), wo [d, Hq*D] (+3), wgate [ffn, d] (+4), wup (+5), wdown [d, ffn] (+6)
         const long long qr = (long long)m->Hq_l * D, kr = (long long)m->Hkv_l * D;
-        fill_shard(L.wqkv, qr, d, d, c.tp_rank * qr, 0, seed, t0 + 0, std, st);
-        fill_shard(L.wqkv + qr * d, kr, d, d, c.tp_rank * kr, 0, seed, t0 + 1, std, st);
-        fill_shard(L.wqkv + (qr + kr) * d, kr, d, d, c.tp_rank * kr, 0, seed, t0 + 2, std, st);
-        fill_shard(L.wo, d, qr, (long long)c.n_heads * D, 0, c.tp_rank * qr, seed, t0 + 3, std, st);
-        fill_shard(L.wgu, m->ffn_l, d, d, (long long)c.tp_rank * m->ffn_l, 0, seed, t0 + 4, std, st);
-        fill_shard(L.wgu + (long long)m->ffn_l * d, m->ffn_l, d, d, (long long)c.tp_rank * m->ffn_l, 0, seed, t0 + 5, std, st);
-        fill_shard(L.wdown, d, m->ffn_l, c.d_ffn, 0, (long long)c.tp_rank * m->ffn_l, seed, t0 + 6, std, st);
-        wbytes += 2ull * ((uint64_t)m->qkv_dim * d + (uint64_t)d * m->Hq_l * D + 2ull * m->ffn_l * d + (uint64_t)d * m->ffn_l) + 8ull * d;
+        {
+            FillSpec f{};
+            f.n_seg = 3;
+            f.seg[0] = RowSeg{0, qr, c.tp_rank * qr, rng_key(seed, t0 + 0)};
+            f.seg[1] = RowSeg{qr, kr, c.tp_rank * kr, rng_key(seed, t0 + 1)};
+            f.seg[2] = RowSeg{qr + kr, kr, c.tp_rank * kr, rng_key(seed, t0 + 2)};
+            f.full_cols = d; f.col0 = 0; f.std = std;
+            fill_packed(L.wqkv, m->qkv_dim, d, 0, f, st);
+        }
+        fill_packed(L.wo, d, qdim, 0, spec1(d, 0, t0 + 3, (long long)c.n_heads * D, c.tp_rank * qr), st);
+        {
+            FillSpec f{};
+            f.n_seg = 2;
+            f.seg[0] = RowSeg{0, m->ffn_l, (long long)c.tp_rank * m->ffn_l, rng_key(seed, t0 + 4)};
+            f.seg[1] = RowSeg{m->ffn_l, m->ffn_l, (long long)c.tp_rank * m->ffn_l, rng_key(seed, t0 + 5)};
+            f.full_cols = d; f.col0 = 0; f.std = std;
+            fill_packed(L.wgu, m->ffn_l, d, 1, f, st);
+        }
+        fill_packed(L.wdown, d, m->ffn_l, 0, spec1(d, 0, t0 + 6, c.d_ffn, (long long)c.tp_rank * m->ffn_l), st);
+        wbytes += 2ull * ((uint64_t)m->qkv_dim * d + (uint64_t)d * qdim + 2ull * m->ffn_l * d + (uint64_t)d * m->ffn_l) + 8ull * d;
     }
     JSM_TRY(dev_alloc(m, &m->emb, (size_t)c.vocab * d));
-    JSM_TRY(dev_alloc(m, &m->lm_head, (size_t)c.vocab * d));
+    JSM_TRY(dev_alloc(m, &m->lm_head, linear_packed_bytes(c.vocab, d, 0)));
     JSM_TRY(dev_alloc(m, &m->gf, (size_t)d));
     fill_shard(m->emb, c.vocab, d, d, 0, 0, seed, 1000000, std, st);
-    fill_shard(m->lm_head, c.vocab, d, d, 0, 0, seed, 1000001, std, st);
+    fill_packed(m->lm_head, c.vocab, d, 0, spec1(c.vocab, 0, 1000001, d, 0), st);
     fill_const_kernel<<<16, 256, 0, st>>>(m->gf, d, 1.0f);
     wbytes += 2ull * (uint64_t)c.vocab * d + 4ull * d;
     m->weight_bytes = wbytes;
@@ -462,11 +477,19 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->qkv, Tm * m->qkv_dim));
     JSM_TRY(dev_alloc(m, &m->attn, Tm * m->Hq_l * D));
     JSM_TRY(dev_alloc(m, &m->act, Tm * m->ffn_l));
-    m->ws_floats = (size_t)m->max_splits * Tm * d;
-    JSM_TRY(dev_alloc(m, &m->partial, m->ws_floats));
-    JSM_TRY(dev_alloc(m, &m->counters, (size_t)8192));
     {
-        cudaError_t e0 = cudaMemset(m->counters, 0, 8192 * sizeof(int));
+        // fp32 partials of the tiles that several CTAs share: the largest need over the model's projections
+        const int Tc = m->max_tokens < 256 ? m->max_tokens : 256;
+        size_t need = linear_packed_ws_floats(Tc, m->qkv_dim, d, 0);
+        need = std::max(need, linear_packed_ws_floats(Tc, d, qdim, 0));
+        need = std::max(need, linear_packed_ws_floats(Tc, m->ffn_l, d, 1));
+        need = std::max(need, linear_packed_ws_floats(Tc, d, m->ffn_l, 0));
+        need = std::max(need, linear_packed_ws_floats(Tc, c.vocab, d, 0));
+        m->ws_floats = need;
+        JSM_TRY(dev_alloc(m, &m->partial, m->ws_floats));
+        m->n_counters = std::max(1024, std::max((c.vocab + 127) / 128, (m->ffn_l + 63) / 64) + 1);
+        JSM_TRY(dev_alloc(m, &m->counters, (size_t)m->n_counters));
+        cudaError_t e0 = cudaMemset(m->counters, 0, m->n_counters * sizeof(int));
         if (e0 != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: %s", cudaGetErrorString(e0)); }
     }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
@@ -483,6 +506,7 @@ jsm_status jsm_llama_destroy(jsm_model* m) {
     if (!m) return JSM_OK;
     cudaDeviceSynchronize();
     for (void* p : m->allocs) cudaFree(p);
+    if (m->unpack_buf) cudaFree(m->unpack_buf);
     delete m;
     return JSM_OK;
 }
@@ -499,21 +523,39 @@ jsm_status jsm_llama_weight(jsm_model* m, const char* name, void** d_ptr, size_t
     const int d = m->c.d_model, D = m->c.head_dim;
     std::string s(name);
     if (s == "emb") { *d_ptr = m->emb; *n_elems = (size_t)m->c.vocab * d; return JSM_OK; }
-    if (s == "lm_head") { *d_ptr = m->lm_head; *n_elems = (size_t)m->c.vocab * d; return JSM_OK; }
     if (s == "gf") { *d_ptr = m->gf; *n_elems = d; return JSM_OK; }
+    // projection weights live packed: the row-major [out, in] matrix is rebuilt into a buffer of the model that the
+    // next call overwrites
+    const uint8_t* packed = nullptr;
+    int N = 0, K = 0, paired = 0;
+    if (s == "lm_head") { packed = m->lm_head; N = m->c.vocab; K = d; }
     int l = -1;
     char field[32] = "";
-    if (sscanf(name, "layers.%d.%31s", &l, field) == 2 && l >= 0 && l < m->c.n_layers) {
+    if (!packed && sscanf(name, "layers.%d.%31s", &l, field) == 2 && l >= 0 && l < m->c.n_layers) {
         LayerW& L = m->layers[l];
         std::string f(field);
         if (f == "g1") { *d_ptr = L.g1; *n_elems = d; return JSM_OK; }
         if (f == "g2") { *d_ptr = L.g2; *n_elems = d; return JSM_OK; }
-        if (f == "wqkv") { *d_ptr = L.wqkv; *n_elems = (size_t)m->qkv_dim * d; return JSM_OK; }
-        if (f == "wo") { *d_ptr = L.wo; *n_elems = (size_t)d * m->Hq_l * D; return JSM_OK; }
-        if (f == "wgu") { *d_ptr = L.wgu; *n_elems = (size_t)2 * m->ffn_l * d; return JSM_OK; }
-        if (f == "wdown") { *d_ptr = L.wdown; *n_elems = (size_t)d * m->ffn_l; return JSM_OK; }
+        if (f == "wqkv") { packed = L.wqkv; N = m->qkv_dim; K = d; }
+        else if (f == "wo") { packed = L.wo; N = d; K = m->Hq_l * D; }
+        else if (f == "wgu") { packed = L.wgu; N = m->ffn_l; K = d; paired = 1; }
+        else if (f == "wdown") { packed = L.wdown; N = d; K = m->ffn_l; }
     }
-    JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_weight: unknown tensor '%s'", name);
+    if (!packed) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_weight: unknown tensor '%s'", name);
+    const size_t elems = (size_t)(paired ? 2 * N : N) * K;
+    if (elems > m->unpack_elems) {
+        JSM_CUDA_CHECK(cudaDeviceSynchronize());
+        if (m->unpack_buf) cudaFree(m->unpack_buf);
+        m->unpack_buf = nullptr; m->unpack_elems = 0;
+        JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&m->unpack_buf), elems * sizeof(__nv_bfloat16)));
+        m->unpack_elems = elems;
+    }
+    jsm_status st = linear_pack_launch(m->unpack_buf, N, K, paired, const_cast<uint8_t*>(packed), true, nullptr);
+    if (st != JSM_OK) return st;
+    JSM_CUDA_CHECK(cudaDeviceSynchronize());
+    *d_ptr = m->unpack_buf;
+    *n_elems = elems;
+    return JSM_OK;
 }
 
 jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T, int32_t* d_next, float* d_logits_last, void* stream) {

@@ -89,3 +89,27 @@ def test_no_cpu_fallback_without_a_device():
     assert L.jsm_llama_create(C.byref(cfg), 0, C.byref(h)) == jb.CUDA
     p = C.c_void_p()
     assert L.jsm_malloc(C.byref(p), 1024) in (jb.CUDA, jb.OOM)
+
+
+@pytest.mark.parametrize("N,K,paired", [(4096, 4096, 0), (12288, 4096, 0), (11008, 4096, 1), (4096, 11008, 0), (32000, 4096, 0),
+                                        (1376, 4096, 1), (4096, 1376, 0), (256, 512, 0), (1000, 1000, 0), (384, 64, 0),
+                                        (704, 1024, 1), (4096, 512, 0)])
+def test_packed_projection_work_split_is_consistent(N, K, paired):
+    """The stream-K split of a packed projection, checked on the host: the CTA ranges tile the unit space, the owner
+    formula inverts the range formula (it decides which workspace slot a CTA writes), and no tile has more
+    contributors than the workspace has slots."""
+    nt, kbt, G, slots = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    assert jb.lib().jsm_linear_packed_plan(N, K, paired, C.byref(nt), C.byref(kbt), C.byref(G), C.byref(slots)) == jb.OK
+    nt, kbt, G, slots = nt.value, kbt.value, G.value, slots.value
+    assert nt == (-(-N // 64) if paired else -(-N // 128)) and kbt == -(-K // 64)
+    U = nt * kbt
+    assert 1 <= G <= 148 or G == U // 4
+    begin = [c * U // G for c in range(G + 1)]
+    assert begin[0] == 0 and begin[G] == U and all(b1 > b0 for b0, b1 in zip(begin, begin[1:]))
+    owner = lambda u: ((u + 1) * G + U - 1) // U - 1
+    for c in range(G):
+        assert owner(begin[c]) == c and owner(begin[c + 1] - 1) == c
+    for tile in range(nt):
+        first, last = owner(tile * kbt), owner(tile * kbt + kbt - 1)
+        assert 1 <= last - first + 1 <= slots
+    assert jb.lib().jsm_linear_packed_bytes(N, K, paired) == U * 16384

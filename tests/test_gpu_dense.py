@@ -106,6 +106,57 @@ def test_linear_bf16_epilogues(T):
     assert_close(host(Y), host(torch.nn.functional.silu(gate) * up), 3e-3, "silu(gate)*up")
 
 
+# ---- packed weights: one linear stream split evenly over the SMs (stream-K), shared tiles folded in slot order ----
+PACKED_SHAPES = [(1, 256, 512), (8, 4096, 4096), (8, 12288, 4096), (5, 1000, 1000), (16, 384, 64), (17, 512, 1024),
+                 (64, 4096, 11008), (64, 1376, 4096), (100, 1024, 1376), (128, 256, 256), (200, 640, 1024), (256, 4096, 512),
+                 (300, 384, 512), (512, 256, 2048), (2, 32000, 512)]
+
+
+@pytest.mark.parametrize("T,N,K", PACKED_SHAPES)
+def test_linear_packed(T, N, K):
+    X, W = make_xw(T, N, K, 140 + T)
+    Wp = jb.linear_pack(W, N)
+    assert torch.equal(jb.linear_unpack(Wp, N, K), W), "pack / unpack round trip"
+    want = host(ref_linear(X, W))
+    Y = torch.empty(T, N, device="cuda", dtype=torch.float32)
+    jb.linear_bf16_packed(X, Wp, Y)
+    jb.check_device_errors()
+    assert_close(host(Y), want, 2e-3, f"packed T={T} N={N} K={K}")
+    # the fold of shared tiles is ordered: a second run gives the same bits
+    Y2 = torch.empty_like(Y)
+    jb.linear_bf16_packed(X, Wp, Y2)
+    assert torch.equal(Y, Y2)
+    Yb = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    jb.linear_bf16_packed(X, Wp, Yb)
+    assert_close(host(Yb), want, BF16_RTOL, "bf16 output")
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (8, 11008, 4096), (32, 1376, 512), (64, 704, 1024), (130, 320, 256)])
+def test_linear_packed_epilogues(T, N, K):
+    X, W = make_xw(T, N, K, 160 + T, rows=2 * N)
+    bias = torch.empty(N, device="cuda"); jb.fill(bias, 161, 2, 0, 0.0, 0.5)
+    R = torch.empty(T, N, device="cuda", dtype=torch.bfloat16); jb.fill(R, 161, 3, 0, 0.0, 1.0)
+    Y = torch.empty(T, N, device="cuda", dtype=torch.float32)
+    Wp = jb.linear_pack(W[:N].contiguous(), N)
+    base = ref_linear(X, W[:N], bias)
+    jb.linear_bf16_packed(X, Wp, Y, bias=bias, epilogue=1)
+    assert_close(host(Y), host(torch.relu(base)), 2e-3, "relu")
+    jb.linear_bf16_packed(X, Wp, Y, bias=bias, epilogue=2)
+    assert_close(host(Y), host(torch.nn.functional.gelu(base)), 2e-3, "gelu")
+    jb.linear_bf16_packed(X, Wp, Y, bias=bias, epilogue=4, residual=R)
+    assert_close(host(Y), host(base + R.float()), 2e-3, "residual")
+    # in place on the residual stream, as the decoder uses it
+    H = R.clone()
+    jb.linear_bf16_packed(X, Wp, H, epilogue=4, residual=H)
+    assert_close(host(H), host(ref_linear(X, W[:N]) + R.float()), BF16_RTOL, "residual in place")
+    Wpair = jb.linear_pack(W, N, paired=True)
+    assert torch.equal(jb.linear_unpack(Wpair, N, K, paired=True), W), "paired pack / unpack round trip"
+    jb.linear_bf16_packed(X, Wpair, Y, epilogue=3)
+    gate, up = ref_linear(X, W[:N]), ref_linear(X, W[N:])
+    assert_close(host(Y), host(torch.nn.functional.silu(gate) * up), 3e-3, "silu(gate)*up")
+    jb.check_device_errors()
+
+
 def test_linear_matches_oracle_on_small_case():
     """The bf16 projection against the CPU oracle's weight_net_t restatement on bf16-rounded inputs."""
     T, N, K = 6, 128, 256

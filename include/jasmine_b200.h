@@ -243,6 +243,18 @@ jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_
                            int n_seqs, int Hq, int Hkv, int D, float scale, const float* d_rope_table,
                            int max_context, void* d_scratch, void* d_out, void* stream);
 
+/* The decode step of one layer in a single launch: appends the new token of every sequence (d_k_new, d_v_new:
+ * [n_seqs, ...] rows with pitch kv_new_stride, head h at column h*D; K is rotated with the rope row of its position
+ * context_len-1 when a table is given) to the cache and attends over the context including it; the chunk partials are
+ * merged by the last CTA of each (sequence, kv head), in chunk order.  d_context_lens already counts the new token.
+ * d_counters: I32 [n_seqs * Hkv], zero before the first call; the kernel leaves them zero.  d_k_new may be NULL
+ * (nothing to append).  Replaces jsm_kv_append + jsm_attn_decode; same arithmetic. */
+jsm_status jsm_attn_decode_append(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
+                                  int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
+                                  const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                  const float* d_rope_table, int max_context, void* d_scratch, int32_t* d_counters,
+                                  void* d_out, void* stream);
+
 /* Decode attention for hosts that must not allocate.
  * No counterpart in the reference (it has neither a KV cache nor device memory).
  * Same arithmetic and arguments as jsm_attn_decode, but the per-chunk partial results live in a

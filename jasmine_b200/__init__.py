@@ -87,6 +87,7 @@ SYMBOLS = {
     "jsm_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "jsm_attn_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "jsm_attn_decode": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp]),
+    "jsm_attn_decode_append": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp]),
     "jsm_attn_decode_static_scratch": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp]),
     "jsm_embedding": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "jsm_add_norm": (_i, [_i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _f, _i, _i, _vp]),
@@ -277,6 +278,25 @@ def attn_decode(q, pool, block_table, context_lens, Hq, Hkv, D, max_context, sca
                                 block_table.shape[1], context_lens.data_ptr(), n, Hq, Hkv, D, scale,
                                 rope.data_ptr() if rope is not None else None, max_context, scratch.data_ptr(),
                                 out.data_ptr(), stream_ptr()))
+    return out
+
+
+def attn_decode_append(q, k_new, v_new, pool, block_table, context_lens, Hq, Hkv, D, max_context, counters, scale=None,
+                       rope=None, scratch=None, out=None):
+    """jsm_attn_decode_append: append the new token of every sequence and attend, one launch."""
+    torch = _torch()
+    n = q.shape[0]
+    out = torch.empty(n, Hq * D, dtype=q.dtype, device=q.device) if out is None else out
+    if scratch is None:
+        nbytes = lib().jsm_attn_decode_scratch_bytes(n, Hq, D, max_context)
+        scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+    scale = float(D) ** -0.5 if scale is None else scale
+    check(lib().jsm_attn_decode_append(q.data_ptr(), q.stride(0), k_new.data_ptr() if k_new is not None else None,
+                                       v_new.data_ptr() if v_new is not None else None,
+                                       k_new.stride(0) if k_new is not None else 0, pool.data_ptr(), block_table.data_ptr(),
+                                       block_table.shape[1], context_lens.data_ptr(), n, Hq, Hkv, D, scale,
+                                       rope.data_ptr() if rope is not None else None, max_context, scratch.data_ptr(),
+                                       counters.data_ptr(), out.data_ptr(), stream_ptr()))
     return out
 
 

@@ -69,11 +69,17 @@ __global__ void __launch_bounds__(128) kv_append_kernel(__nv_bfloat16* __restric
 
 // ---- decode: one partial per (sequence, kv head, chunk) -------------------------------
 // scratch: [n_seqs][Hq][n_chunks][D + 2] floats: o[D] (unnormalised), m (log2 domain), l
-template <int G>
+// FUSED: the kernel also (a) appends the new token's K (rotated) and V of this (sequence, kv head) to the cache - the
+// CTA whose chunk holds position ctx-1 writes them before it reads its chunk - and (b) merges the chunk partials
+// itself: the CTA that arrives last at the (sequence, kv head) counter combines them and writes the output, so that a
+// decode step needs one attention launch instead of three.
+template <int G, bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
-    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ pool,
+    const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ pool,
     const int32_t* __restrict__ block_table, int max_pages, const int32_t* __restrict__ context_lens, int Hq, int Hkv,
-    float scale_log2, const float4* __restrict__ rope, int n_chunks, int chunk_len, float* __restrict__ scratch) {
+    float scale_log2, const float4* __restrict__ rope, int n_chunks, int chunk_len, float* __restrict__ scratch,
+    const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new, long long kv_new_stride,
+    int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     constexpr int D = 128;
     chain_trigger();
     chain_wait();
@@ -83,6 +89,24 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     if (c_begin >= ctx) return;
     const int c_end = min(ctx, c_begin + chunk_len);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (FUSED && k_new && ctx - 1 >= c_begin) {  // ctx - 1 < c_end always: this CTA owns the newest position
+        const int pos = ctx - 1;
+        if (threadIdx.x < D / 2) {
+            const int pr = threadIdx.x;
+            const int page = block_table[(long long)seq * max_pages + pos / JSM_PAGE_SIZE];
+            __nv_bfloat16* kdst = pool + page * (2ll * Hkv * JSM_PAGE_SIZE * D) + ((long long)hk * JSM_PAGE_SIZE + pos % JSM_PAGE_SIZE) * D;
+            __nv_bfloat16* vdst = kdst + (long long)Hkv * JSM_PAGE_SIZE * D;
+            uint32_t kw = *reinterpret_cast<const uint32_t*>(k_new + seq * kv_new_stride + (long long)hk * D + 2 * pr);
+            if (rope) {
+                const float4 e = rope[(long long)pos * (D / 2) + pr];
+                const float x0 = bf16lo(kw), x1 = bf16hi(kw);
+                kw = pack_bf16x2(__fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1)), __fadd_rn(__fmul_rn(e.y, x0), __fmul_rn(e.z, x1)));
+            }
+            *reinterpret_cast<uint32_t*>(kdst + 2 * pr) = kw;
+            *reinterpret_cast<uint32_t*>(vdst + 2 * pr) = *reinterpret_cast<const uint32_t*>(v_new + seq * kv_new_stride + (long long)hk * D + 2 * pr);
+        }
+        __syncthreads();  // the chunk loop below reads what was just written
+    }
     const int ks = lane >> 4;          // which of the two keys of a warp load
     const int dsub = (lane & 15) * 8;  // this lane's 8 dims
 
@@ -220,8 +244,41 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
             L += f * sm_l[w][g];
         }
         float* dst = scratch + (((long long)seq * Hq + hk * G + g) * n_chunks + chunk) * (D + 2);
-        dst[d] = o;
-        if (d == 0) { dst[D] = M; dst[D + 1] = L; }
+        if (FUSED && ctx <= chunk_len) {
+            // a single chunk: this is the result
+            out[((long long)seq * Hq + hk * G + g) * D + d] = __float2bfloat16_rn(o / L);
+        } else {
+            dst[d] = o;
+            if (d == 0) { dst[D] = M; dst[D + 1] = L; }
+        }
+    }
+    if (!FUSED || ctx <= chunk_len) return;
+    // ---- the last CTA of this (sequence, kv head) merges the chunk partials
+    __shared__ int is_last;
+    __syncthreads();  // all partial stores of the CTA precede the release below
+    if (threadIdx.x == 0) {
+        const int n_valid = (ctx + chunk_len - 1) / chunk_len;
+        int old;
+        int* ctr = counters + (long long)seq * Hkv + hk;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
+        is_last = (old == n_valid - 1);
+        if (is_last) *ctr = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    const int n = (ctx + chunk_len - 1) / chunk_len;
+    for (int e = threadIdx.x; e < G * D; e += DEC_WARPS * 32) {
+        const int g = e / D, d = e % D;
+        const float* src = scratch + ((long long)seq * Hq + hk * G + g) * n_chunks * (D + 2);
+        float M = -INFINITY;
+        for (int c = 0; c < n; ++c) M = fmaxf(M, __ldcg(src + c * (D + 2) + D));
+        float o = 0.0f, L = 0.0f;
+        for (int c = 0; c < n; ++c) {
+            const float f = exp2f(__ldcg(src + c * (D + 2) + D) - M);
+            o += f * __ldcg(src + c * (D + 2) + d);
+            L += f * __ldcg(src + c * (D + 2) + D + 1);
+        }
+        out[((long long)seq * Hq + hk * G + g) * D + d] = __float2bfloat16_rn(o / L);
     }
 }
 
@@ -271,31 +328,47 @@ extern "C" size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int m
     return (size_t)n_seqs * Hq * n_chunks * (D + 2) * sizeof(float);
 }
 
-extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_pool, const int32_t* d_block_table,
-                                      int max_pages, const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
-                                      const float* d_rope_table, int max_context, void* d_scratch, void* d_out, void* stream) {
+static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
+                                     const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                     const float* d_rope_table, int max_context, void* d_scratch, void* d_out, const void* d_k_new,
+                                     const void* d_v_new, int64_t kv_new_stride, int* d_counters, bool fused, void* stream,
+                                     const char* who) {
     if (n_seqs == 0) return JSM_OK;
-    if (!d_q || !d_pool || !d_block_table || !d_context_lens || !d_scratch || !d_out)
-        JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode: null pointer");
-    if (D != 128) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_decode: head_dim %d (128 only)", D);
+    if (!d_q || !d_pool || !d_block_table || !d_context_lens || !d_scratch || !d_out) JSM_FAIL(JSM_INVALID_ARG, "%s: null pointer", who);
+    if (D != 128) JSM_FAIL(JSM_UNSUPPORTED, "%s: head_dim %d (128 only)", who, D);
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) JSM_FAIL(JSM_SHAPE, "d_model must be divisible by num_heads (Hq %d, Hkv %d)", Hq, Hkv);
-    if (max_context <= 0 || (q_row_stride % 8)) JSM_FAIL(JSM_INVALID_ARG, "jsm_attn_decode: max_context %d, q stride %lld", max_context, (long long)q_row_stride);
+    if (max_context <= 0 || (q_row_stride % 8)) JSM_FAIL(JSM_INVALID_ARG, "%s: max_context %d, q stride %lld", who, max_context, (long long)q_row_stride);
+    if (fused && !d_counters) JSM_FAIL(JSM_INVALID_ARG, "%s: null counters", who);
+    if (fused && d_k_new && (!d_v_new || kv_new_stride % 2)) JSM_FAIL(JSM_INVALID_ARG, "%s: new K without V, or an odd row stride", who);
     const int G = Hq / Hkv;
     const int chunk = decode_chunk(n_seqs, Hq);
     const int n_chunks = (max_context + chunk - 1) / chunk;
     dim3 grid(n_chunks, Hkv, n_seqs);
     cudaStream_t st = as_stream(stream);
     const float sl2 = scale * LOG2E;
-#define JSM_DEC(GG)                                                                                                            \
-    JSM_CUDA_CHECK(launch_chained(attn_decode_kernel<GG>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)d_q,          \
-                                  (long long)q_row_stride, (const __nv_bfloat16*)d_pool, d_block_table, max_pages, d_context_lens, \
-                                  Hq, Hkv, sl2, (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch))
+#define JSM_DEC(GG, FF)                                                                                                          \
+    JSM_CUDA_CHECK(launch_chained(attn_decode_kernel<GG, FF>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)d_q,       \
+                                  (long long)q_row_stride, (__nv_bfloat16*)d_pool, d_block_table, max_pages, d_context_lens, Hq,  \
+                                  Hkv, sl2, (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch,                      \
+                                  (const __nv_bfloat16*)d_k_new, (const __nv_bfloat16*)d_v_new, (long long)kv_new_stride,         \
+                                  d_counters, (__nv_bfloat16*)d_out))
+    if (fused) {
+        switch (G) {
+            case 1: JSM_DEC(1, true); break;
+            case 2: JSM_DEC(2, true); break;
+            case 4: JSM_DEC(4, true); break;
+            case 8: JSM_DEC(8, true); break;
+            default: JSM_FAIL(JSM_UNSUPPORTED, "%s: %d query heads per kv head (1, 2, 4 or 8)", who, G);
+        }
+        JSM_LAUNCH_CHECK();
+        return JSM_OK;
+    }
     switch (G) {
-        case 1: JSM_DEC(1); break;
-        case 2: JSM_DEC(2); break;
-        case 4: JSM_DEC(4); break;
-        case 8: JSM_DEC(8); break;
-        default: JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_decode: %d query heads per kv head (1, 2, 4 or 8)", G);
+        case 1: JSM_DEC(1, false); break;
+        case 2: JSM_DEC(2, false); break;
+        case 4: JSM_DEC(4, false); break;
+        case 8: JSM_DEC(8, false); break;
+        default: JSM_FAIL(JSM_UNSUPPORTED, "%s: %d query heads per kv head (1, 2, 4 or 8)", who, G);
     }
 #undef JSM_DEC
     JSM_LAUNCH_CHECK();
@@ -303,6 +376,24 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
                                   Hq, n_chunks, chunk, (__nv_bfloat16*)d_out));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
+}
+
+extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_pool, const int32_t* d_block_table,
+                                      int max_pages, const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                      const float* d_rope_table, int max_context, void* d_scratch, void* d_out, void* stream) {
+    return attn_decode_launch(d_q, q_row_stride, const_cast<void*>(d_pool), d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D,
+                              scale, d_rope_table, max_context, d_scratch, d_out, nullptr, nullptr, 0, nullptr, false, stream,
+                              "jsm_attn_decode");
+}
+
+extern "C" jsm_status jsm_attn_decode_append(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
+                                             int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
+                                             const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                             const float* d_rope_table, int max_context, void* d_scratch, int32_t* d_counters,
+                                             void* d_out, void* stream) {
+    return attn_decode_launch(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D, scale,
+                              d_rope_table, max_context, d_scratch, d_out, d_k_new, d_v_new, kv_new_stride, d_counters, true, stream,
+                              "jsm_attn_decode_append");
 }
 
 // ---- decode attention that allocates nothing ---------------------------------------------------------

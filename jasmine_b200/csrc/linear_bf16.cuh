@@ -41,6 +41,14 @@ struct PackedArgs {
     int* counters = nullptr;  // one per tile, zero before the first launch (the kernel leaves them zero)
     int n_counters = 0;
     bool chained = false;     // link of a kernel chain: W may be fetched before the predecessor kernel ends
+    // Fused RMSNorm.  ssq_in: [ssq_in_tiles][ssq_stride] per-tile sums of squares of the rows of X, as a previous launch
+    // wrote them through ssq_out; then Y = (X . W'^T) / sqrt(mean(x^2) + eps) with the norm's gain already folded into
+    // the packed weights.  ssq_out: [ceil(N/128)][ssq_stride], sums of squares of the bf16 outputs of this launch.
+    const float* ssq_in = nullptr;
+    int ssq_in_tiles = 0;
+    int ssq_stride = 0;       // 0 = T
+    float eps = 0.0f;
+    float* ssq_out = nullptr;
 };
 // Row of the logical (stacked) weight matrix that packed row r of tile j holds; -1 = padding.
 // plain : rows j*128 .. j*128+127 of an [N, K] matrix.

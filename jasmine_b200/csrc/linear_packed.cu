@@ -25,6 +25,7 @@
 #include "linear_bf16.cuh"
 #include <math.h>
 #include <mutex>
+#include <stdlib.h>
 
 namespace jsm {
 
@@ -64,6 +65,12 @@ struct PkParams {
     int w_early;          // weights may be fetched before the predecessor kernel has finished
     int pf_units;         // units beyond the ring that are prefetched into L2 up front
     int stages;
+    int pair_ok;          // K is a multiple of 64: two k-blocks of X can be fetched as one 3-D tile
+    const float* ssq_in;  // [ssq_in_tiles][ssq_stride] per-tile sums of squares of X's rows (null: X is used as it is)
+    int ssq_in_tiles;
+    int ssq_stride;       // row pitch of ssq_in and ssq_out (tokens of the whole call)
+    float inv_d, eps;     // 1 / (features of X), epsilon under the square root
+    float* ssq_out;       // [n_tiles][ssq_stride]: sums of squares of this launch's outputs per tile and token, or null
     unsigned long long* trace;  // optional timeline: 8 time stamps (globaltimer, ns) per CTA of this launch
 };
 
@@ -82,12 +89,18 @@ __host__ __device__ inline long long pk_begin(long long c, long long U, long lon
 // CTA that owns unit u: the largest c with c*U/G <= u
 __host__ __device__ inline int pk_owner(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
 
+// Units of the stream a stage holds: two consecutive k-blocks of one tile when the segment has two left (one 32 KB
+// request instead of two of 16 KB: the copy engine's rate of requests, not the bytes in flight, bounds a CTA's stream),
+// else one.  Producer and MMA issuer walk the same sequence.
+__device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok && left >= 2) ? 2 : 1; }
+
 template <int BN>
 __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
-    linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, PkParams P) {
+    linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int B_BYTES = BN * 128;  // BN tokens x 64 k, bf16
-    constexpr int STAGE_BYTES = PK_TILE_BYTES + B_BYTES;
+    constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + B_BYTES);  // [W unit 0][W unit 1][X block 0][X block 1]
+    constexpr int X_OFF = 2 * PK_TILE_BYTES;
     constexpr int TMEM_NEED = 2 * BN;  // two accumulator buffers
     constexpr int TMEM_COLS = TMEM_NEED < 32 ? 32 : TMEM_NEED;
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two, at most 512");
@@ -98,8 +111,10 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
     __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
-    __shared__ int is_last_smem;
+    __shared__ int is_last_smem[2];
     __shared__ float pair_smem[64 * 17];  // paired epilogue: up values of 16 token columns, padded rows
+    __shared__ float row_scale[256];      // 1 / rms of every token when the RMSNorm is fused into this projection
+    __shared__ float ssq_part[4 * 256];   // per-warp sums of squares of a whole tile's outputs
 
     chain_trigger();
     if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
@@ -107,7 +122,6 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
     const int stages = P.stages;
     const long long U = (long long)P.n_tiles * P.kbt, G = gridDim.x;
     const long long u_begin = pk_begin(blockIdx.x, U, G), u_end = pk_begin(blockIdx.x + 1, U, G);
-    const int n_it = (int)(u_end - u_begin);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -121,6 +135,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
         }
         mbar_fence_init();
         tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_x2);
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_smem, TMEM_COLS);
@@ -135,35 +150,53 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
         // ---- producer ------------------------------------------------------------------------------------
         if (lane == 0) {
             const uint8_t* wsrc = P.Wp + (size_t)u_begin * PK_TILE_BYTES;
-            const int pre = P.w_early ? min(n_it, stages) : 0;
-            for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-                bulk_load(tiles + (size_t)i * STAGE_BYTES, wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES, &full_bar[i]);
-            }
+            // weights first: the ring is filled with W before the predecessor kernel has finished (constant weights);
+            // the X blocks of the same stages follow once it has
+            int pre = 0;
+            long long u = u_begin;
             if (P.w_early) {
-                const int pf_end = min(n_it, pre + P.pf_units);
-                for (int i = pre; i < pf_end; ++i) bulk_prefetch_l2(wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES);
+                while (u < u_end && pre < stages) {
+                    const int kb0 = (int)(u % P.kbt);
+                    const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
+                    mbar_expect_tx(&full_bar[pre], (uint32_t)n * (PK_TILE_BYTES + B_BYTES));
+                    bulk_load(tiles + (size_t)pre * STAGE_BYTES, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES,
+                              &full_bar[pre]);
+                    u += n;
+                    ++pre;
+                }
             }
             PK_TRACE(1);  // first ring of W requested
             chain_wait();
             PK_TRACE(2);  // predecessor complete
-            for (int i = 0; i < pre; ++i)
-                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + PK_TILE_BYTES, &tmap_x, (int)((u_begin + i) % P.kbt) * 64, 0, &full_bar[i]);
-            int issued = pre;
-            for (int i = pre; i < n_it; ++i) {
+            u = u_begin;
+            for (int i = 0; i < pre; ++i) {
+                const int kb0 = (int)(u % P.kbt);
+                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
+                uint8_t* xs = tiles + (size_t)i * STAGE_BYTES + X_OFF;
+                if (n == 2) tma_load_3d(xs, &tmap_x2, 0, 0, kb0, &full_bar[i]);
+                else tma_load_2d(xs, &tmap_x, kb0 * 64, 0, &full_bar[i]);
+                u += n;
+            }
+            int i = pre, issued = pre;
+            while (u < u_end) {
                 const int s = i % stages;
                 const uint32_t ph = (i / stages) & 1;
                 if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
+                const int kb0 = (int)(u % P.kbt);
+                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
                 uint8_t* st = tiles + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                bulk_load(st, wsrc + (size_t)i * PK_TILE_BYTES, PK_TILE_BYTES, &full_bar[s]);
-                tma_load_2d(st + PK_TILE_BYTES, &tmap_x, (int)((u_begin + i) % P.kbt) * 64, 0, &full_bar[s]);
-                issued = i + 1;
+                mbar_expect_tx(&full_bar[s], (uint32_t)n * (PK_TILE_BYTES + B_BYTES));
+                bulk_load(st, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES, &full_bar[s]);
+                if (n == 2) tma_load_3d(st + X_OFF, &tmap_x2, 0, 0, kb0, &full_bar[s]);
+                else tma_load_2d(st + X_OFF, &tmap_x, kb0 * 64, 0, &full_bar[s]);
+                u += n;
+                ++i;
+                issued = i;
             }
             if (abort_flag) {  // let the copies in flight land before the CTA exits (bounded)
                 const long long t_start = clock64();
-                for (int i = max(0, issued - stages); i < issued; ++i)
-                    while (!mbar_try_wait(&full_bar[i % stages], (i / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
+                for (int j = max(0, issued - stages); j < issued; ++j)
+                    while (!mbar_try_wait(&full_bar[j % stages], (j / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
             }
         }
     } else if (warp == 1) {
@@ -183,19 +216,23 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                     tc_fence_after();
                 }
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-                for (int j = 0; j < len; ++j, ++it) {
+                for (int j = 0; j < len; ++it) {
+                    const int n = pk_chunk(P.pair_ok, len - j);
                     const int s = it % stages;
                     const uint32_t ph = (it / stages) & 1;
                     if (!mbar_wait(&full_bar[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
                     if (it == 0) PK_TRACE(3);  // first stage landed
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                    const uint64_t a_desc = smem_desc_sw128(a_addr);
-                    const uint64_t b_desc = smem_desc_sw128(a_addr + PK_TILE_BYTES);
+                    for (int q = 0; q < n; ++q) {
+                        const uint64_t a_desc = smem_desc_sw128(a_addr + q * PK_TILE_BYTES);
+                        const uint64_t b_desc = smem_desc_sw128(a_addr + X_OFF + q * B_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        mma_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (j > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 4; ++k)
+                            mma_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (j > 0 || q > 0 || k > 0) ? 1u : 0u);
+                    }
                     mma_commit(&empty_bar[s]);
+                    j += n;
                 }
                 if (!ok) break;
                 mma_commit(&acc_full[buf]);
@@ -209,6 +246,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // packed row of the tile = TMEM lane
         const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
+        const bool want_ssq = P.ssq_out != nullptr;  // plain tiles only (checked on the host)
         bool ok = true, waited = false;
         int seg = 0;
         long long u = u_begin;
@@ -220,36 +258,65 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
             if (!mbar_wait(&acc_full[buf], (seg >> 1) & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
             tc_fence_after();
             if (!waited) {
-                chain_wait();  // R, Y, the workspace and the counters belong to the stream's other kernels
+                chain_wait();  // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels
                 waited = true;
+                // row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into
+                // the packed weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile
+                // sums of squares that the kernel which wrote x left behind (added in tile order)
+                if (P.ssq_in) {
+                    for (int t = etid; t < P.T; t += 128) {
+                        float q = 0.0f;
+                        for (int j = 0; j < P.ssq_in_tiles; ++j) q += __ldcg(P.ssq_in + (size_t)j * P.ssq_stride + t);
+                        row_scale[t] = 1.0f / sqrtf(q * P.inv_d + P.eps);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
             }
+            const bool scaled = P.ssq_in != nullptr;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
             const bool whole = (len == P.kbt);
             if (whole) {
                 // ---- the tile is complete in this CTA: epilogue straight from the accumulator
                 if (!P.paired) {
                     const int n = tile * 128 + row;
-                    const float bias = (P.bias && n < P.N) ? P.bias[n] : 0.0f;
+                    const bool valid = n < P.N;
+                    const float bias = (P.bias && valid) ? P.bias[n] : 0.0f;
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 16) {
                         if (c0 >= P.T) break;
                         uint32_t r[16];
                         tmem_ld16(acc_addr + c0, r);
                         tmem_ld_wait();
-                        if (n < P.N) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const int t = c0 + j;
-                                if (t < P.T) {
-                                    float v = __uint_as_float(r[j]) + bias;
-                                    if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
-                                    else if (P.epilogue == LIN_GELU) v = pk_gelu(v);
-                                    else if (P.epilogue == LIN_RESIDUAL) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
-                                    if (P.out_f32) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
-                                    else reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = __float2bfloat16_rn(v);
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = c0 + j;  // warp-uniform
+                            if (t < P.T) {
+                                float v = __uint_as_float(r[j]);
+                                if (scaled) v *= row_scale[t];
+                                v += bias;
+                                if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
+                                else if (P.epilogue == LIN_GELU) v = pk_gelu(v);
+                                else if (P.epilogue == LIN_RESIDUAL && valid) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
+                                float stored = v;
+                                if (!P.out_f32) {
+                                    const __nv_bfloat16 hb = __float2bfloat16_rn(v);
+                                    stored = __bfloat162float(hb);
+                                    if (valid) reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = hb;
+                                } else if (valid) {
+                                    reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
+                                }
+                                if (want_ssq) {  // sum of squares of what was stored, over the 128 features of the tile
+                                    const float sq = warp_sum(valid ? stored * stored : 0.0f);
+                                    if (lane == 0) ssq_part[quad * 256 + t] = sq;
                                 }
                             }
                         }
+                    }
+                    if (want_ssq) {
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        for (int t = etid; t < P.T; t += 128)
+                            P.ssq_out[(size_t)tile * P.ssq_stride + t] = (ssq_part[t] + ssq_part[256 + t]) + (ssq_part[512 + t] + ssq_part[768 + t]);
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
                     }
                 } else {
                     // lanes 0..63 hold gate, lanes 64..127 the matching up rows: hand the up values over through shared memory
@@ -271,7 +338,8 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                             for (int j = 0; j < 16; ++j) {
                                 const int t = c0 + j;
                                 if (t < P.T) {
-                                    const float v = pk_silu(__uint_as_float(r[j])) * pair_smem[f * 17 + j];
+                                    const float sc = scaled ? row_scale[t] : 1.0f;
+                                    const float v = pk_silu(__uint_as_float(r[j]) * sc) * (pair_smem[f * 17 + j] * sc);
                                     if (P.out_f32) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
                                     else reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = __float2bfloat16_rn(v);
                                 }
@@ -303,33 +371,42 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the MMA warp may reuse the buffer while the fold runs
-                __threadfence();
+                // release / acquire through the tile counter: the barrier orders every thread's partial stores before the
+                // release of thread 0, and its acquire before every thread's loads of the other CTAs' slots
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0) {
-                    const int old = atomicAdd(&P.counters[tile], 1);
+                    int old;
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(P.counters + tile) : "memory");
                     const int last = (old == n_contrib - 1);
                     if (last) P.counters[tile] = 0;  // ready for the next launch
-                    is_last_smem = last;
+                    is_last_smem[seg & 1] = last;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const bool is_last = is_last_smem != 0;
-                asm volatile("bar.sync 1, 128;" ::: "memory");  // is_last_smem may be rewritten by the next shared tile
+                const bool is_last = is_last_smem[seg & 1] != 0;
                 if (is_last) {
-                    __threadfence();
                     // A thread owns 4 consecutive output features of every TS-th token; the partials of four tokens are in
-                    // flight at once and the slots are added in slot order.
+                    // flight at once and the slots are added in slot order.  Plain tiles: a warp shares its tokens (32 groups
+                    // of 4 features), so the per-token sum of squares is one warp reduction.
                     const int groups = P.paired ? 16 : 32;  // groups of 4 features per tile
                     const int f4 = (etid % groups) * 4, tsub = etid / groups, TS = 128 / groups;
                     const int n = (P.paired ? tile * 64 : tile * 128) + f4;
+                    const bool valid = n < P.N;
                     const float* tbase = P.ws + (size_t)tile * P.max_slots * (size_t)P.T * 128;
                     const size_t slot_stride = (size_t)P.T * 128;
-                    if (n < P.N) {
-                        const float4 bias4 = (P.bias && !P.paired) ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int tb = tsub; tb < P.T; tb += 4 * TS) {
-                            float4 g[4], up[4];
+                    const float4 bias4 = (P.bias && !P.paired && valid) ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int tb = tsub; tb < P.T; tb += 4 * TS) {  // warp-uniform trip count for plain tiles
+                        float4 g[4], up[4];
+                        uint2 rr[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { g[i] = make_float4(0.f, 0.f, 0.f, 0.f); up[i] = g[i]; }
-#pragma unroll 2
+                        for (int i = 0; i < 4; ++i) {
+                            g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            up[i] = g[i];
+                            rr[i] = make_uint2(0u, 0u);
+                            const int t = tb + TS * i;
+                            if (P.epilogue == LIN_RESIDUAL && valid && t < P.T) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                        }
+                        if (valid) {
+#pragma unroll 4
                             for (int z = 0; z < n_contrib; ++z) {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
@@ -345,29 +422,37 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                                     }
                                 }
                             }
+                        }
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int t = tb + TS * i;
-                                if (t >= P.T) break;
-                                float v[4] = {g[i].x + bias4.x, g[i].y + bias4.y, g[i].z + bias4.z, g[i].w + bias4.w};
-                                const float uu[4] = {up[i].x, up[i].y, up[i].z, up[i].w};
-                                if (P.epilogue == LIN_RESIDUAL) {
-                                    const uint2 rr = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
-                                    v[0] += bf16lo(rr.x); v[1] += bf16hi(rr.x); v[2] += bf16lo(rr.y); v[3] += bf16hi(rr.y);
-                                }
+                        for (int i = 0; i < 4; ++i) {
+                            const int t = tb + TS * i;
+                            if (t >= P.T) break;
+                            const float sc = scaled ? row_scale[t] : 1.0f;
+                            float v[4] = {g[i].x * sc + bias4.x, g[i].y * sc + bias4.y, g[i].z * sc + bias4.z, g[i].w * sc + bias4.w};
+                            const float uu[4] = {up[i].x * sc, up[i].y * sc, up[i].z * sc, up[i].w * sc};
+                            if (P.epilogue == LIN_RESIDUAL) {
+                                v[0] += bf16lo(rr[i].x); v[1] += bf16hi(rr[i].x); v[2] += bf16lo(rr[i].y); v[3] += bf16hi(rr[i].y);
+                            }
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    if (P.paired) v[j] = pk_silu(v[j]) * uu[j];
-                                    else if (P.epilogue == LIN_RELU) v[j] = fmaxf(v[j], 0.0f);
-                                    else if (P.epilogue == LIN_GELU) v[j] = pk_gelu(v[j]);
-                                }
-                                if (P.out_f32) {
-                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.Y) + (size_t)t * P.N + n) = make_float4(v[0], v[1], v[2], v[3]);
-                                } else {
-                                    uint2 o;
-                                    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-                                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
-                                }
+                            for (int j = 0; j < 4; ++j) {
+                                if (P.paired) v[j] = pk_silu(v[j]) * uu[j];
+                                else if (P.epilogue == LIN_RELU) v[j] = fmaxf(v[j], 0.0f);
+                                else if (P.epilogue == LIN_GELU) v[j] = pk_gelu(v[j]);
+                            }
+                            float sq = 0.0f;
+                            if (P.out_f32) {
+                                if (valid) *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.Y) + (size_t)t * P.N + n) = make_float4(v[0], v[1], v[2], v[3]);
+                                sq = (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
+                            } else {
+                                uint2 o;
+                                o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+                                if (valid) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
+                                const float s0 = bf16lo(o.x), s1 = bf16hi(o.x), s2 = bf16lo(o.y), s3 = bf16hi(o.y);
+                                sq = (s0 * s0 + s1 * s1) + (s2 * s2 + s3 * s3);
+                            }
+                            if (want_ssq) {  // plain tiles: all 32 lanes of the warp hold token t
+                                sq = warp_sum(valid ? sq : 0.0f);
+                                if (lane == 0) P.ssq_out[(size_t)tile * P.ssq_stride + t] = sq;
                             }
                         }
                     }
@@ -442,6 +527,12 @@ int linear_packed_grid(int N, int K, int paired) {
     pk_dims(N, K, paired, &nt, &kbt);
     const long long U = (long long)nt * kbt;
     long long G = sm_count();
+    // few tiles: split every tile over the same number of CTAs (one segment, one fold per CTA) when that still
+    // occupies at least four fifths of the SMs; otherwise the even split of the whole stream
+    if (nt < G) {
+        const long long S = G / nt;
+        if (nt * S * 5 >= G * 4 && kbt >= S) G = nt * S;
+    }
     if (U < 4 * G) G = U / 4;  // at least four units per CTA
     if (G < 1) G = 1;
     return (int)G;
@@ -467,10 +558,15 @@ static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
 template <int BN>
-static jsm_status launch_packed(const CUtensorMap& mx, PkParams& P, int grid, bool chained, cudaStream_t st) {
-    constexpr int STAGE_BYTES = PK_TILE_BYTES + BN * 128;
+static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, bool chained, cudaStream_t st) {
+    constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
-    const int budget = (BN <= 64 ? 106 : 200) * 1024;
+    static int budget_kb = -1;
+    if (budget_kb < 0) {
+        const char* e = getenv("JSM_PK_BUDGET_KB");
+        budget_kb = e ? atoi(e) : 0;
+    }
+    const int budget = (budget_kb > 0 ? budget_kb : (BN <= 64 ? 150 : 200)) * 1024;
     int stages = budget / STAGE_BYTES;
     if (stages > PK_MAX_STAGES) stages = PK_MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -483,21 +579,31 @@ static jsm_status launch_packed(const CUtensorMap& mx, PkParams& P, int grid, bo
     const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        cudaFuncAttributes fa;
+        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN>));
+        // 227 KB per CTA in all: what the kernel's static arrays leave is open to the stage ring
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
     if (chained) {
-        // L2 prefetch beyond the ring: about 32 MB per launch over all CTAs
-        long long pf = (32ll << 20) / ((long long)PK_TILE_BYTES * grid);
+        // L2 prefetch beyond the ring: JSM_PF_MB megabytes per launch over all CTAs (off by default: it measured slower than the ring alone)
+        static long long pf_mb = -1;
+        if (pf_mb < 0) {
+            const char* e = getenv("JSM_PF_MB");
+            pf_mb = e ? atoll(e) : 0;
+            if (pf_mb < 0) pf_mb = 0;
+        }
+        long long pf = (pf_mb << 20) / ((long long)PK_TILE_BYTES * grid);
         P.pf_units = (int)(pf > 128 ? 128 : pf);
         P.w_early = 1;
-        JSM_CUDA_CHECK(launch_chained(linear_packed_kernel<BN>, dim3(grid), dim3(PK_THREADS), smem, st, mx, P));
+        JSM_CUDA_CHECK(launch_chained(linear_packed_kernel<BN>, dim3(grid), dim3(PK_THREADS), smem, st, mx, mx2, P));
         g_launches.fetch_add(1);
         return JSM_OK;
     }
     P.w_early = 0;
     P.pf_units = 0;
-    linear_packed_kernel<BN><<<grid, PK_THREADS, smem, st>>>(mx, P);
+    linear_packed_kernel<BN><<<grid, PK_THREADS, smem, st>>>(mx, mx2, P);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -531,16 +637,29 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     }
     P.ws = a.ws; P.counters = a.counters;
     P.err = tc_error_word();
+    if (a.ssq_out && (paired || a.out_f32)) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: row statistics are written for plain bf16 outputs only");
+    if (a.ssq_in && (a.ssq_in_tiles <= 0 || a.K <= 0)) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: row statistics without their tile count");
+    P.ssq_in = a.ssq_in; P.ssq_in_tiles = a.ssq_in_tiles; P.ssq_stride = a.ssq_stride > 0 ? a.ssq_stride : a.T;
+    P.inv_d = 1.0f / (float)a.K; P.eps = a.eps; P.ssq_out = a.ssq_out;
     const int bn = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : a.T <= 128 ? 128 : 256;
     CUtensorMap mx;
     jsm_status s = make_tmap_bf16_2d(&mx, a.X, (uint64_t)a.T, (uint64_t)a.K, (uint64_t)(a.x_row_stride > 0 ? a.x_row_stride : a.K), bn, 64);
     if (s != JSM_OK) return s;
+    // the same matrix as [k-block][row][64]: a box two k-blocks deep lands as two consecutive swizzled X blocks
+    const long long xs = a.x_row_stride > 0 ? a.x_row_stride : a.K;
+    P.pair_ok = (a.K % 64 == 0) ? 1 : 0;
+    CUtensorMap mx2 = mx;
+    if (P.pair_ok) {
+        s = make_tmap_bf16_3d(&mx2, a.X, 64, (uint64_t)a.T, (uint64_t)(a.K / 64), (uint64_t)xs, 64, 64, bn, 2);
+        if (s != JSM_OK) return s;
+        if (a.K / 64 < 2) P.pair_ok = 0;
+    }
     switch (bn) {
-        case 16: return launch_packed<16>(mx, P, grid, a.chained, st);
-        case 32: return launch_packed<32>(mx, P, grid, a.chained, st);
-        case 64: return launch_packed<64>(mx, P, grid, a.chained, st);
-        case 128: return launch_packed<128>(mx, P, grid, a.chained, st);
-        default: return launch_packed<256>(mx, P, grid, a.chained, st);
+        case 16: return launch_packed<16>(mx, mx2, P, grid, a.chained, st);
+        case 32: return launch_packed<32>(mx, mx2, P, grid, a.chained, st);
+        case 64: return launch_packed<64>(mx, mx2, P, grid, a.chained, st);
+        case 128: return launch_packed<128>(mx, mx2, P, grid, a.chained, st);
+        default: return launch_packed<256>(mx, mx2, P, grid, a.chained, st);
     }
 }
 

@@ -15,6 +15,7 @@
 #include "attn.cuh"
 #include <math.h>
 #include <string.h>
+#include <stdlib.h>
 #include <string>
 #include <vector>
 #include <algorithm>
@@ -53,9 +54,11 @@ struct jsm_model {
     float* partial = nullptr;
     float* logits = nullptr;
     float* dec_scratch = nullptr;
+    float *ssq0 = nullptr, *ssq_a = nullptr, *ssq_b = nullptr;  // row statistics: after the embedding, after wo, after down
     size_t ws_floats = 0;        // capacity of `partial`: fp32 partials of the tiles that several CTAs share
     int* counters = nullptr;     // one arrival counter per tile (self-resetting)
     int n_counters = 0;
+    int32_t* attn_counters = nullptr;  // one per (sequence, kv head) of the decode attention (self-resetting)
     std::vector<void*> allocs;
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
@@ -68,7 +71,7 @@ namespace jsm {
 // `key`; value (r, c) of a shard = element ((row0 + r) * full_cols + col0 + c) of the full tensor, so that all TP
 // layouts agree.
 struct RowSeg { long long start, rows, row0; uint64_t key; };
-struct FillSpec { RowSeg seg[3]; int n_seg; long long full_cols, col0; float std; };
+struct FillSpec { RowSeg seg[3]; int n_seg; long long full_cols, col0; float std; const float* gain; };  // gain[k] (or null) scales column k
 
 // generates a weight matrix straight into its packed image (one thread per 16-byte chunk, see pack_weights_kernel)
 __global__ void __launch_bounds__(256) fill_packed_kernel(uint8_t* __restrict__ dst, int N, int K, int n_tiles, int kbt, int paired,
@@ -90,7 +93,10 @@ __global__ void __launch_bounds__(256) fill_packed_kernel(uint8_t* __restrict__ 
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float lo = rng_value(S.key, base + 2 * e, 0, 0.0f, spec.std), hi = rng_value(S.key, base + 2 * e + 1, 0, 0.0f, spec.std);
+                // the tensor's own value is its bf16 rounding; the gain of the norm in front of the projection is folded in
+                float lo = bf16_bits_to_f32(f32_to_bf16_bits(rng_value(S.key, base + 2 * e, 0, 0.0f, spec.std)));
+                float hi = bf16_bits_to_f32(f32_to_bf16_bits(rng_value(S.key, base + 2 * e + 1, 0, 0.0f, spec.std)));
+                if (spec.gain) { lo *= spec.gain[k + 2 * e]; hi *= spec.gain[k + 2 * e + 1]; }
                 w[e] = (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
             }
             v = make_uint4(w[0], w[1], w[2], w[3]);
@@ -187,12 +193,30 @@ __global__ void __launch_bounds__(256) fold_add_norm_kernel(__nv_bfloat16* __res
         if (c < d) {
             float o[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = gain[c + j] * (v[i][j] / sd);
+            for (int j = 0; j < 8; ++j) o[j] = (gain ? gain[c + j] : 1.0f) * (v[i][j] / sd);
             uint4 w;
             w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]); w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
             *reinterpret_cast<uint4*>(y + base + c) = w;
         }
     }
+}
+
+// ssq[t] = sum of squares of row t of x (bf16): the row statistics of the embedding output, in the form the packed
+// projections exchange them (one "tile" per row)
+__global__ void __launch_bounds__(256) row_ssq_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ ssq, int d) {
+    __shared__ float smem[8];
+    chain_trigger();
+    chain_wait();
+    const __nv_bfloat16* row = x + (long long)blockIdx.x * d;
+    float q = 0.0f;
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+        const uint4 w = *reinterpret_cast<const uint4*>(row + c);
+        const float f[8] = {bf16lo(w.x), bf16hi(w.x), bf16lo(w.y), bf16hi(w.y), bf16lo(w.z), bf16hi(w.z), bf16lo(w.w), bf16hi(w.w)};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q += f[j] * f[j];
+    }
+    q = block_sum_256(q, smem);
+    if (threadIdx.x == 0) ssq[blockIdx.x] = q;
 }
 
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n) {
@@ -255,72 +279,99 @@ static void fill_packed(uint8_t* dst, int N, int K, int paired, const FillSpec& 
     g_launches.fetch_add(1);
 }
 
+// Row statistics handed from the projection that writes the residual stream to the one that reads it (fused RMSNorm)
+struct RowStats {
+    const float* in = nullptr;  // [in_tiles][T] sums of squares of X's rows
+    int in_tiles = 0;
+    float* out = nullptr;       // [ceil(N/128)][T] sums of squares of the outputs
+};
+
 // One projection over packed weights for any number of tokens: chunks of 256 tokens, each streaming the weights once.
 static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_stride, const uint8_t* Wp, int N, int K, int epilogue,
-                             const __nv_bfloat16* R, void* Y, bool out_f32, int T, cudaStream_t st) {
+                             const __nv_bfloat16* R, void* Y, bool out_f32, int T, cudaStream_t st, RowStats rs = RowStats(),
+                             int stats_stride = 0) {
     PackedArgs a;
     a.Wp = Wp; a.bias = nullptr; a.epilogue = epilogue; a.out_f32 = out_f32; a.N = N; a.K = K; a.x_row_stride = x_stride;
     a.ws = m->partial; a.ws_floats = m->ws_floats; a.counters = m->counters; a.n_counters = m->n_counters;
     a.chained = true;  // the model's weights are constant while its stream runs
+    a.eps = m->c.norm_eps;
+    a.ssq_in_tiles = rs.in_tiles;
+    a.ssq_stride = stats_stride > 0 ? stats_stride : T;
     for (int t0 = 0; t0 < T; t0 += 256) {
         a.T = T - t0 < 256 ? T - t0 : 256;
         a.X = X + (long long)t0 * x_stride;
         a.R = R ? R + (long long)t0 * N : nullptr;
         a.Y = out_f32 ? static_cast<void*>(reinterpret_cast<float*>(Y) + (long long)t0 * N)
                       : static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(Y) + (long long)t0 * N);
+        a.ssq_in = rs.in ? rs.in + t0 : nullptr;
+        a.ssq_out = rs.out ? rs.out + t0 : nullptr;
         jsm_status s = linear_packed_launch(a, st);
         if (s != JSM_OK) return s;
     }
     return JSM_OK;
 }
 
-// h += X . W^T (the residual stream), then xn = RMSNorm(h) * gain (gain may be null: no norm).  On one GPU the
-// projection adds into h in its epilogue; under tensor parallelism the rank-local product goes through the all-reduce.
-static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K,
-                                        const float* next_gain, cudaStream_t st) {
+// h += X . W^T (the residual stream).  One GPU: the projection adds into h in its epilogue and leaves the row
+// statistics of the new h in `stats_out` for the projection that reads h next (which applies the RMSNorm itself).
+// Tensor parallel: the rank-local product goes through the all-reduce, then h += sum and xn = RMSNorm(h) (the gain is
+// folded into the next projection's weights) unless `normalise` is false.
+static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K, float* stats_out,
+                                        bool normalise, cudaStream_t st) {
     const int d = m->c.d_model;
     if (m->c.tp_size == 1) {
-        jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_RESIDUAL, m->h, m->h, false, T, st);
-        if (s != JSM_OK) return s;
-        if (next_gain) {
-            JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, next_gain,
-                                          m->c.norm_eps, m->xn, d));
-            JSM_LAUNCH_CHECK();
-        }
-        return JSM_OK;
+        RowStats rs;
+        rs.out = stats_out;
+        return run_linear(m, X, K, Wp, N, K, LIN_RESIDUAL, m->h, m->h, false, T, st, rs);
     }
     jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->red, false, T, st);
     if (s != JSM_OK) return s;
     // tensor parallel: sum the rank-local outputs, then add into the residual stream
     if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
     if (m->allreduce(m->red, (size_t)T * N, JSM_BF16, st, m->allreduce_user) != 0) JSM_FAIL(JSM_NCCL, "all-reduce callback failed");
-    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, next_gain,
-                                  m->c.norm_eps, next_gain ? m->xn : nullptr, d));
+    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, nullptr,
+                                  m->c.norm_eps, normalise ? m->xn : nullptr, d));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
 
+// On one GPU no normalised copy of the residual stream exists: every projection that follows an RMSNorm reads h itself
+// and scales its output rows by 1/rms (row statistics from the kernel that wrote h; gains folded into its weights).
+// Under tensor parallelism the kernel that adds the all-reduced sum into h also writes xn.
 static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool decode, int batch, int prefill_seq, cudaStream_t st) {
     const jsm_model_config& c = m->c;
     const int d = c.d_model, D = c.head_dim;
+    const bool tp = c.tp_size > 1;
+    const int d_tiles = (d + 127) / 128;
     jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
     if (s != JSM_OK) return s;
-    JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, m->layers[0].g1,
-                                  c.norm_eps, m->xn, d));
+    if (tp) {
+        JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, nullptr,
+                                      c.norm_eps, m->xn, d));
+    } else {
+        JSM_CUDA_CHECK(launch_chained(row_ssq_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)m->h, m->ssq0, d));
+    }
     JSM_LAUNCH_CHECK();
+    const __nv_bfloat16* x_in = tp ? m->xn : m->h;  // what the projections after a norm read
     const float scale = 1.0f / sqrtf((float)D);
+    RowStats after_down;  // statistics of h as the previous layer (or the embedding) left it
+    if (!tp) { after_down.in = m->ssq0; after_down.in_tiles = 1; }
     for (int l = 0; l < c.n_layers; ++l) {
         LayerW& L = m->layers[l];
-        s = run_linear(m, m->xn, d, L.wqkv, m->qkv_dim, d, LIN_NONE, nullptr, m->qkv, false, T, st);
+        s = run_linear(m, x_in, d, L.wqkv, m->qkv_dim, d, LIN_NONE, nullptr, m->qkv, false, T, st, after_down);
         if (s != JSM_OK) return s;
         const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
         const __nv_bfloat16* vv = kk + (long long)m->Hkv_l * D;
         if (decode) {
-            // the new token: K is rotated on its way into the cache, q inside the attention kernel
-            s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
-            if (s != JSM_OK) return s;
-            s = jsm_attn_decode(m->qkv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch, m->Hq_l, m->Hkv_l, D, scale,
-                                m->rope, c.max_context, m->dec_scratch, m->attn, st);
+            // the new token: one launch rotates K into the cache, stores V, rotates q and attends over the context
+            static const bool unfused = getenv("JSM_ATTN_UNFUSED") != nullptr;
+            if (unfused) {
+                s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
+                if (s != JSM_OK) return s;
+                s = jsm_attn_decode(m->qkv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch, m->Hq_l, m->Hkv_l, D, scale,
+                                    m->rope, c.max_context, m->dec_scratch, m->attn, st);
+            } else
+            s = jsm_attn_decode_append(m->qkv, m->qkv_dim, kk, vv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch,
+                                       m->Hq_l, m->Hkv_l, D, scale, m->rope, c.max_context, m->dec_scratch, m->attn_counters, m->attn, st);
         } else {
             // prompt of one sequence starting at position 0: rotate q and k in place (the first Hq + Hkv heads of every
             // fused row), cache K and V, then causal attention over the fresh q, k, v
@@ -336,22 +387,29 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
                                      m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
         }
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, L.g2, st);
+        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, st);
         if (s != JSM_OK) return s;
-        s = run_linear(m, m->xn, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st);
+        RowStats after_wo;
+        if (!tp) { after_wo.in = m->ssq_a; after_wo.in_tiles = d_tiles; }
+        s = run_linear(m, x_in, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st, after_wo);
         if (s != JSM_OK) return s;
-        const float* next_gain = (l + 1 < c.n_layers) ? m->layers[l + 1].g1 : m->gf;
-        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, next_gain, st);
+        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, st);
         if (s != JSM_OK) return s;
+        if (!tp) { after_down.in = m->ssq_b; after_down.in_tiles = d_tiles; }
     }
     (void)prefill_seq;
     return JSM_OK;
 }
 
-static jsm_status logits_and_argmax(jsm_model* m, const __nv_bfloat16* xn_rows, int rows, int32_t* d_next, float* d_logits,
-                                    cudaStream_t st) {
+// logits of `rows` consecutive tokens starting at token `first` of the last forward call (which had T tokens)
+static jsm_status logits_and_argmax(jsm_model* m, int first, int rows, int T, int32_t* d_next, float* d_logits, cudaStream_t st) {
     float* lg = d_logits ? d_logits : m->logits;
-    jsm_status s = run_linear(m, xn_rows, m->c.d_model, m->lm_head, m->c.vocab, m->c.d_model, LIN_NONE, nullptr, lg, true, rows, st);
+    const int d = m->c.d_model;
+    const bool tp = m->c.tp_size > 1;
+    RowStats rs;
+    if (!tp) { rs.in = m->ssq_b + first; rs.in_tiles = (d + 127) / 128; }
+    const __nv_bfloat16* x = (tp ? m->xn : m->h) + (long long)first * d;
+    jsm_status s = run_linear(m, x, d, m->lm_head, m->c.vocab, d, LIN_NONE, nullptr, lg, true, rows, st, rs, T);
     if (s != JSM_OK) return s;
     if (d_next) {
         JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
@@ -412,7 +470,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
         FillSpec f{};
         f.n_seg = 1;
         f.seg[0] = RowSeg{0, rows, row0, rng_key(seed, tid)};
-        f.full_cols = full_cols; f.col0 = col0; f.std = std;
+        f.full_cols = full_cols; f.col0 = col0; f.std = std; f.gain = nullptr;
         return f;
     };
     for (int l = 0; l < c.n_layers; ++l) {
@@ -435,7 +493,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
             f.seg[0] = RowSeg{0, qr, c.tp_rank * qr, rng_key(seed, t0 + 0)};
             f.seg[1] = RowSeg{qr, kr, c.tp_rank * kr, rng_key(seed, t0 + 1)};
             f.seg[2] = RowSeg{qr + kr, kr, c.tp_rank * kr, rng_key(seed, t0 + 2)};
-            f.full_cols = d; f.col0 = 0; f.std = std;
+            f.full_cols = d; f.col0 = 0; f.std = std; f.gain = L.g1;
             fill_packed(L.wqkv, m->qkv_dim, d, 0, f, st);
         }
         fill_packed(L.wo, d, qdim, 0, spec1(d, 0, t0 + 3, (long long)c.n_heads * D, c.tp_rank * qr), st);
@@ -444,7 +502,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
             f.n_seg = 2;
             f.seg[0] = RowSeg{0, m->ffn_l, (long long)c.tp_rank * m->ffn_l, rng_key(seed, t0 + 4)};
             f.seg[1] = RowSeg{m->ffn_l, m->ffn_l, (long long)c.tp_rank * m->ffn_l, rng_key(seed, t0 + 5)};
-            f.full_cols = d; f.col0 = 0; f.std = std;
+            f.full_cols = d; f.col0 = 0; f.std = std; f.gain = L.g2;
             fill_packed(L.wgu, m->ffn_l, d, 1, f, st);
         }
         fill_packed(L.wdown, d, m->ffn_l, 0, spec1(d, 0, t0 + 6, c.d_ffn, (long long)c.tp_rank * m->ffn_l), st);
@@ -454,8 +512,12 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->lm_head, linear_packed_bytes(c.vocab, d, 0)));
     JSM_TRY(dev_alloc(m, &m->gf, (size_t)d));
     fill_shard(m->emb, c.vocab, d, d, 0, 0, seed, 1000000, std, st);
-    fill_packed(m->lm_head, c.vocab, d, 0, spec1(c.vocab, 0, 1000001, d, 0), st);
     fill_const_kernel<<<16, 256, 0, st>>>(m->gf, d, 1.0f);
+    {
+        FillSpec f = spec1(c.vocab, 0, 1000001, d, 0);
+        f.gain = m->gf;
+        fill_packed(m->lm_head, c.vocab, d, 0, f, st);
+    }
     wbytes += 2ull * (uint64_t)c.vocab * d + 4ull * d;
     m->weight_bytes = wbytes;
     JSM_TRY(dev_alloc(m, &m->rope, (size_t)c.max_context * (D / 2) * 4));
@@ -492,6 +554,11 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
         cudaError_t e0 = cudaMemset(m->counters, 0, m->n_counters * sizeof(int));
         if (e0 != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: %s", cudaGetErrorString(e0)); }
     }
+    JSM_TRY(dev_alloc(m, &m->ssq0, Tm));
+    JSM_TRY(dev_alloc(m, &m->ssq_a, Tm * ((d + 127) / 128)));
+    JSM_TRY(dev_alloc(m, &m->ssq_b, Tm * ((d + 127) / 128)));
+    JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
+    if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
     JSM_TRY(dev_alloc(m, &m->dec_scratch, jsm_attn_decode_scratch_bytes(c.max_batch, m->Hq_l, D, c.max_context) / sizeof(float) + 4));
     cudaError_t e = cudaMemset(m->ctx, 0, sizeof(int32_t) * c.max_batch);
@@ -569,8 +636,7 @@ jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T,
     if (s != JSM_OK) return s;
     set_ctx_kernel<<<1, 1, 0, st>>>(m->ctx, seq, T);
     JSM_LAUNCH_CHECK();
-    const __nv_bfloat16* last = m->xn + (long long)(T - 1) * m->c.d_model;
-    return logits_and_argmax(m, last, 1, d_next ? d_next + seq : nullptr, d_logits_last, st);
+    return logits_and_argmax(m, T - 1, 1, T, d_next ? d_next + seq : nullptr, d_logits_last, st);
 }
 
 jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, int32_t* d_next, float* d_logits, void* stream) {
@@ -581,7 +647,7 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     JSM_LAUNCH_CHECK();
     jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
     if (s != JSM_OK) return s;
-    return logits_and_argmax(m, m->xn, batch, d_next, d_logits, st);
+    return logits_and_argmax(m, 0, batch, batch, d_next, d_logits, st);
 }
 
 jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len) {

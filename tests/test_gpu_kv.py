@@ -75,6 +75,33 @@ def test_append_and_decode_with_rope():
         o += L
 
 
+@pytest.mark.parametrize("Hq,Hkv,use_rope", [(4, 4, True), (8, 2, True), (4, 1, False)])
+def test_fused_append_decode_equals_append_then_decode(Hq, Hkv, use_rope):
+    """jsm_attn_decode_append (one launch: append + attention + merge) against jsm_kv_append followed by
+    jsm_attn_decode on a copy of the same cache: same cache contents bit for bit, same outputs; repeated for three
+    steps so that the self-resetting counters and the growing contexts are exercised (context 64 -> 65 crosses a page)."""
+    lens = [1, 63, 64, 129, 700, 1299]
+    n = len(lens)
+    table = jb.rope_table(1, D, 10000.0, 2048) if use_rope else None
+    pool, bt, *_ = build_cache(lens, Hkv, 830 + Hq, rope_table=table)
+    pool_ref = pool.clone()
+    counters = torch.zeros(n * Hkv, dtype=torch.int32, device="cuda")
+    ctx_len = list(lens)
+    for step in range(3):
+        qkv = dev(cases.normal((n, (Hq + 2 * Hkv) * D), 840 + step, 0), torch.bfloat16)
+        q, k_new, v_new = qkv[:, :Hq * D], qkv[:, Hq * D:(Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D:]
+        pos = torch.tensor(ctx_len, dtype=torch.int32, device="cuda")
+        ctx_len = [c + 1 for c in ctx_len]
+        ctx = torch.tensor(ctx_len, dtype=torch.int32, device="cuda")
+        jb.kv_append(pool_ref, bt, k_new, v_new, torch.arange(n, dtype=torch.int32, device="cuda"), pos, Hkv, D, rope=table)
+        want = jb.attn_decode(q, pool_ref, bt, ctx, Hq, Hkv, D, 2048, rope=table)
+        got = jb.attn_decode_append(q, k_new, v_new, pool, bt, ctx, Hq, Hkv, D, 2048, counters, rope=table)
+        torch.cuda.synchronize()
+        assert torch.equal(pool, pool_ref), f"cache contents differ at step {step}"
+        assert_close(host(got), host(want), 1e-6, f"fused decode step {step}")
+        assert int(counters.abs().sum()) == 0, "counters must be left at zero"
+
+
 def test_decode_equals_prefill_last_row():
     """KV-cache decode == attention of the last query over the whole prefix (the recompute the reference does)."""
     Hq, Hkv, L = 4, 4, 200

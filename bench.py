@@ -168,7 +168,7 @@ def run_reference_arm(args):
 def workload_config(args, n):
     return {"workload": f"llama7b_decode_b{args.batch}", "layers": 32, "d_model": 4096, "heads": "32x128", "d_ffn": 11008,
             "vocab": 32000, "batch": args.batch, "prompt_len": PROMPT, "generated": GEN,
-            "parallelism": f"tp{n}", "l2": "inputs larger than L2 (13.2 GB of weights per step)"}
+            "parallelism": f"tp{n}", "exchange": ("nccl" if os.environ.get("JSM_TP_NCCL", "0") == "1" else "peer memory") if n > 1 else "none", "l2": "inputs larger than L2 (13.2 GB of weights per step)"}
 
 
 # ---- kernel-level workloads: configurations 2, 3 and 4 of the baseline ------------------------------------
@@ -338,6 +338,10 @@ def main():
                 t = t.view(torch.bfloat16)
             dist.all_reduce(t)
         model.set_allreduce(allreduce)
+        if os.environ.get("JSM_TP_NCCL", "0") != "1":
+            # the product path: the model's own exchange over peer memory (NCCL stays as the plumbing and, with
+            # JSM_TP_NCCL=1, as the comparison)
+            model.connect_peers(dist)
 
     # synthetic prompt: B sequences of PROMPT token ids, uniform in [0, vocab)
     nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
@@ -357,9 +361,11 @@ def main():
 
     # warm-up steps (eager: first-use set-up happens here), then capture one step
     launches0 = jb.launch_count()
-    for _ in range(W):
+    for i in range(W):
         model.decode_step(ids, nxt)
         ids.copy_(nxt)
+        if i == 0:
+            jb.check_device_errors()  # a bounded device-side wait that ran out (a peer that never arrived) stops the run here
     torch.cuda.synchronize()
     launches_per_step = (jb.launch_count() - launches0) // W
     if args.profile_steps > 0:
@@ -406,6 +412,7 @@ def main():
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
+    last_tokens = nxt[:8].tolist()
     if world > 1:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -488,6 +495,8 @@ def main():
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "steps": Ke},
         "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "cuda_graph": graph is not None,
         "prefill_s": prefill_s, "clocks": clock_info,
+        # greedy tokens of the last timed step (first 8 sequences): the same at every GPU count unless two logits tie
+        "last_tokens": last_tokens,
     }
     if args.layers != 32:
         line["invalid"] = "debug run with fewer layers"

@@ -306,6 +306,29 @@ typedef int (*jsm_allreduce_fn)(void* d_buf, size_t count, int dtype, void* stre
 jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_model** out);
 jsm_status jsm_llama_destroy(jsm_model* m);
 jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user);
+/* Tensor-parallel exchange over peer memory (no counterpart in the reference, which has no parallelism).
+ * Every rank owns a region [flags | buffer A | buffer B] in its own memory (jsm_llama_tp_region); the host makes the
+ * peers' regions addressable (jsm_ipc_export / jsm_ipc_import between processes of one node) and hands them to
+ * jsm_llama_tp_connect ([tp_size] device pointers, the entry of the own rank is ignored).  From then on the model sums
+ * the rank-local outputs of the attention output projection and of the FFN down projection itself: one kernel per
+ * exchange that signals the peers, waits (bounded) for them, adds all ranks' buffers in rank order, adds the sum into
+ * the residual stream and normalises.  Without a connection the all-reduce hook (jsm_llama_set_allreduce) is used. */
+jsm_status jsm_llama_tp_region(jsm_model* m, void** d_region, size_t* bytes);
+jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions);
+/* The exchange kernel on its own.  d_regions: [size] regions of jsm_tp_region_bytes(max_tokens, d) bytes, zero before
+ * the first call; d_state: I32 [2] of this rank, zero before the first call; which_buffer 0 / 1 must alternate from
+ * call to call; h (bf16 [T, d]) += sum over ranks of their buffer; xn (or NULL) = RMSNorm(h) without gain.
+ * A peer that does not arrive within the wait limit (jsm_tp_set_wait_limit_ms, default about 1 s) leaves h untouched
+ * and raises JSM_TIMEOUT at the next jsm_check_device_errors. */
+size_t jsm_tp_region_bytes(int max_tokens, int d);
+jsm_status jsm_tp_set_wait_limit_ms(int ms);
+jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
+                                     int32_t* d_state, void* d_h, void* d_xn, float eps, int T, int d, void* stream);
+/* CUDA IPC plumbing for regions that live in another process of the same node (64-byte handles). */
+jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64);
+jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr);
+jsm_status jsm_ipc_close(void* d_ptr);
+
 /* Device pointer / element count of a named weight of this rank's shard ("layers.3.wqkv", "lm_head", ...). */
 jsm_status jsm_llama_weight(jsm_model* m, const char* name, void** d_ptr, size_t* n_elems);
 /* Prefill `T` prompt tokens of sequence `seq` (positions 0..T-1); writes the argmax of the last position to d_next[seq]. */

@@ -94,6 +94,14 @@ SYMBOLS = {
     "jsm_llama_create": (_i, [C.POINTER(ModelConfig), _u64, C.POINTER(_vp)]),
     "jsm_llama_destroy": (_i, [_vp]),
     "jsm_llama_set_allreduce": (_i, [_vp, ALLREDUCE_FN, _vp]),
+    "jsm_llama_tp_region": (_i, [_vp, C.POINTER(_vp), C.POINTER(_sz)]),
+    "jsm_llama_tp_connect": (_i, [_vp, C.POINTER(_vp)]),
+    "jsm_tp_region_bytes": (_sz, [_i, _i]),
+    "jsm_tp_set_wait_limit_ms": (_i, [_i]),
+    "jsm_tp_allreduce_add_norm": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _vp, _vp, _f, _i, _i, _vp]),
+    "jsm_ipc_export": (_i, [_vp, C.c_char_p]),
+    "jsm_ipc_import": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "jsm_ipc_close": (_i, [_vp]),
     "jsm_llama_weight": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(_sz)]),
     "jsm_llama_prefill": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "jsm_llama_decode_step": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),

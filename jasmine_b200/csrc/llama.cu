@@ -22,6 +22,11 @@
 
 namespace jsm {
 
+size_t tp_region_bytes(int max_tokens, int d);
+size_t tp_buffer_offset(int which, int max_tokens, int d);
+jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, int* state, void* h, void* xn,
+                                        float eps, int T, int d, cudaStream_t st);
+
 // The projection weights are kept packed (linear_packed.cu: contiguous 16 KB tiles in stream order); the logical
 // matrices are the reference's [out, in] layout (mat_net_t.hpp:25-26).
 struct LayerW {
@@ -60,6 +65,11 @@ struct jsm_model {
     int n_counters = 0;
     int32_t* attn_counters = nullptr;  // one per (sequence, kv head) of the decode attention (self-resetting)
     std::vector<void*> allocs;
+    // tensor-parallel exchange over peer memory (tp_comm.cu): own region, the peers' regions once connected, call state
+    uint8_t* tp_region = nullptr;
+    void* tp_regions[8] = {nullptr};
+    int32_t* tp_state = nullptr;
+    bool tp_connected = false;
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
     uint64_t weight_bytes = 0;
@@ -316,17 +326,26 @@ static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_s
 // Tensor parallel: the rank-local product goes through the all-reduce, then h += sum and xn = RMSNorm(h) (the gain is
 // folded into the next projection's weights) unless `normalise` is false.
 static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K, float* stats_out,
-                                        bool normalise, cudaStream_t st) {
+                                        bool normalise, int which, cudaStream_t st) {
     const int d = m->c.d_model;
     if (m->c.tp_size == 1) {
         RowStats rs;
         rs.out = stats_out;
         return run_linear(m, X, K, Wp, N, K, LIN_RESIDUAL, m->h, m->h, false, T, st, rs);
     }
+    if (m->tp_connected) {
+        // the rank-local product goes into this call site's exchange buffer; one kernel then sums the ranks' buffers
+        // over peer memory, adds the sum into h and normalises
+        const size_t off = tp_buffer_offset(which, m->max_tokens, d);
+        jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->tp_region + off, false, T, st);
+        if (s != JSM_OK) return s;
+        return tp_allreduce_add_norm_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, off, m->tp_state, m->h, normalise ? m->xn : nullptr,
+                                            m->c.norm_eps, T, d, st);
+    }
     jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->red, false, T, st);
     if (s != JSM_OK) return s;
-    // tensor parallel: sum the rank-local outputs, then add into the residual stream
-    if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without an all-reduce callback");
+    // no peer regions connected: the host's all-reduce (NCCL) sums the rank-local outputs, then add into the residual stream
+    if (!m->allreduce) JSM_FAIL(JSM_NCCL, "tensor-parallel model without peer regions and without an all-reduce callback");
     if (m->allreduce(m->red, (size_t)T * N, JSM_BF16, st, m->allreduce_user) != 0) JSM_FAIL(JSM_NCCL, "all-reduce callback failed");
     JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, m->red, nullptr,
                                   m->c.norm_eps, normalise ? m->xn : nullptr, d));
@@ -334,9 +353,6 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
     return JSM_OK;
 }
 
-// On one GPU no normalised copy of the residual stream exists: every projection that follows an RMSNorm reads h itself
-// and scales its output rows by 1/rms (row statistics from the kernel that wrote h; gains folded into its weights).
-// Under tensor parallelism the kernel that adds the all-reduced sum into h also writes xn.
 static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool decode, int batch, int prefill_seq, cudaStream_t st) {
     const jsm_model_config& c = m->c;
     const int d = c.d_model, D = c.head_dim;
@@ -387,13 +403,13 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
                                      m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
         }
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, st);
+        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, 0, st);
         if (s != JSM_OK) return s;
         RowStats after_wo;
         if (!tp) { after_wo.in = m->ssq_a; after_wo.in_tiles = d_tiles; }
         s = run_linear(m, x_in, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st, after_wo);
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, st);
+        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, 1, st);
         if (s != JSM_OK) return s;
         if (!tp) { after_down.in = m->ssq_b; after_down.in_tiles = d_tiles; }
     }
@@ -557,6 +573,15 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->ssq0, Tm));
     JSM_TRY(dev_alloc(m, &m->ssq_a, Tm * ((d + 127) / 128)));
     JSM_TRY(dev_alloc(m, &m->ssq_b, Tm * ((d + 127) / 128)));
+    if (c.tp_size > 1) {
+        const size_t rb = tp_region_bytes(m->max_tokens, d);
+        JSM_TRY(dev_alloc(m, &m->tp_region, rb));
+        JSM_TRY(dev_alloc(m, &m->tp_state, (size_t)2));
+        if (cudaMemset(m->tp_region, 0, rb) != cudaSuccess || cudaMemset(m->tp_state, 0, 2 * sizeof(int32_t)) != cudaSuccess) {
+            jsm_llama_destroy(m);
+            JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset of the exchange region failed");
+        }
+    }
     JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
@@ -582,6 +607,26 @@ jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user
     if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_set_allreduce: null model");
     m->allreduce = fn;
     m->allreduce_user = user;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_tp_region(jsm_model* m, void** d_region, size_t* bytes) {
+    if (!m || !d_region || !bytes) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_tp_region: null argument");
+    if (!m->tp_region) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_tp_region: the model is not tensor parallel");
+    *d_region = m->tp_region;
+    *bytes = tp_region_bytes(m->max_tokens, m->c.d_model);
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions) {
+    if (!m || !d_peer_regions) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_tp_connect: null argument");
+    if (!m->tp_region) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_tp_connect: the model is not tensor parallel");
+    for (int r = 0; r < m->c.tp_size; ++r) {
+        void* p = r == m->c.tp_rank ? static_cast<void*>(m->tp_region) : d_peer_regions[r];
+        if (!p) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_tp_connect: no region for rank %d", r);
+        m->tp_regions[r] = p;
+    }
+    m->tp_connected = true;
     return JSM_OK;
 }
 

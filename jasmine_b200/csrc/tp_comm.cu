@@ -1,0 +1,215 @@
+// Tensor-parallel exchange of the decoder: the all-reduce after the attention output projection and after the FFN
+// down projection, fused with what consumes it (residual add + RMSNorm), over peer memory.
+//
+// The reference has no parallelism at all (one thread, no collectives); its heads are independent
+// (mat_mha_t.hpp:278-282) and its FFN columns are, so the split needs exactly one sum per block.
+//
+// One process per GPU.  Every rank owns a REGION in its own HBM: [flags | buffer A | buffer B].  The projection
+// writes the rank-local product [T, d] (bf16) into one of its buffers; then ONE kernel per rank
+//   1. tells every peer "my buffer is complete" by storing the call's epoch into the peer's flag word for this rank
+//      (release, system scope) and waits (acquire, bounded) until all peers have said the same,
+//   2. reads every rank's buffer - its own from HBM, the peers' over NVLink with plain peer loads - and adds them in
+//      rank order in fp32, so that all ranks compute bit-identical sums,
+//   3. adds the sum into the residual stream h (bf16) and writes xn = RMSNorm(h) for the next projection.
+// There is no second barrier: the two call sites of a layer alternate between buffer A and buffer B, and a rank can
+// only write buffer A again after it has passed the barrier of the B exchange, which every peer enters only after it
+// has finished reading A.
+// A wait that runs out (a peer that never arrives) records an error code and the kernel returns without touching h;
+// the host sees it through jsm_check_device_errors.  No in-switch reduction and no multicast objects are involved:
+// a rank that leaves cannot fault its peers' GPUs.
+#include "tc_utils.cuh"
+#include <math.h>
+
+namespace jsm {
+
+constexpr int TP_MAX_RANKS = 8;
+constexpr size_t TP_FLAG_BYTES = 1024;
+constexpr int TP_TIMEOUT_CODE = 16;  // error word code of an exchange whose peers did not arrive in time
+
+static long long g_tp_wait_limit_cycles = 2000000000ll;  // about one second
+
+struct TpArgs {
+    uint8_t* regions[TP_MAX_RANKS];  // regions[rank] is the local one
+    int rank, size;
+    size_t buf_offset;  // of the buffer of this call inside a region
+    int* state;         // local: [0] epoch of the last finished call, [1] CTAs of this call that are done
+    __nv_bfloat16* h;   // [T, d] residual stream (updated in place)
+    __nv_bfloat16* xn;  // [T, d] normalised copy, or null
+    float eps;
+    int d;
+    int* err;
+    long long wait_limit;
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// one CTA per token, d <= 256 * 8 * MAXV
+template <int MAXV>
+__global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
+    __shared__ float red[8];
+    __shared__ int ok_s;
+    chain_trigger();
+    chain_wait();  // this rank's projection has written its buffer
+    const int E = *reinterpret_cast<volatile int*>(a.state) + 1;
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < a.size) {
+        const int r = threadIdx.x;
+        if (blockIdx.x == 0 && r != a.rank) st_release_sys(reinterpret_cast<int*>(a.regions[r]) + a.rank, E);
+        if (r != a.rank) {
+            const int* flag = reinterpret_cast<const int*>(a.regions[a.rank]) + r;
+            const long long t0 = clock64();
+            while (ld_acquire_sys(flag) < E) {
+                if (clock64() - t0 > a.wait_limit) {
+                    ok_s = 0;
+                    if (a.err) atomicCAS(a.err, 0, TP_TIMEOUT_CODE);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const bool ok = ok_s != 0;
+    const long long base = (long long)blockIdx.x * a.d;
+    if (ok) {
+        float v[MAXV][8];
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int c = (i * 256 + threadIdx.x) * 8;
+            if (c < a.d) {
+                float s[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s[j] = 0.0f;
+                for (int r = 0; r < a.size; ++r) {  // rank order: every rank forms the same sum
+                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.regions[r] + a.buf_offset) + base + c;
+                    const uint4 w = (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : ld_relaxed_sys_v4(src);
+                    s[0] += bf16lo(w.x); s[1] += bf16hi(w.x); s[2] += bf16lo(w.y); s[3] += bf16hi(w.y);
+                    s[4] += bf16lo(w.z); s[5] += bf16hi(w.z); s[6] += bf16lo(w.w); s[7] += bf16hi(w.w);
+                }
+                const uint4 hw = *reinterpret_cast<const uint4*>(a.h + base + c);
+                const float hv[8] = {bf16lo(hw.x), bf16hi(hw.x), bf16lo(hw.y), bf16hi(hw.y), bf16lo(hw.z), bf16hi(hw.z), bf16lo(hw.w), bf16hi(hw.w)};
+                uint4 o;
+                // the rank-local products were rounded to bf16 when they were stored; the sum is rounded once more, like
+                // the all-reduce of a bf16 buffer followed by the residual add
+                uint32_t sb[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sb[j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
+                o.x = pack_bf16x2(hv[0] + bf16lo(sb[0]), hv[1] + bf16hi(sb[0]));
+                o.y = pack_bf16x2(hv[2] + bf16lo(sb[1]), hv[3] + bf16hi(sb[1]));
+                o.z = pack_bf16x2(hv[4] + bf16lo(sb[2]), hv[5] + bf16hi(sb[2]));
+                o.w = pack_bf16x2(hv[6] + bf16lo(sb[3]), hv[7] + bf16hi(sb[3]));
+                *reinterpret_cast<uint4*>(a.h + base + c) = o;
+                v[i][0] = bf16lo(o.x); v[i][1] = bf16hi(o.x); v[i][2] = bf16lo(o.y); v[i][3] = bf16hi(o.y);
+                v[i][4] = bf16lo(o.z); v[i][5] = bf16hi(o.z); v[i][6] = bf16lo(o.w); v[i][7] = bf16hi(o.w);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q += v[i][j] * v[i][j];
+            }
+        }
+        if (a.xn) {
+            q = warp_sum(q);
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) tot += red[w];
+            const float sd = sqrtf(tot / (float)a.d + a.eps);
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i) {
+                const int c = (i * 256 + threadIdx.x) * 8;
+                if (c < a.d) {
+                    uint4 w;
+                    w.x = pack_bf16x2(v[i][0] / sd, v[i][1] / sd); w.y = pack_bf16x2(v[i][2] / sd, v[i][3] / sd);
+                    w.z = pack_bf16x2(v[i][4] / sd, v[i][5] / sd); w.w = pack_bf16x2(v[i][6] / sd, v[i][7] / sd);
+                    *reinterpret_cast<uint4*>(a.xn + base + c) = w;
+                }
+            }
+        }
+    }
+    // the call is over when its last CTA is: only then does the epoch advance (every CTA read it at its start)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(a.state + 1, 1);
+        if (old == (int)gridDim.x - 1) {
+            a.state[1] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile int*>(a.state) = E;
+        }
+    }
+}
+
+size_t tp_region_bytes(int max_tokens, int d) { return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16); }
+size_t tp_buffer_offset(int which, int max_tokens, int d) { return TP_FLAG_BYTES + (size_t)(which & 1) * max_tokens * d * sizeof(__nv_bfloat16); }
+
+jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, int* state, void* h, void* xn,
+                                        float eps, int T, int d, cudaStream_t st) {
+    if (T <= 0) return JSM_OK;
+    if (!regions || !state || !h) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: null pointer");
+    if (size < 1 || size > TP_MAX_RANKS || rank < 0 || rank >= size) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: rank %d of %d", rank, size);
+    if (d % 8 || d > 256 * 8 * 2) JSM_FAIL(JSM_UNSUPPORTED, "tp_allreduce: d %d (multiple of 8, at most 4096)", d);
+    TpArgs a;
+    for (int r = 0; r < TP_MAX_RANKS; ++r) a.regions[r] = r < size ? reinterpret_cast<uint8_t*>(regions[r]) : nullptr;
+    for (int r = 0; r < size; ++r)
+        if (!a.regions[r]) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: region of rank %d is not connected", r);
+    a.rank = rank; a.size = size; a.buf_offset = buf_offset; a.state = state;
+    a.h = reinterpret_cast<__nv_bfloat16*>(h); a.xn = reinterpret_cast<__nv_bfloat16*>(xn);
+    a.eps = eps; a.d = d; a.err = tc_error_word(); a.wait_limit = g_tp_wait_limit_cycles;
+    JSM_CUDA_CHECK(launch_chained(tp_allreduce_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, a));
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+}  // namespace jsm
+
+using namespace jsm;
+
+extern "C" size_t jsm_tp_region_bytes(int max_tokens, int d) {
+    if (max_tokens <= 0 || d <= 0) return 0;
+    return tp_region_bytes(max_tokens, d);
+}
+
+extern "C" jsm_status jsm_tp_set_wait_limit_ms(int ms) {
+    if (ms <= 0 || ms > 60000) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_set_wait_limit_ms: %d", ms);
+    g_tp_wait_limit_cycles = (long long)ms * 2000000ll;  // about 2 GHz
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
+                                                int32_t* d_state, void* d_h, void* d_xn, float eps, int T, int d, void* stream) {
+    if (T > max_tokens) JSM_FAIL(JSM_SHAPE, "jsm_tp_allreduce_add_norm: %d tokens, the region holds %d", T, max_tokens);
+    return tp_allreduce_add_norm_launch(d_regions, rank, size, tp_buffer_offset(which_buffer, max_tokens, d), d_state, d_h, d_xn, eps, T, d,
+                                        as_stream(stream));
+}
+
+extern "C" jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64) {
+    if (!d_ptr || !handle64) JSM_FAIL(JSM_INVALID_ARG, "jsm_ipc_export: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    JSM_CUDA_CHECK(cudaIpcGetMemHandle(&h, const_cast<void*>(d_ptr)));
+    memcpy(handle64, &h, 64);
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr) {
+    if (!handle64 || !d_ptr) JSM_FAIL(JSM_INVALID_ARG, "jsm_ipc_import: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    JSM_CUDA_CHECK(cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_ipc_close(void* d_ptr) {
+    if (!d_ptr) return JSM_OK;
+    JSM_CUDA_CHECK(cudaIpcCloseMemHandle(d_ptr));
+    return JSM_OK;
+}

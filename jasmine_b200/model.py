@@ -41,6 +41,29 @@ class Llama:
         self._cb = ALLREDUCE_FN(tramp)
         check(lib().jsm_llama_set_allreduce(self._h, self._cb, None))
 
+    def connect_peers(self, dist) -> None:
+        """Makes the exchange regions of all ranks of one node addressable from this rank (CUDA IPC handles passed
+        through torch.distributed) and switches the model to its own all-reduce over peer memory."""
+        rank, world = self.cfg.tp_rank, self.cfg.tp_size
+        p, n = C.c_void_p(), C.c_size_t()
+        check(lib().jsm_llama_tp_region(self._h, C.byref(p), C.byref(n)))
+        handle = C.create_string_buffer(64)
+        check(lib().jsm_ipc_export(p, handle))
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw)
+        ptrs = (C.c_void_p * world)()
+        self._peer_ptrs = []
+        for r in range(world):
+            if r == rank:
+                ptrs[r] = p.value
+                continue
+            q = C.c_void_p()
+            check(lib().jsm_ipc_import(C.create_string_buffer(handles[r], 64), C.byref(q)))
+            ptrs[r] = q.value
+            self._peer_ptrs.append(q)
+        check(lib().jsm_llama_tp_connect(self._h, ptrs))
+        dist.barrier()
+
     def weight(self, name: str) -> np.ndarray:
         """A weight of this rank's shard as float32 (bf16 tensors are widened)."""
         p, n = C.c_void_p(), C.c_size_t()

@@ -1,0 +1,87 @@
+"""GPU check of the tensor-parallel exchange kernel (sum of the ranks' buffers + residual add + RMSNorm) on ONE GPU:
+the "ranks" are regions of the same device and every flag a kernel waits for has been set by the host before the
+launch, so no kernel ever waits for another kernel.  The multi-GPU path itself runs in bench.py --gpus N."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import jasmine_b200 as jb
+from gpu_util import assert_close, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def make_regions(n, max_tokens, d):
+    nbytes = jb.lib().jsm_tp_region_bytes(max_tokens, d)
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(n)]
+    ptrs = (C.c_void_p * n)(*[r.data_ptr() for r in regions])
+    return regions, ptrs
+
+
+def buffer_view(region, which, max_tokens, d):
+    off = 1024 + which * max_tokens * d * 2
+    return region[off:off + max_tokens * d * 2].view(torch.bfloat16).view(max_tokens, d)
+
+
+def set_flags(regions, epoch):
+    for r in regions:
+        r[:64].view(torch.int32).fill_(epoch)
+
+
+@pytest.mark.parametrize("n,T,d", [(2, 8, 4096), (4, 5, 512), (8, 64, 1024), (3, 1, 256)])
+def test_exchange_sums_in_rank_order_adds_and_normalises(n, T, d):
+    max_tokens = 64
+    regions, ptrs = make_regions(n, max_tokens, d)
+    states = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(n)]
+    h0 = dev(cases.normal((T, d), 900, 0), torch.bfloat16)
+    eps = 1e-5
+    for call in range(3):                      # buffers A, B, A: epochs 1, 2, 3
+        which = call % 2
+        parts = [dev(cases.normal((T, d), 901 + call, r), torch.bfloat16) for r in range(n)]
+        for r in range(n):
+            buffer_view(regions[r], which, max_tokens, d)[:T] = parts[r]
+        set_flags(regions, call + 1)           # every peer has "arrived" before any kernel starts
+        s = torch.zeros(T, d, device="cuda")
+        for r in range(n):
+            s = s + parts[r].float()
+        want_h = (h0.float() + s.to(torch.bfloat16).float()).to(torch.bfloat16)
+        want_xn = want_h.float() / torch.sqrt((want_h.float() ** 2).mean(dim=1, keepdim=True) + eps)
+        outs = []
+        for r in range(n):
+            h = h0.clone()
+            xn = torch.empty_like(h)
+            jb.check(jb.lib().jsm_tp_allreduce_add_norm(ptrs, r, n, which, max_tokens, states[r].data_ptr(), h.data_ptr(),
+                                                         xn.data_ptr(), eps, T, d, jb.stream_ptr()))
+            outs.append((h, xn))
+        jb.check_device_errors()
+        for r, (h, xn) in enumerate(outs):
+            assert torch.equal(h, outs[0][0]), f"rank {r} differs from rank 0"
+            assert_close(host(h), host(want_h), 1e-2, f"h of rank {r}, call {call}")   # one bf16 ulp of the sum order
+            assert_close(host(xn), host(want_xn), 1e-2, f"xn of rank {r}, call {call}")
+            assert int(states[r][0]) == call + 1 and int(states[r][1]) == 0
+        h0 = outs[0][0]
+
+
+def test_exchange_gives_up_when_a_peer_never_arrives():
+    """A flag that nothing sets: the wait runs out after the (shortened) limit, h stays untouched and the host reads the
+    error; the context stays usable."""
+    n, T, d, max_tokens = 2, 4, 512, 16
+    regions, ptrs = make_regions(n, max_tokens, d)
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    h = dev(cases.normal((T, d), 910, 0), torch.bfloat16)
+    before = h.clone()
+    jb.check(jb.lib().jsm_tp_set_wait_limit_ms(20))
+    try:
+        jb.check(jb.lib().jsm_tp_allreduce_add_norm(ptrs, 0, n, 0, max_tokens, state.data_ptr(), h.data_ptr(), None, 1e-5, T, d,
+                                                     jb.stream_ptr()))
+        with pytest.raises(jb.JsmError) as e:
+            jb.check_device_errors()
+        assert e.value.status == jb.TIMEOUT
+        assert torch.equal(h, before)
+        jb.check_device_errors()                # the error word was cleared; the device still answers
+        assert int(torch.ones(4, device="cuda").sum()) == 4
+    finally:
+        jb.check(jb.lib().jsm_tp_set_wait_limit_ms(1000))

@@ -287,6 +287,51 @@ def run_kernel_workload(args):
         emit("kv_decode_attention_GBps", timed(lambda _: jb.attn_decode(q, pool, bt, ctx, Hq, Hkv, D, max_ctx, scratch=scratch, out=out)), "hbm", kv_bytes, hbm, "GB/s", cfg)
 
 
+def run_timeline(args):
+    """Device timeline of the packed projections of one eager decode step (jsm_trace_begin / jsm_trace_end): for every
+    projection kind the time its CTAs were resident before their predecessor finished, the main loop, the tail (last
+    MMA issued -> last CTA done), and the gap the kernels between two projections leave.  Text output, not a bench line."""
+    import numpy as np
+    import torch
+    import jasmine_b200 as jb
+    from jasmine_b200.model import Llama
+    torch.cuda.set_device(0)
+    B, L = args.batch, min(args.layers, 8)
+    m = Llama(L, 4096, 32, 32, 11008, 32000, max_batch=B, max_context=PROMPT + 128, seed=SEED)
+    nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+    for b in range(B):
+        ids = torch.empty(PROMPT, dtype=torch.int32, device="cuda")
+        jb.fill(ids, SEED, 5000 + b, 2, 0, 32000)
+        m.prefill(ids, b, nxt)
+    ids = nxt.clone()
+    for _ in range(3):
+        m.decode_step(ids, nxt)
+        ids.copy_(nxt)
+    torch.cuda.synchronize()
+    n_max = 4 * L + 1
+    jb.check(jb.lib().jsm_trace_begin(n_max))
+    m.decode_step(ids, nxt)
+    torch.cuda.synchronize()
+    buf = np.zeros((n_max, 148, 8), np.uint64)
+    n, ctas = C.c_int(), C.c_int()
+    jb.check(jb.lib().jsm_trace_end(buf.ctypes.data, n_max, C.byref(n), C.byref(ctas)))
+    t = buf[:n.value].astype(np.int64)
+    valid = t[:, :, 0] > 0
+    names = ["qkv", "wo", "gate/up", "down"]
+    mid = range(4, 4 * L - 4)
+    print(f"# timeline of one eager decode step, batch {B}, {L} layers of the 7B shape, context {PROMPT + 4}; times in us")
+    print("# projection  resident_before_wait  wait->first_stages_landed  wait->last_mma_issued  tail  wait->end  gap_before")
+    ends = [t[i][valid[i]][:, 7].max() for i in range(n.value)]
+    for k in range(4):
+        sel = [i for i in mid if i % 4 == k]
+        f = lambda fn: float(np.mean([fn(t[i][valid[i]], i) for i in sel])) / 1e3
+        print(f"{names[k]:10s} {f(lambda x, i: x[:, 2].min() - x[:, 0].min()):8.1f} {f(lambda x, i: x[:, 3].max() - x[:, 2].min()):8.1f} "
+              f"{f(lambda x, i: x[:, 4].max() - x[:, 2].min()):8.1f} {f(lambda x, i: x[:, 7].max() - x[:, 4].max()):8.1f} "
+              f"{f(lambda x, i: x[:, 7].max() - x[:, 2].min()):8.1f} {f(lambda x, i: x[:, 2].min() - ends[i - 1]):8.1f}")
+    per_layer = [(ends[4 * (l + 1) + 3] - ends[4 * l + 3]) / 1e3 for l in range(L - 1)]
+    print("# per-layer time (us):", " ".join(f"{v:.1f}" for v in per_layer))
+
+
 # ---- the GPU arm --------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -297,7 +342,7 @@ def main():
     ap.add_argument("--impl", default="jasmine_b200")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode", "gateup"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode", "gateup", "timeline"],
                     help="decode = the headline; expr / flash / kvdecode = configurations 2 / 3 / 4 of the baseline "
                          "(kernel-level lines, one JSON line per kernel)")
     ap.add_argument("--profile-steps", type=int, default=0,
@@ -307,6 +352,8 @@ def main():
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.workload == "timeline":
+        return run_timeline(args)
     if args.workload != "decode":
         return run_kernel_workload(args)
 

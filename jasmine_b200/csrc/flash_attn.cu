@@ -205,15 +205,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         for (int j = 0; j < n_tiles[t] && ok; ++j) {
             if (!mbar_wait(&s_full[t], j & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
             tc_fence_after();
+            // the whole score row of this thread: four TMEM loads in flight, one wait
+            uint32_t sr[FA_BN];
+#pragma unroll
+            for (int c = 0; c < FA_BN; c += 32) tmem_ld32(s_addr + c, reinterpret_cast<uint32_t(&)[32]>(sr[c]));
+            tmem_ld_wait();
             float sv[FA_BN];
 #pragma unroll
-            for (int c = 0; c < FA_BN; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + c, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]);
-            }
+            for (int i = 0; i < FA_BN; ++i) sv[i] = __uint_as_float(sr[i]);
             const int key0 = j * FA_BN;
             const bool needs_mask = (P.causal && key0 + FA_BN - 1 > q0 + t * FA_BM + shift) || key0 + FA_BN > P.Tk;
             if (needs_mask) {
@@ -222,9 +221,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                     if ((P.causal && key0 + i > qpos) || key0 + i >= P.Tk) sv[i] = -INFINITY;
             }
             // scores stay unscaled in registers; the scale (> 0, log2 domain) is applied inside the exponent's FMA
-            float mx = sv[0];
+            // eight independent chains instead of one 127-deep dependency chain (two warps per scheduler: the row needs ILP)
+            float mxs[8];
 #pragma unroll
-            for (int i = 1; i < FA_BN; ++i) mx = fmaxf(mx, sv[i]);
+            for (int k = 0; k < 8; ++k) mxs[k] = sv[k];
+#pragma unroll
+            for (int i = 8; i < FA_BN; i += 8)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) mxs[k] = fmaxf(mxs[k], sv[i + k]);
+            float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
             mx *= P.scale_log2;
             // tcgen05.ld / st are warp-collective: the decision to touch the accumulator is taken per warp,
             // each lane then applies its own factor (1 for the rows whose maximum did not move)
@@ -253,7 +258,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 }
             }
             // p = 2^(s - m_ref), packed to bf16 pairs, written over the first 64 columns of S
-            float lsum = 0.0f;
+            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const float neg_m = -m_ref, sc = P.scale_log2;
 #pragma unroll
             for (int c = 0; c < FA_BN / 2; c += 16) {
@@ -261,11 +266,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float p0 = ex2_approx(fmaf(sv[2 * (c + i)], sc, neg_m)), p1 = ex2_approx(fmaf(sv[2 * (c + i) + 1], sc, neg_m));
-                    lsum += p0 + p1;
+                    ls[i & 3] += p0 + p1;
                     w[i] = pack_bf16x2(p0, p1);
                 }
                 tmem_st16(s_addr + c, w);
             }
+            const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
             l += lsum;
             tmem_st_wait();
             tc_fence_before();

@@ -16,7 +16,8 @@
 // (a counter per tile) adds the slots in slot order, so the sum does not depend on the arrival order, and runs the
 // epilogue.  All SMs stream the same number of bytes whatever the shape.
 //
-// Kernel roles (192 threads): warp 0 producer (bulk copies of W, TMA tiles of X), warp 1 MMA issuer
+// Kernel roles (224 threads): warp 0 streams W (bulk copies), warp 6 the tiles of X (TMA): two issuing threads, because a
+// thread's rate of copy requests, not the bytes in flight, bounds the stream; warp 1 MMA issuer
 // (tcgen05.mma 128 x BN x 16, accumulators in TMEM, two accumulator buffers so that the epilogue of one segment
 // overlaps the MMAs of the next), warps 2-5 epilogue (tcgen05.ld, one TMEM lane = one packed row per thread).
 // Chained launches: the W stream does not depend on the predecessor kernel, so the first ring of W tiles is
@@ -32,7 +33,7 @@ namespace jsm {
 using namespace tc;
 
 constexpr int PK_TILE_BYTES = 128 * 64 * 2;  // one packed unit: 128 rows x 64 k, bf16
-constexpr int PK_THREADS = 192;
+constexpr int PK_THREADS = 224;
 constexpr int PK_MAX_STAGES = 12;
 
 __device__ __forceinline__ float pk_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], 2);  // the W producer and the X producer each arrive with their bytes
             mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 while (u < u_end && pre < stages) {
                     const int kb0 = (int)(u % P.kbt);
                     const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
-                    mbar_expect_tx(&full_bar[pre], (uint32_t)n * (PK_TILE_BYTES + B_BYTES));
+                    mbar_expect_tx(&full_bar[pre], (uint32_t)n * PK_TILE_BYTES);
                     bulk_load(tiles + (size_t)pre * STAGE_BYTES, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES,
                               &full_bar[pre]);
                     u += n;
@@ -166,17 +167,6 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 }
             }
             PK_TRACE(1);  // first ring of W requested
-            chain_wait();
-            PK_TRACE(2);  // predecessor complete
-            u = u_begin;
-            for (int i = 0; i < pre; ++i) {
-                const int kb0 = (int)(u % P.kbt);
-                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
-                uint8_t* xs = tiles + (size_t)i * STAGE_BYTES + X_OFF;
-                if (n == 2) tma_load_3d(xs, &tmap_x2, 0, 0, kb0, &full_bar[i]);
-                else tma_load_2d(xs, &tmap_x, kb0 * 64, 0, &full_bar[i]);
-                u += n;
-            }
             int i = pre, issued = pre;
             while (u < u_end) {
                 const int s = i % stages;
@@ -184,11 +174,8 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
                 const int kb0 = (int)(u % P.kbt);
                 const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
-                uint8_t* st = tiles + (size_t)s * STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], (uint32_t)n * (PK_TILE_BYTES + B_BYTES));
-                bulk_load(st, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES, &full_bar[s]);
-                if (n == 2) tma_load_3d(st + X_OFF, &tmap_x2, 0, 0, kb0, &full_bar[s]);
-                else tma_load_2d(st + X_OFF, &tmap_x, kb0 * 64, 0, &full_bar[s]);
+                mbar_expect_tx(&full_bar[s], (uint32_t)n * PK_TILE_BYTES);
+                bulk_load(tiles + (size_t)s * STAGE_BYTES, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES, &full_bar[s]);
                 u += n;
                 ++i;
                 issued = i;
@@ -197,6 +184,27 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 const long long t_start = clock64();
                 for (int j = max(0, issued - stages); j < issued; ++j)
                     while (!mbar_try_wait(&full_bar[j % stages], (j / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
+            }
+        }
+    } else if (warp == 6) {
+        // ---- X producer: the token blocks of every stage, once the predecessor kernel has written them --------------
+        if (lane == 0) {
+            chain_wait();
+            PK_TRACE(2);  // predecessor complete
+            long long u = u_begin;
+            int i = 0;
+            while (u < u_end) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
+                const int kb0 = (int)(u % P.kbt);
+                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
+                uint8_t* xs = tiles + (size_t)s * STAGE_BYTES + X_OFF;
+                mbar_expect_tx(&full_bar[s], (uint32_t)n * B_BYTES);
+                if (n == 2) tma_load_3d(xs, &tmap_x2, 0, 0, kb0, &full_bar[s]);
+                else tma_load_2d(xs, &tmap_x, kb0 * 64, 0, &full_bar[s]);
+                u += n;
+                ++i;
             }
         }
     } else if (warp == 1) {

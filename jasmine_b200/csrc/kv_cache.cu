@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include <math.h>
 #include <mutex>
+#include <stdlib.h>
 
 namespace jsm {
 
@@ -27,7 +28,13 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 // Context positions per CTA: small batches get short chunks so that the grid still fills the GPU
 // (chunks x kv heads x sequences CTAs); always a multiple of the 32 positions a CTA covers per step.
-__host__ __device__ inline int decode_chunk(int n_seqs, int Hq) {
+inline int decode_chunk(int n_seqs, int Hq) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("JSM_DEC_CHUNK");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced >= 32 && forced % 32 == 0) return forced;
     const int work = n_seqs * Hq;
     return work >= 512 ? DEC_CHUNK_MAX : work >= 128 ? 256 : work >= 32 ? 128 : 64;
 }
@@ -145,21 +152,33 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     const int32_t* bt = block_table + (long long)seq * max_pages;
     constexpr int STEP = 2 * DEC_UNROLL;  // keys per warp step
 
-    for (int base = c_begin + warp * STEP; base < c_end; base += DEC_WARPS * STEP) {
-        const int page = bt[base / JSM_PAGE_SIZE];
-        const __nv_bfloat16* kp = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + base % JSM_PAGE_SIZE) * D;
-        uint4 kw[DEC_UNROLL], vw[DEC_UNROLL];
+    // the K and V rows of one warp step (8 keys); the next step's rows are requested before this step's arithmetic so that
+    // the memory round trips of consecutive steps overlap
+    auto fetch = [&](int base, uint4 (&kw)[DEC_UNROLL], uint4 (&vw)[DEC_UNROLL]) {
+        if (base < c_end) {
+            const int page = bt[base / JSM_PAGE_SIZE];
+            const __nv_bfloat16* kp = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + base % JSM_PAGE_SIZE) * D;
 #pragma unroll
-        for (int u = 0; u < DEC_UNROLL; ++u) {
-            const int key = base + 2 * u + ks;
-            if (key < c_end) {
-                kw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + (long long)(2 * u + ks) * D + dsub));
-                vw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + v_off + (long long)(2 * u + ks) * D + dsub));
-            } else {
-                kw[u] = make_uint4(0, 0, 0, 0);
-                vw[u] = make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < DEC_UNROLL; ++u) {
+                const int key = base + 2 * u + ks;
+                if (key < c_end) {
+                    kw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + (long long)(2 * u + ks) * D + dsub));
+                    vw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + v_off + (long long)(2 * u + ks) * D + dsub));
+                } else {
+                    kw[u] = make_uint4(0, 0, 0, 0);
+                    vw[u] = make_uint4(0, 0, 0, 0);
+                }
             }
         }
+    };
+    uint4 kw[DEC_UNROLL], vw[DEC_UNROLL], kw_next[DEC_UNROLL], vw_next[DEC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) kw_next[u] = vw_next[u] = make_uint4(0, 0, 0, 0);
+    fetch(c_begin + warp * STEP, kw_next, vw_next);
+    for (int base = c_begin + warp * STEP; base < c_end; base += DEC_WARPS * STEP) {
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) { kw[u] = kw_next[u]; vw[u] = vw_next[u]; }
+        fetch(base + DEC_WARPS * STEP, kw_next, vw_next);
         float s[DEC_UNROLL][G];
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) {

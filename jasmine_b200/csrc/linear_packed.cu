@@ -26,6 +26,7 @@
 #include "linear_bf16.cuh"
 #include <math.h>
 #include <mutex>
+#include <algorithm>
 #include <stdlib.h>
 
 namespace jsm {
@@ -66,6 +67,7 @@ struct PkParams {
     int w_early;          // weights may be fetched before the predecessor kernel has finished
     int pf_units;         // units beyond the ring that are prefetched into L2 up front
     int stages;
+    int cluster_s;        // > 1: aligned split, the cluster_s CTAs of a tile form a cluster and fold through shared memory
     int pair_ok;          // K is a multiple of 64: two k-blocks of X can be fetched as one 3-D tile
     const float* ssq_in;  // [ssq_in_tiles][ssq_stride] per-tile sums of squares of X's rows (null: X is used as it is)
     int ssq_in_tiles;
@@ -90,12 +92,28 @@ __host__ __device__ inline long long pk_begin(long long c, long long U, long lon
 // CTA that owns unit u: the largest c with c*U/G <= u
 __host__ __device__ inline int pk_owner(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
 
+// ---- thread-block cluster helpers: the CTAs that share a tile exchange their partials through distributed shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta_rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 // Units of the stream a stage holds: two consecutive k-blocks of one tile when the segment has two left (one 32 KB
 // request instead of two of 16 KB: the copy engine's rate of requests, not the bytes in flight, bounds a CTA's stream),
 // else one.  Producer and MMA issuer walk the same sequence.
 __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok && left >= 2) ? 2 : 1; }
 
-template <int BN>
+// CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it
+template <int BN, bool CL = (BN >= 32)>
 __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -186,6 +204,11 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                     while (!mbar_try_wait(&full_bar[j % stages], (j / stages) & 1) && clock64() - t_start < WAIT_LIMIT_CYCLES) {}
             }
         }
+        if (CL && P.cluster_s > 1) {  // every thread of the cluster takes part in its two barriers (see the epilogue)
+            __syncwarp();
+            cluster_sync_all();
+            cluster_sync_all();
+        }
     } else if (warp == 6) {
         // ---- X producer: the token blocks of every stage, once the predecessor kernel has written them --------------
         if (lane == 0) {
@@ -206,6 +229,11 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 u += n;
                 ++i;
             }
+        }
+        if (CL && P.cluster_s > 1) {
+            __syncwarp();
+            cluster_sync_all();
+            cluster_sync_all();
         }
     } else if (warp == 1) {
         // ---- MMA issuer ------------------------------------------------------------------------------------
@@ -249,6 +277,11 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
             }
             PK_TRACE(4);  // last MMA issued
         }
+        if (CL && P.cluster_s > 1) {
+            __syncwarp();
+            cluster_sync_all();
+            cluster_sync_all();
+        }
     } else {
         // ---- epilogue: warps 2..5 own the TMEM lane quadrants warp % 4 ------------------------------------------
         const int quad = warp & 3;
@@ -256,7 +289,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
         const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
         const bool want_ssq = P.ssq_out != nullptr;  // plain tiles only (checked on the host)
         bool ok = true, waited = false;
-        int seg = 0;
+        int seg = 0, cl_syncs = 0;  // cluster barriers this thread has taken part in (two per CTA, whatever happens)
         long long u = u_begin;
         while (u < u_end && ok) {
             const int tile = (int)(u / P.kbt);
@@ -365,6 +398,10 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                 const int c_first = pk_owner(uf, U, G), c_last = pk_owner(uf + P.kbt - 1, U, G);
                 const int n_contrib = c_last - c_first + 1;
                 const int slot = (int)blockIdx.x - c_first;
+                // aligned split: the contributors are the CTAs of this cluster and the partial goes to this CTA's own shared
+                // memory (the stage ring is free: every MMA of the CTA has completed); otherwise to its workspace slot
+                const bool cl = CL && P.cluster_s > 1;
+                float* part_smem = reinterpret_cast<float*>(tiles);
                 float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * (size_t)P.T * 128;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -373,25 +410,41 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                     tmem_ld16(acc_addr + c0, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j < P.T) __stcg(wbase + (size_t)(c0 + j) * 128 + row, __uint_as_float(r[j]));
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < P.T) {
+                            if (cl) part_smem[(c0 + j) * 128 + row] = __uint_as_float(r[j]);
+                            else __stcg(wbase + (size_t)(c0 + j) * 128 + row, __uint_as_float(r[j]));
+                        }
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the MMA warp may reuse the buffer while the fold runs
-                // release / acquire through the tile counter: the barrier orders every thread's partial stores before the
-                // release of thread 0, and its acquire before every thread's loads of the other CTAs' slots
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (etid == 0) {
-                    int old;
-                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(P.counters + tile) : "memory");
-                    const int last = (old == n_contrib - 1);
-                    if (last) P.counters[tile] = 0;  // ready for the next launch
-                    is_last_smem[seg & 1] = last;
+                int t_lo = 0, t_hi = P.T;
+                bool do_fold;
+                if (cl) {
+                    // first cluster barrier: every CTA's partial is in place.  CTA `slot` then folds its share of the tokens
+                    // reading all partials in slot order; the second barrier keeps the shared memory alive until all have read.
+                    cluster_sync_all();
+                    ++cl_syncs;
+                    t_lo = (int)((long long)slot * P.T / n_contrib);
+                    t_hi = (int)((long long)(slot + 1) * P.T / n_contrib);
+                    do_fold = true;
+                } else {
+                    // release / acquire through the tile counter: the barrier orders every thread's partial stores before the
+                    // release of thread 0, and its acquire before every thread's loads of the other CTAs' slots
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (etid == 0) {
+                        int old;
+                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(P.counters + tile) : "memory");
+                        const int last = (old == n_contrib - 1);
+                        if (last) P.counters[tile] = 0;  // ready for the next launch
+                        is_last_smem[seg & 1] = last;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    do_fold = is_last_smem[seg & 1] != 0;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const bool is_last = is_last_smem[seg & 1] != 0;
-                if (is_last) {
+                if (do_fold) {
                     // A thread owns 4 consecutive output features of every TS-th token; the partials of four tokens are in
                     // flight at once and the slots are added in slot order.  Plain tiles: a warp shares its tokens (32 groups
                     // of 4 features), so the per-token sum of squares is one warp reduction.
@@ -402,7 +455,8 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                     const float* tbase = P.ws + (size_t)tile * P.max_slots * (size_t)P.T * 128;
                     const size_t slot_stride = (size_t)P.T * 128;
                     const float4 bias4 = (P.bias && !P.paired && valid) ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int tb = tsub; tb < P.T; tb += 4 * TS) {  // warp-uniform trip count for plain tiles
+                    const uint32_t part_addr = smem_u32(part_smem);
+                    for (int tb = t_lo + tsub; tb < t_hi; tb += 4 * TS) {  // warp-uniform trip count for plain tiles
                         float4 g[4], up[4];
                         uint2 rr[4];
 #pragma unroll
@@ -411,7 +465,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                             up[i] = g[i];
                             rr[i] = make_uint2(0u, 0u);
                             const int t = tb + TS * i;
-                            if (P.epilogue == LIN_RESIDUAL && valid && t < P.T) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                            if (P.epilogue == LIN_RESIDUAL && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
                         }
                         if (valid) {
 #pragma unroll 4
@@ -419,14 +473,19 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const int t = tb + TS * i;
-                                    if (t < P.T) {
-                                        const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
-                                        const float4 a = __ldcg(reinterpret_cast<const float4*>(w));
-                                        g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
-                                        if (P.paired) {
-                                            const float4 c = __ldcg(reinterpret_cast<const float4*>(w + 64));
-                                            up[i].x += c.x; up[i].y += c.y; up[i].z += c.z; up[i].w += c.w;
+                                    if (t < t_hi) {
+                                        float4 a, c = make_float4(0.f, 0.f, 0.f, 0.f);
+                                        if (cl) {
+                                            const uint32_t ra = dsmem_addr(part_addr, (uint32_t)z) + (uint32_t)(t * 128 + f4) * 4u;
+                                            a = ld_dsmem_f4(ra);
+                                            if (P.paired) c = ld_dsmem_f4(ra + 256u);
+                                        } else {
+                                            const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
+                                            a = __ldcg(reinterpret_cast<const float4*>(w));
+                                            if (P.paired) c = __ldcg(reinterpret_cast<const float4*>(w + 64));
                                         }
+                                        g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
+                                        up[i].x += c.x; up[i].y += c.y; up[i].z += c.z; up[i].w += c.w;
                                     }
                                 }
                             }
@@ -434,7 +493,7 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int t = tb + TS * i;
-                            if (t >= P.T) break;
+                            if (t >= t_hi) break;
                             const float sc = scaled ? row_scale[t] : 1.0f;
                             float v[4] = {g[i].x * sc + bias4.x, g[i].y * sc + bias4.y, g[i].z * sc + bias4.z, g[i].w * sc + bias4.w};
                             const float uu[4] = {up[i].x * sc, up[i].y * sc, up[i].z * sc, up[i].w * sc};
@@ -465,11 +524,14 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                         }
                     }
                 }
+                if (cl) { cluster_sync_all(); ++cl_syncs; }
             }
             if (etid == 0) PK_TRACE(5 + (seg > 1 ? 1 : seg));  // end of the first / of the last segment's epilogue
             u += len;
             ++seg;
         }
+        if (CL && P.cluster_s > 1)
+            for (; cl_syncs < 2; ++cl_syncs) cluster_sync_all();  // a CTA that gave up on a wait must not leave its peers waiting
     }
     tc_fence_before();
     __syncthreads();
@@ -530,35 +592,65 @@ jsm_status linear_pack_launch(const void* W, int N, int K, int paired, void* pac
     return JSM_OK;
 }
 
-int linear_packed_grid(int N, int K, int paired) {
+// Work split of a launch with T tokens.  Few tokens (T < 32): the fold of a shared tile is a short chain of round trips,
+// so SM coverage decides: the even split of the whole stream, or, with few tiles, every tile over the same number of
+// CTAs when that still occupies four fifths of the SMs.  Many tokens: the fold's volume grows with T, so whole tiles
+// (no fold at all) or an aligned split whose CTAs fold through distributed shared memory win as soon as they occupy
+// three fifths of the SMs.
+int linear_packed_grid(int N, int K, int paired, int T) {
     int nt, kbt;
     pk_dims(N, K, paired, &nt, &kbt);
     const long long U = (long long)nt * kbt;
     long long G = sm_count();
-    // few tiles: split every tile over the same number of CTAs (one segment, one fold per CTA) when that still
-    // occupies at least four fifths of the SMs; otherwise the even split of the whole stream
     if (nt < G) {
         const long long S = G / nt;
-        if (nt * S * 5 >= G * 4 && kbt >= S) G = nt * S;
+        const long long need_num = T >= 32 ? 3 : 4;  // fifths of the SMs
+        if (nt * S * 5 >= G * need_num && kbt >= S) G = nt * S;
     }
     if (U < 4 * G) G = U / 4;  // at least four units per CTA
     if (G < 1) G = 1;
     return (int)G;
 }
 
-int linear_packed_slots(int N, int K, int paired) {
+// > 1 when the grid is the aligned split (every tile shared by the same power-of-two number of consecutive CTAs) and
+// the launch has enough tokens for the exchange to matter: those CTAs are launched as one thread-block cluster and fold
+// their partials through distributed shared memory
+int linear_packed_cluster(int N, int K, int paired, int T) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("JSM_PK_CLUSTER");
+        enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (!enabled || T < 32) return 0;
     int nt, kbt;
     pk_dims(N, K, paired, &nt, &kbt);
-    const long long U = (long long)nt * kbt, G = linear_packed_grid(N, K, paired);
+    const int G = linear_packed_grid(N, K, paired, T);
+    if (G % nt) return 0;
+    const int S = G / nt;
+    if (S != 2 && S != 4 && S != 8) return 0;
+    if ((long long)nt * kbt / G < 1) return 0;
+    return S;
+}
+
+static int slots_for_grid(int nt, int kbt, long long G) {
+    const long long U = (long long)nt * kbt;
     // a tile of kbt units is covered by at most ceil(kbt / floor(U/G)) + 1 consecutive CTA ranges
     const long long per = U / G > 0 ? U / G : 1;
     return (int)((kbt + per - 1) / per + 1);
 }
 
+int linear_packed_slots(int N, int K, int paired, int T) {
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    return slots_for_grid(nt, kbt, linear_packed_grid(N, K, paired, T));
+}
+
+// enough for every launch of at most T tokens (the split depends on the token count)
 size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
     int nt, kbt;
     pk_dims(N, K, paired, &nt, &kbt);
-    return (size_t)nt * linear_packed_slots(N, K, paired) * (size_t)T * 128;
+    const int slots = std::max(linear_packed_slots(N, K, paired, 1), linear_packed_slots(N, K, paired, 64));
+    return (size_t)nt * slots * (size_t)T * 128;
 }
 
 // ---- optional timeline of the packed projections (a profiling aid; off unless jsm_trace_begin was called) ----------
@@ -566,7 +658,7 @@ static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
 template <int BN>
-static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, bool chained, cudaStream_t st) {
+static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
     static int budget_kb = -1;
@@ -594,25 +686,32 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
                                             227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
-    if (chained) {
-        // L2 prefetch beyond the ring: JSM_PF_MB megabytes per launch over all CTAs (off by default: it measured slower than the ring alone)
-        static long long pf_mb = -1;
-        if (pf_mb < 0) {
-            const char* e = getenv("JSM_PF_MB");
-            pf_mb = e ? atoll(e) : 0;
-            if (pf_mb < 0) pf_mb = 0;
-        }
-        long long pf = (pf_mb << 20) / ((long long)PK_TILE_BYTES * grid);
-        P.pf_units = (int)(pf > 128 ? 128 : pf);
-        P.w_early = 1;
-        JSM_CUDA_CHECK(launch_chained(linear_packed_kernel<BN>, dim3(grid), dim3(PK_THREADS), smem, st, mx, mx2, P));
-        g_launches.fetch_add(1);
-        return JSM_OK;
-    }
-    P.w_early = 0;
+    P.w_early = chained ? 1 : 0;
     P.pf_units = 0;
-    linear_packed_kernel<BN><<<grid, PK_THREADS, smem, st>>>(mx, mx2, P);
-    JSM_LAUNCH_CHECK();
+    P.cluster_s = cluster > 1 ? cluster : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(PK_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (chained && chained_launch_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (cluster > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = (unsigned)cluster;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN>, mx, mx2, P));
+    g_launches.fetch_add(1);
     return JSM_OK;
 }
 
@@ -632,13 +731,13 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     pk_dims(a.N, a.K, paired, &P.n_tiles, &P.kbt);
     P.paired = paired; P.epilogue = a.epilogue; P.out_f32 = a.out_f32 ? 1 : 0;
     P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y; P.Wp = (const uint8_t*)a.Wp;
-    const int grid = linear_packed_grid(a.N, a.K, paired);
-    P.max_slots = linear_packed_slots(a.N, a.K, paired);
+    const int grid = linear_packed_grid(a.N, a.K, paired, a.T);
+    P.max_slots = linear_packed_slots(a.N, a.K, paired, a.T);
     const long long U = (long long)P.n_tiles * P.kbt;
     const bool shared_tiles = (U % grid) != 0 || ((U / grid) % P.kbt) != 0;
     if (shared_tiles) {
         if (!a.ws || !a.counters) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace and counters are required");
-        if (linear_packed_ws_floats(a.T, a.N, a.K, paired) > a.ws_floats)
+        if ((size_t)P.n_tiles * P.max_slots * (size_t)a.T * 128 > a.ws_floats)
             JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace of %zu floats, %zu needed", a.ws_floats,
                      linear_packed_ws_floats(a.T, a.N, a.K, paired));
         if (P.n_tiles > a.n_counters) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: %d tile counters, %d needed", a.n_counters, P.n_tiles);
@@ -662,12 +761,13 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         if (s != JSM_OK) return s;
         if (a.K / 64 < 2) P.pair_ok = 0;
     }
+    const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
     switch (bn) {
-        case 16: return launch_packed<16>(mx, mx2, P, grid, a.chained, st);
-        case 32: return launch_packed<32>(mx, mx2, P, grid, a.chained, st);
-        case 64: return launch_packed<64>(mx, mx2, P, grid, a.chained, st);
-        case 128: return launch_packed<128>(mx, mx2, P, grid, a.chained, st);
-        default: return launch_packed<256>(mx, mx2, P, grid, a.chained, st);
+        case 16: return launch_packed<16>(mx, mx2, P, grid, cluster, a.chained, st);
+        case 32: return launch_packed<32>(mx, mx2, P, grid, cluster, a.chained, st);
+        case 64: return launch_packed<64>(mx, mx2, P, grid, cluster, a.chained, st);
+        case 128: return launch_packed<128>(mx, mx2, P, grid, cluster, a.chained, st);
+        default: return launch_packed<256>(mx, mx2, P, grid, cluster, a.chained, st);
     }
 }
 
@@ -715,8 +815,8 @@ extern "C" jsm_status jsm_trace_end(uint64_t* h_stamps, int max_launches, int* n
 extern "C" jsm_status jsm_linear_packed_plan(int N, int K, int paired, int* n_tiles, int* kbt, int* grid, int* max_slots) {
     if (N <= 0 || K <= 0 || !n_tiles || !kbt || !grid || !max_slots) JSM_FAIL(JSM_INVALID_ARG, "jsm_linear_packed_plan: bad argument");
     pk_dims(N, K, paired ? 1 : 0, n_tiles, kbt);
-    *grid = linear_packed_grid(N, K, paired ? 1 : 0);
-    *max_slots = linear_packed_slots(N, K, paired ? 1 : 0);
+    *grid = linear_packed_grid(N, K, paired ? 1 : 0, 1);
+    *max_slots = linear_packed_slots(N, K, paired ? 1 : 0, 1);
     return JSM_OK;
 }
 

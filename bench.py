@@ -297,7 +297,23 @@ def run_timeline(args):
     from jasmine_b200.model import Llama
     torch.cuda.set_device(0)
     B, L = args.batch, min(args.layers, 8)
-    m = Llama(L, 4096, 32, 32, 11008, 32000, max_batch=B, max_context=PROMPT + 128, seed=SEED)
+    tp = max(1, args.tp_emulate)
+    m = Llama(L, 4096, 32, 32, 11008, 32000, max_batch=B, max_context=PROMPT + 128, seed=SEED, tp_rank=0, tp_size=tp)
+    if tp > 1:
+        # one rank of a tensor-parallel group on one GPU: the peers are zero-filled regions of this device whose flags
+        # already say "arrived" (no kernel waits for another one); the kernels and their shapes are those of a real
+        # rank, the results are not (the peers contribute zeros), the NVLink round trips are absent
+        p, nb = C.c_void_p(), C.c_size_t()
+        jb.check(jb.lib().jsm_llama_tp_region(m._h, C.byref(p), C.byref(nb)))
+        fakes = [torch.zeros(nb.value, dtype=torch.uint8, device="cuda") for _ in range(tp - 1)]
+        ptrs = (C.c_void_p * tp)()
+        ptrs[0] = p.value
+        for r in range(1, tp):
+            ptrs[r] = fakes[r - 1].data_ptr()
+        flags = torch.full((16,), 1 << 30, dtype=torch.int32)
+        jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 64, jb.stream_ptr()))
+        torch.cuda.synchronize()
+        jb.check(jb.lib().jsm_llama_tp_connect(m._h, ptrs))
     nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
     for b in range(B):
         ids = torch.empty(PROMPT, dtype=torch.int32, device="cuda")
@@ -345,6 +361,8 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode", "gateup", "timeline"],
                     help="decode = the headline; expr / flash / kvdecode = configurations 2 / 3 / 4 of the baseline "
                          "(kernel-level lines, one JSON line per kernel)")
+    ap.add_argument("--tp-emulate", type=int, default=1,
+                    help="timeline workload only: run ONE rank of a tensor-parallel group of this size on one GPU")
     ap.add_argument("--profile-steps", type=int, default=0,
                     help="run this many eager decode steps between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off); prints no bench line")

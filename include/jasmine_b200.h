@@ -316,14 +316,17 @@ jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user
 jsm_status jsm_llama_tp_region(jsm_model* m, void** d_region, size_t* bytes);
 jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions);
 /* The exchange kernel on its own.  d_regions: [size] regions of jsm_tp_region_bytes(max_tokens, d) bytes, zero before
- * the first call; d_state: I32 [2] of this rank, zero before the first call; which_buffer 0 / 1 must alternate from
- * call to call; h (bf16 [T, d]) += sum over ranks of their buffer; xn (or NULL) = RMSNorm(h) without gain.
+ * the first call; which_buffer 0 / 1 must alternate from call to call; the call's epoch is
+ * (*d_pass) * n_sites + site + 1 and must grow from call to call, identically on every rank (d_pass: I32 in device
+ * memory, written before the launch); h (bf16 [T, d]) += sum over ranks of their buffer; xn (or NULL) = RMSNorm(h)
+ * without gain.
  * A peer that does not arrive within the wait limit (jsm_tp_set_wait_limit_ms, default about 1 s) leaves h untouched
  * and raises JSM_TIMEOUT at the next jsm_check_device_errors. */
 size_t jsm_tp_region_bytes(int max_tokens, int d);
 jsm_status jsm_tp_set_wait_limit_ms(int ms);
 jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
-                                     int32_t* d_state, void* d_h, void* d_xn, float eps, int T, int d, void* stream);
+                                     const int32_t* d_pass, int site, int n_sites, void* d_h, void* d_xn, float eps,
+                                     int T, int d, void* stream);
 /* CUDA IPC plumbing for regions that live in another process of the same node (64-byte handles). */
 jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64);
 jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr);

@@ -603,11 +603,24 @@ int linear_packed_grid(int N, int K, int paired, int T) {
     const long long U = (long long)nt * kbt;
     long long G = sm_count();
     if (nt < G) {
-        const long long S = G / nt;
-        const long long need_num = T >= 32 ? 3 : 4;  // fifths of the SMs
-        if (nt * S * 5 >= G * need_num && kbt >= S) G = nt * S;
+        long long S = G / nt;  // CTAs per tile of the aligned split
+        bool use;
+        if (T >= 32) {
+            // a power of two up to 8 (the cluster that folds through shared memory), from half of the SMs on
+            S = S >= 8 ? 8 : S >= 4 ? 4 : S >= 2 ? 2 : 1;
+            use = nt * S * 2 >= G;
+        } else {
+            // at most 8 contributors per tile (the fold reads every slot); from four fifths of the SMs on, or whenever the
+            // even split of the stream would put more than 8 CTAs on a tile
+            const bool capped = S > 8;
+            if (capped) S = 8;
+            use = capped || nt * S * 5 >= G * 4;
+        }
+        if (S > kbt) S = kbt;
+        if (use && S >= 1) G = nt * S;
     }
-    if (U < 4 * G) G = U / 4;  // at least four units per CTA
+    if (U < 4 * G && T < 32) G = U / 4;  // at least four units per CTA
+    if (G > U) G = U;
     if (G < 1) G = 1;
     return (int)G;
 }

@@ -24,8 +24,8 @@ namespace jsm {
 
 size_t tp_region_bytes(int max_tokens, int d);
 size_t tp_buffer_offset(int which, int max_tokens, int d);
-jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, int* state, void* h, void* xn,
-                                        float eps, int T, int d, cudaStream_t st);
+jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, const int* pass, int site,
+                                        int n_sites, void* h, void* xn, float eps, int T, int d, cudaStream_t st);
 
 // The projection weights are kept packed (linear_packed.cu: contiguous 16 KB tiles in stream order); the logical
 // matrices are the reference's [out, in] layout (mat_net_t.hpp:25-26).
@@ -127,18 +127,21 @@ __global__ void fill_shard_kernel(__nv_bfloat16* dst, long long rows, long long 
 __global__ void fill_const_kernel(float* dst, long long n, float v) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = v;
 }
-__global__ void iota_kernel(int32_t* pos, int32_t* seq_ids, int T, int seq, int pos0) {
+// pass: number of the forward pass (the epoch base of the tensor-parallel exchanges), bumped by the first kernel of a pass
+__global__ void iota_kernel(int32_t* pos, int32_t* seq_ids, int T, int seq, int pos0, int32_t* pass) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < T) { pos[i] = pos0 + i; seq_ids[i] = seq; }
+    if (i == 0 && pass) *pass = *pass + 1;
 }
 __global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = value; }
 // decode bookkeeping on the device so that a captured step can be replayed: the new token of
 // sequence b goes to position ctx[b], then the context grows by one
-__global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch) {
+__global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch, int32_t* pass) {
     chain_trigger();
     chain_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch) { pos[b] = ctx[b]; seq_ids[b] = b; ctx[b] = ctx[b] + 1; }
+    if (b == 0 && pass) *pass = *pass + 1;
 }
 
 __device__ __forceinline__ float block_sum_256(float v, float* smem) {
@@ -326,7 +329,7 @@ static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_s
 // Tensor parallel: the rank-local product goes through the all-reduce, then h += sum and xn = RMSNorm(h) (the gain is
 // folded into the next projection's weights) unless `normalise` is false.
 static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K, float* stats_out,
-                                        bool normalise, int which, cudaStream_t st) {
+                                        bool normalise, int which, int site, cudaStream_t st) {
     const int d = m->c.d_model;
     if (m->c.tp_size == 1) {
         RowStats rs;
@@ -339,8 +342,8 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
         const size_t off = tp_buffer_offset(which, m->max_tokens, d);
         jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->tp_region + off, false, T, st);
         if (s != JSM_OK) return s;
-        return tp_allreduce_add_norm_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, off, m->tp_state, m->h, normalise ? m->xn : nullptr,
-                                            m->c.norm_eps, T, d, st);
+        return tp_allreduce_add_norm_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, off, m->tp_state, site, 2 * m->c.n_layers, m->h,
+                                            normalise ? m->xn : nullptr, m->c.norm_eps, T, d, st);
     }
     jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->red, false, T, st);
     if (s != JSM_OK) return s;
@@ -403,13 +406,13 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
                                      m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
         }
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, 0, st);
+        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, 0, 2 * l, st);
         if (s != JSM_OK) return s;
         RowStats after_wo;
         if (!tp) { after_wo.in = m->ssq_a; after_wo.in_tiles = d_tiles; }
         s = run_linear(m, x_in, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st, after_wo);
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, 1, st);
+        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, 1, 2 * l + 1, st);
         if (s != JSM_OK) return s;
         if (!tp) { after_down.in = m->ssq_b; after_down.in_tiles = d_tiles; }
     }
@@ -675,7 +678,7 @@ jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T,
     if (seq < 0 || seq >= m->c.max_batch) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_prefill: sequence %d outside 0..%d", seq, m->c.max_batch - 1);
     if (T <= 0 || T > m->max_tokens || T > m->c.max_context) JSM_FAIL(JSM_SHAPE, "jsm_llama_prefill: %d tokens (1..%d)", T, m->max_tokens);
     cudaStream_t st = as_stream(stream);
-    iota_kernel<<<(T + 255) / 256, 256, 0, st>>>(m->pos, m->seq_ids, T, seq, 0);
+    iota_kernel<<<(T + 255) / 256, 256, 0, st>>>(m->pos, m->seq_ids, T, seq, 0, m->tp_state);
     JSM_LAUNCH_CHECK();
     jsm_status s = forward_tokens(m, d_ids, T, false, 1, seq, st);
     if (s != JSM_OK) return s;
@@ -688,7 +691,7 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step: null argument");
     if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step: batch %d (1..%d)", batch, m->c.max_batch);
     cudaStream_t st = as_stream(stream);
-    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch));
+    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch, m->tp_state));
     JSM_LAUNCH_CHECK();
     jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
     if (s != JSM_OK) return s;

@@ -11,6 +11,9 @@
 //   2. reads every rank's buffer - its own from HBM, the peers' over NVLink with plain peer loads - and adds them in
 //      rank order in fp32, so that all ranks compute bit-identical sums,
 //   3. adds the sum into the residual stream h (bf16) and writes xn = RMSNorm(h) for the next projection.
+// The epoch of a call is (number of the forward pass) * (exchanges per pass) + (index of the exchange) + 1: every rank
+// runs the same sequence, the pass number lives in device memory (graph replays see it change) and is bumped by the
+// first kernel of the pass, so the exchange kernel neither counts nor publishes anything itself.
 // There is no second barrier: the two call sites of a layer alternate between buffer A and buffer B, and a rank can
 // only write buffer A again after it has passed the barrier of the B exchange, which every peer enters only after it
 // has finished reading A.
@@ -32,7 +35,8 @@ struct TpArgs {
     uint8_t* regions[TP_MAX_RANKS];  // regions[rank] is the local one
     int rank, size;
     size_t buf_offset;  // of the buffer of this call inside a region
-    int* state;         // local: [0] epoch of the last finished call, [1] CTAs of this call that are done
+    const int* pass;    // local: number of the forward pass (bumped by the pass's first kernel, long before this one runs)
+    int site, n_sites;  // exchange `site` of `n_sites` per forward pass: the call's epoch is pass * n_sites + site + 1
     __nv_bfloat16* h;   // [T, d] residual stream (updated in place)
     __nv_bfloat16* xn;  // [T, d] normalised copy, or null
     float eps;
@@ -59,8 +63,9 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
     __shared__ float red[8];
     __shared__ int ok_s;
     chain_trigger();
+    // the epoch needs no hand-shake inside the kernel: every rank runs the same sequence of passes and sites
+    const int E = *reinterpret_cast<const volatile int*>(a.pass) * a.n_sites + a.site + 1;
     chain_wait();  // this rank's projection has written its buffer
-    const int E = *reinterpret_cast<volatile int*>(a.state) + 1;
     if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
     if (threadIdx.x < a.size) {
@@ -88,14 +93,25 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
         for (int i = 0; i < MAXV; ++i) {
             const int c = (i * 256 + threadIdx.x) * 8;
             if (c < a.d) {
+                // all ranks' loads are issued before the first add (one NVLink round trip, not one per rank); the adds run in
+                // rank order: every rank forms the same sum
+                uint4 w[TP_MAX_RANKS];
+#pragma unroll
+                for (int r = 0; r < TP_MAX_RANKS; ++r) {
+                    if (r < a.size) {
+                        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.regions[r] + a.buf_offset) + base + c;
+                        w[r] = (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : ld_relaxed_sys_v4(src);
+                    }
+                }
                 float s[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) s[j] = 0.0f;
-                for (int r = 0; r < a.size; ++r) {  // rank order: every rank forms the same sum
-                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(a.regions[r] + a.buf_offset) + base + c;
-                    const uint4 w = (r == a.rank) ? *reinterpret_cast<const uint4*>(src) : ld_relaxed_sys_v4(src);
-                    s[0] += bf16lo(w.x); s[1] += bf16hi(w.x); s[2] += bf16lo(w.y); s[3] += bf16hi(w.y);
-                    s[4] += bf16lo(w.z); s[5] += bf16hi(w.z); s[6] += bf16lo(w.w); s[7] += bf16hi(w.w);
+#pragma unroll
+                for (int r = 0; r < TP_MAX_RANKS; ++r) {
+                    if (r < a.size) {
+                        s[0] += bf16lo(w[r].x); s[1] += bf16hi(w[r].x); s[2] += bf16lo(w[r].y); s[3] += bf16hi(w[r].y);
+                        s[4] += bf16lo(w[r].z); s[5] += bf16hi(w[r].z); s[6] += bf16lo(w[r].w); s[7] += bf16hi(w[r].w);
+                    }
                 }
                 const uint4 hw = *reinterpret_cast<const uint4*>(a.h + base + c);
                 const float hv[8] = {bf16lo(hw.x), bf16hi(hw.x), bf16lo(hw.y), bf16hi(hw.y), bf16lo(hw.z), bf16hi(hw.z), bf16lo(hw.w), bf16hi(hw.w)};
@@ -136,32 +152,23 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
             }
         }
     }
-    // the call is over when its last CTA is: only then does the epoch advance (every CTA read it at its start)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(a.state + 1, 1);
-        if (old == (int)gridDim.x - 1) {
-            a.state[1] = 0;
-            __threadfence();
-            *reinterpret_cast<volatile int*>(a.state) = E;
-        }
-    }
 }
 
 size_t tp_region_bytes(int max_tokens, int d) { return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16); }
 size_t tp_buffer_offset(int which, int max_tokens, int d) { return TP_FLAG_BYTES + (size_t)(which & 1) * max_tokens * d * sizeof(__nv_bfloat16); }
 
-jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, int* state, void* h, void* xn,
-                                        float eps, int T, int d, cudaStream_t st) {
+jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, const int* pass, int site,
+                                        int n_sites, void* h, void* xn, float eps, int T, int d, cudaStream_t st) {
     if (T <= 0) return JSM_OK;
-    if (!regions || !state || !h) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: null pointer");
+    if (!regions || !pass || !h) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: null pointer");
+    if (n_sites < 1 || site < 0 || site >= n_sites) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: site %d of %d", site, n_sites);
     if (size < 1 || size > TP_MAX_RANKS || rank < 0 || rank >= size) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: rank %d of %d", rank, size);
     if (d % 8 || d > 256 * 8 * 2) JSM_FAIL(JSM_UNSUPPORTED, "tp_allreduce: d %d (multiple of 8, at most 4096)", d);
     TpArgs a;
     for (int r = 0; r < TP_MAX_RANKS; ++r) a.regions[r] = r < size ? reinterpret_cast<uint8_t*>(regions[r]) : nullptr;
     for (int r = 0; r < size; ++r)
         if (!a.regions[r]) JSM_FAIL(JSM_INVALID_ARG, "tp_allreduce: region of rank %d is not connected", r);
-    a.rank = rank; a.size = size; a.buf_offset = buf_offset; a.state = state;
+    a.rank = rank; a.size = size; a.buf_offset = buf_offset; a.pass = pass; a.site = site; a.n_sites = n_sites;
     a.h = reinterpret_cast<__nv_bfloat16*>(h); a.xn = reinterpret_cast<__nv_bfloat16*>(xn);
     a.eps = eps; a.d = d; a.err = tc_error_word(); a.wait_limit = g_tp_wait_limit_cycles;
     JSM_CUDA_CHECK(launch_chained(tp_allreduce_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, a));
@@ -185,10 +192,11 @@ extern "C" jsm_status jsm_tp_set_wait_limit_ms(int ms) {
 }
 
 extern "C" jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
-                                                int32_t* d_state, void* d_h, void* d_xn, float eps, int T, int d, void* stream) {
+                                                const int32_t* d_pass, int site, int n_sites, void* d_h, void* d_xn, float eps, int T,
+                                                int d, void* stream) {
     if (T > max_tokens) JSM_FAIL(JSM_SHAPE, "jsm_tp_allreduce_add_norm: %d tokens, the region holds %d", T, max_tokens);
-    return tp_allreduce_add_norm_launch(d_regions, rank, size, tp_buffer_offset(which_buffer, max_tokens, d), d_state, d_h, d_xn, eps, T, d,
-                                        as_stream(stream));
+    return tp_allreduce_add_norm_launch(d_regions, rank, size, tp_buffer_offset(which_buffer, max_tokens, d), d_pass, site, n_sites, d_h,
+                                        d_xn, eps, T, d, as_stream(stream));
 }
 
 extern "C" jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64) {

@@ -8,6 +8,7 @@
 // the whole row in registers between the reduction and the write, so each
 // operand is read once and the result written once.
 #include "common.cuh"
+#include <stdlib.h>
 #include <math.h>
 #include <string.h>
 
@@ -233,8 +234,9 @@ __device__ __forceinline__ float group_sum(float v, float* smem) {
         if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
         __syncthreads();
         v = 0.0f;
+        const int g0 = (threadIdx.x / GROUP) * (GROUP / 32);  // first warp of this row's group
 #pragma unroll
-        for (int w = 0; w < GROUP / 32; ++w) v += smem[w];
+        for (int w = 0; w < GROUP / 32; ++w) v += smem[g0 + w];
     }
     return v;
 }
@@ -245,9 +247,10 @@ __device__ __forceinline__ float group_max(float v, float* smem) {
         __syncthreads();
         if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
         __syncthreads();
-        v = smem[0];
+        const int g0 = (threadIdx.x / GROUP) * (GROUP / 32);
+        v = smem[g0];
 #pragma unroll
-        for (int w = 1; w < GROUP / 32; ++w) v = fmaxf(v, smem[w]);
+        for (int w = 1; w < GROUP / 32; ++w) v = fmaxf(v, smem[g0 + w]);
     }
     return v;
 }
@@ -265,10 +268,11 @@ __device__ __forceinline__ void group_argmax(float& v, int& idx, float* smem) {
         __syncthreads();
         if ((threadIdx.x & 31) == 0) { smem[threadIdx.x >> 5] = v; ismem[threadIdx.x >> 5] = idx; }
         __syncthreads();
-        v = smem[0]; idx = ismem[0];
+        const int g0 = (threadIdx.x / GROUP) * (GROUP / 32);
+        v = smem[g0]; idx = ismem[g0];
 #pragma unroll
         for (int w = 1; w < GROUP / 32; ++w) {
-            float ov = smem[w]; int oi = ismem[w];
+            float ov = smem[g0 + w]; int oi = ismem[g0 + w];
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
     }
@@ -705,7 +709,16 @@ jsm_status jsm_eval_rows(int kind, int axis, const jsm_instr* prog, int n_instr,
         else if (C <= 512) launch_rows<32, 4>(Lw, A, st);
         else if (C <= 1024) launch_rows<256, 1>(Lw, A, st);
         else if (C <= 2048) launch_rows<256, 2>(Lw, A, st);
-        else if (C <= 4096) launch_rows<256, 4>(Lw, A, st);
+        else if (C <= 4096) {
+            static int g = -1;
+            if (g < 0) {
+                const char* e = getenv("JSM_ROWS_GROUP");
+                g = e ? atoi(e) : 256;
+            }
+            if (g == 128) launch_rows<128, 8>(Lw, A, st);
+            else if (g == 64) launch_rows<64, 16>(Lw, A, st);
+            else launch_rows<256, 4>(Lw, A, st);
+        }
         else launch_rows<256, 8>(Lw, A, st);
     } else {
         const unsigned lines = (unsigned)(axis == 1 ? Lw.R : Lw.C);

@@ -709,16 +709,7 @@ jsm_status jsm_eval_rows(int kind, int axis, const jsm_instr* prog, int n_instr,
         else if (C <= 512) launch_rows<32, 4>(Lw, A, st);
         else if (C <= 1024) launch_rows<256, 1>(Lw, A, st);
         else if (C <= 2048) launch_rows<256, 2>(Lw, A, st);
-        else if (C <= 4096) {
-            static int g = -1;
-            if (g < 0) {
-                const char* e = getenv("JSM_ROWS_GROUP");
-                g = e ? atoi(e) : 256;
-            }
-            if (g == 128) launch_rows<128, 8>(Lw, A, st);
-            else if (g == 64) launch_rows<64, 16>(Lw, A, st);
-            else launch_rows<256, 4>(Lw, A, st);
-        }
+        else if (C <= 4096) launch_rows<256, 4>(Lw, A, st);  // fewer threads per row (128 x 8, 64 x 16 values) measured 25-60 % slower
         else launch_rows<256, 8>(Lw, A, st);
     } else {
         const unsigned lines = (unsigned)(axis == 1 ? Lw.R : Lw.C);

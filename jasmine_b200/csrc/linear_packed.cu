@@ -113,7 +113,7 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
 __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok && left >= 2) ? 2 : 1; }
 
 // CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it
-template <int BN, bool CL = (BN >= 32)>
+template <int BN, bool CL>
 __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -634,7 +634,12 @@ int linear_packed_cluster(int N, int K, int paired, int T) {
         const char* e = getenv("JSM_PK_CLUSTER");
         enabled = (e && e[0] == '0') ? 0 : 1;
     }
-    if (!enabled || T < 32) return 0;
+    static int min_t = -1;
+    if (min_t < 0) {
+        const char* e = getenv("JSM_PK_CLUSTER_MIN_T");
+        min_t = e ? atoi(e) : 32;
+    }
+    if (!enabled || T < min_t) return 0;
     int nt, kbt;
     pk_dims(N, K, paired, &nt, &kbt);
     const int G = linear_packed_grid(N, K, paired, T);
@@ -670,7 +675,7 @@ size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
 static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
-template <int BN>
+template <int BN, bool CL>
 static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
@@ -693,9 +698,9 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaFuncAttributes fa;
-        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN>));
+        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL>));
         // 227 KB per CTA in all: what the kernel's static arrays leave is open to the stage ring
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
@@ -723,7 +728,7 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN>, mx, mx2, P));
+    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL>, mx, mx2, P));
     g_launches.fetch_add(1);
     return JSM_OK;
 }
@@ -775,13 +780,18 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         if (a.K / 64 < 2) P.pair_ok = 0;
     }
     const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
+    // the cluster path lives in instantiations of its own: launches without a cluster run a kernel that carries none of it
+#define PK_GO(BN_)                                                                                  \
+    return cluster > 1 ? launch_packed<BN_, true>(mx, mx2, P, grid, cluster, a.chained, st)        \
+                       : launch_packed<BN_, false>(mx, mx2, P, grid, cluster, a.chained, st)
     switch (bn) {
-        case 16: return launch_packed<16>(mx, mx2, P, grid, cluster, a.chained, st);
-        case 32: return launch_packed<32>(mx, mx2, P, grid, cluster, a.chained, st);
-        case 64: return launch_packed<64>(mx, mx2, P, grid, cluster, a.chained, st);
-        case 128: return launch_packed<128>(mx, mx2, P, grid, cluster, a.chained, st);
-        default: return launch_packed<256>(mx, mx2, P, grid, cluster, a.chained, st);
+        case 16: PK_GO(16);
+        case 32: PK_GO(32);
+        case 64: PK_GO(64);
+        case 128: PK_GO(128);
+        default: PK_GO(256);
     }
+#undef PK_GO
 }
 
 // ---- per-device workspace of the public entry point -------------------------------------------------------------

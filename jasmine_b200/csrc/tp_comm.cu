@@ -63,9 +63,9 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
     __shared__ float red[8];
     __shared__ int ok_s;
     chain_trigger();
+    chain_wait();  // this rank's projection has written its buffer (and, before it, the pass counter was bumped)
     // the epoch needs no hand-shake inside the kernel: every rank runs the same sequence of passes and sites
     const int E = *reinterpret_cast<const volatile int*>(a.pass) * a.n_sites + a.site + 1;
-    chain_wait();  // this rank's projection has written its buffer
     if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
     if (threadIdx.x < a.size) {

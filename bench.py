@@ -544,6 +544,30 @@ def main():
     k_ms = r0.elapsed_time(r1) / reps
     alg_bytes = 2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+    # the same kernel inside the step (chained launches: its ring is full of weights when its predecessor ends): device
+    # time stamps of one eager step, predecessor end -> last CTA done, mean over the gate/up launches of the layers
+    in_step = None
+    if world == 1 and cfg["n_layers"] >= 4:
+        import numpy as np
+        n_max = 4 * cfg["n_layers"] + 1
+        jb.check(jb.lib().jsm_trace_begin(n_max))
+        model.decode_step(ids, nxt)
+        torch.cuda.synchronize()
+        buf = np.zeros((n_max, 148, 8), np.uint64)
+        n_tr, n_ctas = C.c_int(), C.c_int()
+        jb.check(jb.lib().jsm_trace_end(buf.ctypes.data, n_max, C.byref(n_tr), C.byref(n_ctas)))
+        tr = buf[:n_tr.value].astype(np.int64)
+        spans = []
+        for i in range(6, n_tr.value - 1, 4):  # launch 4l+2 of layer l is the gate/up projection
+            v = tr[i][tr[i][:, 0] > 0]
+            if len(v):
+                spans.append((v[:, 7].max() - v[:, 2].min()) / 1e6)
+        if spans:
+            ms_in = float(np.mean(spans))
+            in_step = {"ms_per_launch": ms_in, "achieved": (2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2) / (ms_in * 1e-3) / 1e9,
+                       "how": "device time stamps (globaltimer) of one eager decode step: predecessor kernel finished -> last "
+                              "CTA of the gate/up projection done, mean over the layers"}
+            in_step["frac"] = in_step["achieved"] / peak
     wbytes, kv_per_tok = model.step_bytes()
     step_bytes = wbytes + B * ctx_mid * kv_per_tok
     step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
@@ -557,7 +581,9 @@ def main():
                      "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape at 8 tokens "
                                      "from one ncu capture (profiles/linear_packed_gate_up_b8_ncu.md); algorithmic bytes_per_launch beside it",
                      "kernel": "linear_packed_kernel: gate/up projection weight stream (jsm_linear_bf16_packed, silu*up epilogue)",
-                     "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes},
+                     "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes,
+                     "timed": "isolated launches of the kernel (CUDA events, 96 launches over 4 rotating weight sets)",
+                     "in_step": in_step},
         "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_gbs, "frac": step_gbs / peak,
                           "note": "all weights + cached K/V of the step over the measured step time"},
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "steps": Ke},

@@ -114,7 +114,7 @@ __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok
 
 // CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it
 template <int BN, bool CL>
-__global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(PK_THREADS, (BN >= 32 && BN <= 64) ? 2 : 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int B_BYTES = BN * 128;  // BN tokens x 64 k, bf16
@@ -467,25 +467,58 @@ __global__ void __launch_bounds__(PK_THREADS, BN <= 64 ? 2 : 1)
                             const int t = tb + TS * i;
                             if (P.epilogue == LIN_RESIDUAL && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
                         }
-                        if (valid) {
+                        if (valid && cl) {
+                            // shared-memory partials of the cluster: short latency, four tokens in flight, adds in slot order
 #pragma unroll 4
                             for (int z = 0; z < n_contrib; ++z) {
+                                const uint32_t zbase = dsmem_addr(part_addr, (uint32_t)z);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const int t = tb + TS * i;
                                     if (t < t_hi) {
-                                        float4 a, c = make_float4(0.f, 0.f, 0.f, 0.f);
-                                        if (cl) {
-                                            const uint32_t ra = dsmem_addr(part_addr, (uint32_t)z) + (uint32_t)(t * 128 + f4) * 4u;
-                                            a = ld_dsmem_f4(ra);
-                                            if (P.paired) c = ld_dsmem_f4(ra + 256u);
-                                        } else {
-                                            const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
-                                            a = __ldcg(reinterpret_cast<const float4*>(w));
-                                            if (P.paired) c = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                        const uint32_t ra = zbase + (uint32_t)(t * 128 + f4) * 4u;
+                                        const float4 av = ld_dsmem_f4(ra);
+                                        g[i].x += av.x; g[i].y += av.y; g[i].z += av.z; g[i].w += av.w;
+                                        if (P.paired) {
+                                            const float4 cv = ld_dsmem_f4(ra + 256u);
+                                            up[i].x += cv.x; up[i].y += cv.y; up[i].z += cv.z; up[i].w += cv.w;
                                         }
-                                        g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
-                                        up[i].x += c.x; up[i].y += c.y; up[i].z += c.z; up[i].w += c.w;
+                                    }
+                                }
+                            }
+                        }
+                        if (valid && !cl) {
+                            // workspace partials (L2 round trips): slots in batches of four, two tokens at a time; all loads of a
+                            // batch are issued before the first add, so a batch costs one round trip; the adds run in slot order
+                            constexpr int TOKB = 2;
+#pragma unroll
+                            for (int ip = 0; ip < 4; ip += TOKB) {
+                                if (tb + TS * ip >= t_hi) break;
+                                for (int zb = 0; zb < n_contrib; zb += 4) {
+                                    float4 a[4][TOKB], c[4][TOKB];
+#pragma unroll
+                                    for (int zz = 0; zz < 4; ++zz) {
+#pragma unroll
+                                        for (int ii = 0; ii < TOKB; ++ii) {
+                                            const int t = tb + TS * (ip + ii);
+                                            const int z = zb + zz;
+                                            a[zz][ii] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                            c[zz][ii] = a[zz][ii];
+                                            if (t < t_hi && z < n_contrib) {
+                                                const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
+                                                a[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w));
+                                                if (P.paired) c[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                            }
+                                        }
+                                    }
+#pragma unroll
+                                    for (int zz = 0; zz < 4; ++zz) {
+#pragma unroll
+                                        for (int ii = 0; ii < TOKB; ++ii) {
+                                            const int i = ip + ii;
+                                            g[i].x += a[zz][ii].x; g[i].y += a[zz][ii].y; g[i].z += a[zz][ii].z; g[i].w += a[zz][ii].w;
+                                            up[i].x += c[zz][ii].x; up[i].y += c[zz][ii].y; up[i].z += c[zz][ii].z; up[i].w += c[zz][ii].w;
+                                        }
                                     }
                                 }
                             }

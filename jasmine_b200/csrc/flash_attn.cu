@@ -36,6 +36,29 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// Blackwell's packed fp32 pairs and three-input maximum: half the FMA / ADD / MAX instructions of the softmax rows
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 struct FlashParams {
     int Tq, Tk, Hq, Hkv, causal;
     float scale_log2;
@@ -226,10 +249,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
             for (int k = 0; k < 8; ++k) mxs[k] = sv[k];
 #pragma unroll
-            for (int i = 8; i < FA_BN; i += 8)
+            for (int i = 8; i + 16 <= FA_BN; i += 16)
 #pragma unroll
-                for (int k = 0; k < 8; ++k) mxs[k] = fmaxf(mxs[k], sv[i + k]);
-            float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+                for (int k = 0; k < 8; ++k) mxs[k] = fmax3(mxs[k], sv[i + k], sv[i + 8 + k]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) mxs[k] = fmaxf(mxs[k], sv[FA_BN - 8 + k]);
+            float mx = fmaxf(fmax3(mxs[0], mxs[1], mxs[2]), fmaxf(fmax3(mxs[3], mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
             mx *= P.scale_log2;
             // tcgen05.ld / st are warp-collective: the decision to touch the accumulator is taken per warp,
             // each lane then applies its own factor (1 for the rows whose maximum did not move)
@@ -258,20 +283,26 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 }
             }
             // p = 2^(s - m_ref), packed to bf16 pairs, written over the first 64 columns of S
-            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const float neg_m = -m_ref, sc = P.scale_log2;
+            uint64_t ls2[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ls2[k] = pack2(0.0f, 0.0f);
+            const uint64_t neg_m2 = pack2(-m_ref, -m_ref), sc2 = pack2(P.scale_log2, P.scale_log2);
 #pragma unroll
             for (int c = 0; c < FA_BN / 2; c += 16) {
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = ex2_approx(fmaf(sv[2 * (c + i)], sc, neg_m)), p1 = ex2_approx(fmaf(sv[2 * (c + i) + 1], sc, neg_m));
-                    ls[i & 3] += p0 + p1;
+                    float x0, x1;
+                    unpack2(ffma2(pack2(sv[2 * (c + i)], sv[2 * (c + i) + 1]), sc2, neg_m2), x0, x1);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    ls2[i & 3] = fadd2(ls2[i & 3], pack2(p0, p1));
                     w[i] = pack_bf16x2(p0, p1);
                 }
                 tmem_st16(s_addr + c, w);
             }
-            const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            float la, lb;
+            unpack2(fadd2(fadd2(ls2[0], ls2[1]), fadd2(ls2[2], ls2[3])), la, lb);
+            const float lsum = la + lb;
             l += lsum;
             tmem_st_wait();
             tc_fence_before();

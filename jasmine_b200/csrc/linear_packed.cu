@@ -114,7 +114,7 @@ __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok
 
 // CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it
 template <int BN, bool CL>
-__global__ void __launch_bounds__(PK_THREADS, (BN >= 32 && BN <= 64) ? 2 : 1)
+__global__ void __launch_bounds__(PK_THREADS, 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int B_BYTES = BN * 128;  // BN tokens x 64 k, bf16
@@ -288,8 +288,30 @@ __global__ void __launch_bounds__(PK_THREADS, (BN >= 32 && BN <= 64) ? 2 : 1)
         const int row = quad * 32 + lane;  // packed row of the tile = TMEM lane
         const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
         const bool want_ssq = P.ssq_out != nullptr;  // plain tiles only (checked on the host)
-        bool ok = true, waited = false;
-        int seg = 0, cl_syncs = 0;  // cluster barriers this thread has taken part in (two per CTA, whatever happens)
+        bool ok = true;
+        int seg = 0, cl_syncs = 0;
+        // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
+        // predecessor now (the MMA warp is busy with the weight stream meanwhile) and prepare what does not need the accumulator.
+        chain_wait();
+        // Row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into the packed
+        // weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile sums of squares that
+        // the kernel which wrote x left behind (added in tile order).
+        if (P.ssq_in) {
+            for (int t = etid; t < P.T; t += 128) {
+                float q = 0.0f;
+                int j = 0;
+                for (; j + 8 <= P.ssq_in_tiles; j += 8) {  // eight loads in flight, added in tile order
+                    float v8[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v8[k] = __ldcg(P.ssq_in + (size_t)(j + k) * P.ssq_stride + t);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) q += v8[k];
+                }
+                for (; j < P.ssq_in_tiles; ++j) q += __ldcg(P.ssq_in + (size_t)j * P.ssq_stride + t);
+                row_scale[t] = 1.0f / sqrtf(q * P.inv_d + P.eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }  // cluster barriers this thread has taken part in (two per CTA, whatever happens)
         long long u = u_begin;
         while (u < u_end && ok) {
             const int tile = (int)(u / P.kbt);
@@ -298,21 +320,6 @@ __global__ void __launch_bounds__(PK_THREADS, (BN >= 32 && BN <= 64) ? 2 : 1)
             const int buf = seg & 1;
             if (!mbar_wait(&acc_full[buf], (seg >> 1) & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
             tc_fence_after();
-            if (!waited) {
-                chain_wait();  // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels
-                waited = true;
-                // row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into
-                // the packed weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile
-                // sums of squares that the kernel which wrote x left behind (added in tile order)
-                if (P.ssq_in) {
-                    for (int t = etid; t < P.T; t += 128) {
-                        float q = 0.0f;
-                        for (int j = 0; j < P.ssq_in_tiles; ++j) q += __ldcg(P.ssq_in + (size_t)j * P.ssq_stride + t);
-                        row_scale[t] = 1.0f / sqrtf(q * P.inv_d + P.eps);
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                }
-            }
             const bool scaled = P.ssq_in != nullptr;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
             const bool whole = (len == P.kbt);
@@ -488,9 +495,9 @@ __global__ void __launch_bounds__(PK_THREADS, (BN >= 32 && BN <= 64) ? 2 : 1)
                             }
                         }
                         if (valid && !cl) {
-                            // workspace partials (L2 round trips): slots in batches of four, two tokens at a time; all loads of a
+                            // workspace partials (L2 round trips): slots in batches of four, two (few-token launches) or four tokens at a time; all loads of a
                             // batch are issued before the first add, so a batch costs one round trip; the adds run in slot order
-                            constexpr int TOKB = 2;
+                            constexpr int TOKB = BN >= 32 ? 4 : 2;  // more tokens in flight where the fold is long
 #pragma unroll
                             for (int ip = 0; ip < 4; ip += TOKB) {
                                 if (tb + TS * ip >= t_hi) break;

@@ -45,6 +45,34 @@ __global__ void rope_apply_kernel(const T* __restrict__ x, T* __restrict__ out, 
     }
 }
 
+// bf16, 128-bit path: a thread rotates four pairs (8 elements, 16 bytes) with four consecutive table entries; same
+// arithmetic (each product rounded on its own) as the scalar kernel
+__global__ void __launch_bounds__(256) rope_apply_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                                  const float4* __restrict__ table, int d, int n_heads,
+                                                                  const int32_t* __restrict__ positions, int T_tokens,
+                                                                  long long row_stride) {
+    const int quads = d / 8;  // groups of four pairs per head
+    const long long total = (long long)T_tokens * n_heads * quads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int qd = (int)(i % quads);
+        const long long th = i / quads;
+        const int t = (int)(th / n_heads);
+        const int m = positions ? positions[t] : t;
+        const float4* e = table + (long long)m * (d / 2) + qd * 4;
+        const long long base = (long long)t * row_stride + (long long)(th % n_heads) * d + 8 * qd;
+        const uint4 w = *reinterpret_cast<const uint4*>(x + base);
+        const uint32_t in[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float4 c = e[p];
+            const float x0 = bf16lo(in[p]), x1 = bf16hi(in[p]);
+            o[p] = pack_bf16x2(__fadd_rn(__fmul_rn(c.x, x0), __fmul_rn(-c.w, x1)), __fadd_rn(__fmul_rn(c.y, x0), __fmul_rn(c.z, x1)));
+        }
+        *reinterpret_cast<uint4*>(out + base) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 }  // namespace jsm
 
 using namespace jsm;
@@ -90,7 +118,16 @@ jsm_status jsm::rope_apply_strided(const void* d_x, void* d_out, jsm_dtype dtype
     const long long total = (long long)T * n_heads * (d / 2);
     long long blocks = (total + 255) / 256;
     if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
-    if (dtype == JSM_F32)
+    const bool vec = dtype == JSM_BF16 && d % 8 == 0 && row_stride % 8 == 0 && !(reinterpret_cast<uintptr_t>(d_x) & 15) &&
+                     !(reinterpret_cast<uintptr_t>(d_out) & 15);
+    if (vec) {
+        const long long work = (long long)T * n_heads * (d / 8);
+        long long vb = (work + 255) / 256;
+        if (vb > (long long)sm_count() * 16) vb = (long long)sm_count() * 16;
+        rope_apply_bf16_vec_kernel<<<(unsigned)vb, 256, 0, as_stream(stream)>>>(
+            reinterpret_cast<const __nv_bfloat16*>(d_x), reinterpret_cast<__nv_bfloat16*>(d_out),
+            reinterpret_cast<const float4*>(d_table), d, n_heads, d_positions, T, row_stride);
+    } else if (dtype == JSM_F32)
         rope_apply_kernel<float><<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(
             reinterpret_cast<const float*>(d_x), reinterpret_cast<float*>(d_out), reinterpret_cast<const float4*>(d_table), d,
             n_heads, d_positions, T, row_stride);

@@ -15,4 +15,10 @@ jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, voi
 jsm_status rope_apply_strided(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
                               const int32_t* d_positions, int T, long long row_stride, void* stream);
 
+// decode attention of grouped-query models on the tensor cores (attn_decode_mma.cu)
+bool attn_decode_mma_usable(int G, int chunk, const void* pool);
+jsm_status attn_decode_mma_launch(const void* q, long long q_stride, const void* pool, const int32_t* block_table, int max_pages,
+                                  const int32_t* context_lens, int n_seqs, int Hq, int Hkv, float scale_log2, const float* rope,
+                                  int n_chunks, int chunk, float* scratch, cudaStream_t st);
+
 }  // namespace jsm

@@ -14,7 +14,7 @@
 // and the running (max, sum, weighted V) is kept per warp, merged through shared
 // memory and written as one partial per chunk; a second kernel merges the
 // partials of a sequence.
-#include "common.cuh"
+#include "attn.cuh"
 #include <math.h>
 #include <mutex>
 #include <stdlib.h>
@@ -382,6 +382,11 @@ static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void
         JSM_LAUNCH_CHECK();
         return JSM_OK;
     }
+    if (attn_decode_mma_usable(G, chunk, d_pool)) {
+        jsm_status s = attn_decode_mma_launch(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, sl2,
+                                              d_rope_table, n_chunks, chunk, (float*)d_scratch, st);
+        if (s != JSM_OK) return s;
+    } else
     switch (G) {
         case 1: JSM_DEC(1, false); break;
         case 2: JSM_DEC(2, false); break;

@@ -98,8 +98,26 @@ def test_fused_append_decode_equals_append_then_decode(Hq, Hkv, use_rope):
         got = jb.attn_decode_append(q, k_new, v_new, pool, bt, ctx, Hq, Hkv, D, 2048, counters, rope=table)
         torch.cuda.synchronize()
         assert torch.equal(pool, pool_ref), f"cache contents differ at step {step}"
-        assert_close(host(got), host(want), 1e-6, f"fused decode step {step}")
+        # one query head per kv head: both calls run the same CUDA-core arithmetic.  Grouped heads: the separate call
+        # runs its contractions on the tensor cores with the probabilities rounded to bf16
+        assert_close(host(got), host(want), 1e-6 if Hq == Hkv else 2e-2, f"fused decode step {step}")
         assert int(counters.abs().sum()) == 0, "counters must be left at zero"
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(4, 4), (8, 2), (8, 1), (4, 2)])
+def test_decode_ignores_cache_past_context(Hq, Hkv):
+    """Whatever the last page holds past the context length (NaN here) must not reach the result."""
+    lens = [1, 17, 63, 64, 65, 200, 1000]
+    pool, bt, *_ = build_cache(lens, Hkv, 860 + Hq)
+    q = dev(cases.normal((len(lens), Hq * D), 861, 0), torch.bfloat16)
+    ctx = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    want = jb.attn_decode(q, pool, bt, ctx, Hq, Hkv, D, max(lens))
+    for i, L in enumerate(lens):
+        if L % jb.PAGE_SIZE:
+            pool[int(bt[i, (L - 1) // jb.PAGE_SIZE]), :, :, L % jb.PAGE_SIZE:, :] = float("nan")
+    got = jb.attn_decode(q, pool, bt, ctx, Hq, Hkv, D, max(lens))
+    assert torch.isfinite(got.float()).all()
+    assert torch.equal(got, want)
 
 
 def test_decode_equals_prefill_last_row():

@@ -17,8 +17,25 @@ jsm_status rope_apply_strided(const void* d_x, void* d_out, jsm_dtype dtype, con
 
 // decode attention of grouped-query models on the tensor cores (attn_decode_mma.cu)
 bool attn_decode_mma_usable(int G, int chunk, const void* pool);
-jsm_status attn_decode_mma_launch(const void* q, long long q_stride, const void* pool, const int32_t* block_table, int max_pages,
-                                  const int32_t* context_lens, int n_seqs, int Hq, int Hkv, float scale_log2, const float* rope,
-                                  int n_chunks, int chunk, float* scratch, cudaStream_t st);
+struct DecodeMmaArgs {
+    const void* q;
+    long long q_stride;
+    void* pool;
+    const int32_t* block_table;
+    int max_pages;
+    const int32_t* context_lens;
+    int n_seqs, Hq, Hkv;
+    float scale_log2;
+    const float* rope;
+    int n_chunks, chunk;
+    float* scratch;   // [n_seqs][Hq][n_chunks][130] floats of chunk partials
+    bool fused;       // append k_new / v_new first and merge the partials into `out` (needs counters)
+    const void* k_new;
+    const void* v_new;
+    long long kv_new_stride;
+    int* counters;
+    void* out;
+};
+jsm_status attn_decode_mma_launch(const DecodeMmaArgs& a, cudaStream_t st);
 
 }  // namespace jsm

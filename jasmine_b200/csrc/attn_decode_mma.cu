@@ -60,11 +60,16 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
 // the cache as a matrix of 128-wide rows: row of the first key of block (page, K or V, kv head)
 __device__ __forceinline__ int dm_block_row(int page, int kv, int Hkv, int hk) { return ((page * 2 + kv) * Hkv + hk) * DM_PAGE; }
 
-template <int G>
+// FUSED: like attn_decode_kernel<G, true> the kernel first appends the new token's K (rotated) and V - the CTA whose
+// chunk holds position ctx-1 writes them, then orders those writes before its bulk copies with a proxy fence - and the
+// CTA that arrives last at the (sequence, kv head) counter merges the chunk partials and writes the output.
+template <int G, bool FUSED>
 __global__ void __launch_bounds__(DM_THREADS) attn_decode_mma_kernel(
     const __grid_constant__ CUtensorMap tmap, const __nv_bfloat16* __restrict__ q, long long q_stride,
-    const int32_t* __restrict__ block_table, int max_pages, const int32_t* __restrict__ context_lens, int Hq, int Hkv,
-    float scale_log2, const float4* __restrict__ rope, int n_chunks, int chunk_len, float* __restrict__ scratch, int* err) {
+    __nv_bfloat16* __restrict__ pool, const int32_t* __restrict__ block_table, int max_pages,
+    const int32_t* __restrict__ context_lens, int Hq, int Hkv, float scale_log2, const float4* __restrict__ rope, int n_chunks,
+    int chunk_len, float* __restrict__ scratch, const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+    long long kv_new_stride, int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int* err) {
     extern __shared__ uint8_t dm_dyn[];
     uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dm_dyn) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full_bar[DM_STAGES], empty_bar[DM_STAGES];
@@ -89,6 +94,25 @@ __global__ void __launch_bounds__(DM_THREADS) attn_decode_mma_kernel(
     const int c_end = min(ctx, c_begin + chunk_len);
     const int n_it = (c_end - c_begin + DM_PAGE - 1) / DM_PAGE;
     const int32_t* bt = block_table + (long long)seq * max_pages + c_begin / DM_PAGE;
+    if (FUSED && k_new && ctx - 1 >= c_begin) {  // ctx - 1 < c_end always: this CTA owns the newest position
+        const int pos = ctx - 1;
+        if (threadIdx.x < DM_D / 2) {
+            const int pr = threadIdx.x;
+            const int page = block_table[(long long)seq * max_pages + pos / DM_PAGE];
+            __nv_bfloat16* kdst = pool + ((long long)dm_block_row(page, 0, Hkv, hk) + pos % DM_PAGE) * DM_D;
+            __nv_bfloat16* vdst = pool + ((long long)dm_block_row(page, 1, Hkv, hk) + pos % DM_PAGE) * DM_D;
+            uint32_t kw = *reinterpret_cast<const uint32_t*>(k_new + seq * kv_new_stride + (long long)hk * DM_D + 2 * pr);
+            if (rope) {
+                const float4 e = rope[(long long)pos * (DM_D / 2) + pr];
+                const float x0 = bf16lo(kw), x1 = bf16hi(kw);
+                kw = pack_bf16x2(__fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1)), __fadd_rn(__fmul_rn(e.y, x0), __fmul_rn(e.z, x1)));
+            }
+            *reinterpret_cast<uint32_t*>(kdst + 2 * pr) = kw;
+            *reinterpret_cast<uint32_t*>(vdst + 2 * pr) = *reinterpret_cast<const uint32_t*>(v_new + seq * kv_new_stride + (long long)hk * DM_D + 2 * pr);
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // the bulk copies below read these rows
+        }
+        __syncthreads();
+    }
 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;  // heads (lane%4)*2 and +1
     float o[8][4];  // O^T: tile j = dims j*16 .. +15; [0],[1]: dim lane/4, the two heads; [2],[3]: dim lane/4 + 8
@@ -246,28 +270,59 @@ __global__ void __launch_bounds__(DM_THREADS) attn_decode_mma_kernel(
             L += f * sm_l[w][g];
         }
         float* dst = scratch + (((long long)seq * Hq + hk * G + g) * n_chunks + chunk) * (DM_D + 2);
-        dst[d] = acc;
-        if (d == 0) {
-            dst[DM_D] = M;
-            dst[DM_D + 1] = L;
+        if (FUSED && ctx <= chunk_len) {
+            out[((long long)seq * Hq + hk * G + g) * DM_D + d] = __float2bfloat16_rn(acc / L);  // a single chunk: the result
+        } else {
+            dst[d] = acc;
+            if (d == 0) {
+                dst[DM_D] = M;
+                dst[DM_D + 1] = L;
+            }
         }
+    }
+    if (!FUSED || ctx <= chunk_len) return;
+    // ---- the last CTA of this (sequence, kv head) merges the chunk partials
+    __shared__ int is_last;
+    __syncthreads();  // all partial stores of the CTA precede the release below
+    const int n = (ctx + chunk_len - 1) / chunk_len;
+    if (threadIdx.x == 0) {
+        int old;
+        int* ctr = counters + (long long)seq * Hkv + hk;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(ctr) : "memory");
+        is_last = (old == n - 1);
+        if (is_last) *ctr = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    for (int e = threadIdx.x; e < G * DM_D; e += DM_THREADS) {
+        const int g = e / DM_D, d = e % DM_D;
+        const float* src = scratch + ((long long)seq * Hq + hk * G + g) * n_chunks * (DM_D + 2);
+        float M = -INFINITY;
+        for (int c = 0; c < n; ++c) M = fmaxf(M, __ldcg(src + c * (DM_D + 2) + DM_D));
+        float acc = 0.0f, L = 0.0f;
+        for (int c = 0; c < n; ++c) {
+            const float f = exp2f(__ldcg(src + c * (DM_D + 2) + DM_D) - M);
+            acc += f * __ldcg(src + c * (DM_D + 2) + d);
+            L += f * __ldcg(src + c * (DM_D + 2) + DM_D + 1);
+        }
+        out[((long long)seq * Hq + hk * G + g) * DM_D + d] = __float2bfloat16_rn(acc / L);
     }
 }
 
-template <int G>
-static jsm_status dm_launch(const CUtensorMap& map, dim3 grid, cudaStream_t st, const void* q, long long q_stride, const int32_t* bt,
-                            int max_pages, const int32_t* ctx, int Hq, int Hkv, float sl2, const float* rope, int n_chunks, int chunk,
-                            float* scratch) {
+template <int G, bool FUSED>
+static jsm_status dm_launch(const CUtensorMap& map, dim3 grid, cudaStream_t st, const DecodeMmaArgs& a) {
     static bool configured[64] = {false};
     int dev = 0;
     JSM_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_mma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM));
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_mma_kernel<G, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM));
         configured[dev] = true;
     }
-    JSM_CUDA_CHECK(launch_chained(attn_decode_mma_kernel<G>, grid, dim3(DM_THREADS), (size_t)DM_SMEM, st, map, (const __nv_bfloat16*)q,
-                                  q_stride, bt, max_pages, ctx, Hq, Hkv, sl2, (const float4*)rope, n_chunks, chunk, scratch,
-                                  tc_error_word()));
+    JSM_CUDA_CHECK(launch_chained(attn_decode_mma_kernel<G, FUSED>, grid, dim3(DM_THREADS), (size_t)DM_SMEM, st, map,
+                                  (const __nv_bfloat16*)a.q, a.q_stride, (__nv_bfloat16*)a.pool, a.block_table, a.max_pages,
+                                  a.context_lens, a.Hq, a.Hkv, a.scale_log2, (const float4*)a.rope, a.n_chunks, a.chunk, a.scratch,
+                                  (const __nv_bfloat16*)a.k_new, (const __nv_bfloat16*)a.v_new, a.kv_new_stride, a.counters,
+                                  (__nv_bfloat16*)a.out, tc_error_word()));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -281,22 +336,28 @@ bool attn_decode_mma_usable(int G, int chunk, const void* pool) {
     return enabled && (G == 2 || G == 4 || G == 8) && chunk % DM_PAGE == 0 && (reinterpret_cast<uintptr_t>(pool) & 15) == 0;
 }
 
-// Chunk partials of one decode step into `scratch` ([n_seqs][Hq][n_chunks][130] floats), merged by attn_decode_merge_kernel.
-jsm_status attn_decode_mma_launch(const void* q, long long q_stride, const void* pool, const int32_t* block_table, int max_pages,
-                                  const int32_t* context_lens, int n_seqs, int Hq, int Hkv, float scale_log2, const float* rope,
-                                  int n_chunks, int chunk, float* scratch, cudaStream_t st) {
+jsm_status attn_decode_mma_launch(const DecodeMmaArgs& a, cudaStream_t st) {
     // The pool as rows of 128 bf16.  Its size is not known here: the row count only bounds the coordinates the copy
     // engine accepts, the block table decides which rows are read.
     CUtensorMap map;
-    jsm_status s = make_tmap_bf16_2d(&map, pool, 1ull << 30, DM_D, DM_D, DM_PAGE, 64);
+    jsm_status s = make_tmap_bf16_2d(&map, a.pool, 1ull << 30, DM_D, DM_D, DM_PAGE, 64);
     if (s != JSM_OK) return s;
-    dim3 grid(n_chunks, Hkv, n_seqs);
-    switch (Hq / Hkv) {
-        case 2: return dm_launch<2>(map, grid, st, q, q_stride, block_table, max_pages, context_lens, Hq, Hkv, scale_log2, rope, n_chunks, chunk, scratch);
-        case 4: return dm_launch<4>(map, grid, st, q, q_stride, block_table, max_pages, context_lens, Hq, Hkv, scale_log2, rope, n_chunks, chunk, scratch);
-        case 8: return dm_launch<8>(map, grid, st, q, q_stride, block_table, max_pages, context_lens, Hq, Hkv, scale_log2, rope, n_chunks, chunk, scratch);
+    dim3 grid(a.n_chunks, a.Hkv, a.n_seqs);
+    const int G = a.Hq / a.Hkv;
+    if (a.fused) {
+        switch (G) {
+            case 2: return dm_launch<2, true>(map, grid, st, a);
+            case 4: return dm_launch<4, true>(map, grid, st, a);
+            case 8: return dm_launch<8, true>(map, grid, st, a);
+        }
+    } else {
+        switch (G) {
+            case 2: return dm_launch<2, false>(map, grid, st, a);
+            case 4: return dm_launch<4, false>(map, grid, st, a);
+            case 8: return dm_launch<8, false>(map, grid, st, a);
+        }
     }
-    JSM_FAIL(JSM_UNSUPPORTED, "attn_decode_mma: %d query heads per kv head", Hq / Hkv);
+    JSM_FAIL(JSM_UNSUPPORTED, "attn_decode_mma: %d query heads per kv head", G);
 }
 
 }  // namespace jsm

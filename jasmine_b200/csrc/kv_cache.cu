@@ -371,6 +371,10 @@ static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void
                                   Hkv, sl2, (const float4*)d_rope_table, n_chunks, chunk, (float*)d_scratch,                      \
                                   (const __nv_bfloat16*)d_k_new, (const __nv_bfloat16*)d_v_new, (long long)kv_new_stride,         \
                                   d_counters, (__nv_bfloat16*)d_out))
+    const DecodeMmaArgs mma_args = {d_q, (long long)q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, sl2,
+                                    d_rope_table, n_chunks, chunk, (float*)d_scratch, fused, d_k_new, d_v_new,
+                                    (long long)kv_new_stride, d_counters, d_out};
+    if (fused && attn_decode_mma_usable(G, chunk, d_pool)) return attn_decode_mma_launch(mma_args, st);
     if (fused) {
         switch (G) {
             case 1: JSM_DEC(1, true); break;
@@ -383,8 +387,7 @@ static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void
         return JSM_OK;
     }
     if (attn_decode_mma_usable(G, chunk, d_pool)) {
-        jsm_status s = attn_decode_mma_launch(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, sl2,
-                                              d_rope_table, n_chunks, chunk, (float*)d_scratch, st);
+        jsm_status s = attn_decode_mma_launch(mma_args, st);
         if (s != JSM_OK) return s;
     } else
     switch (G) {

@@ -53,6 +53,7 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t byte
 struct PkParams {
     int T, N, K;          // tokens (<= BN), output features (paired: gate features), reduction length
     int n_tiles, kbt;     // tiles of 128 packed rows, k-blocks of 64 per tile
+    int local_epi;        // whole tiles that end a CTA's range use the vectorised epilogue through shared memory
     int paired;           // epilogue silu(gate) * up over a paired tile
     int epilogue;         // LIN_* (LIN_SILU_MUL exactly when paired)
     int out_f32;
@@ -318,12 +319,32 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             const int kb0 = (int)(u % P.kbt);
             const int len = (int)min((long long)(P.kbt - kb0), u_end - u);
             const int buf = seg & 1;
+            // A shared tile that ends this CTA's range: if every other contributor has already arrived at the tile counter
+            // (the usual case: they hold the tile's later k-blocks as their FIRST segment), this CTA is the one that folds,
+            // and its own partial need not travel through the workspace - it stays in shared memory.  The counter is read
+            // while the accumulator is still being produced.
+            bool solo = false;
+            if (len != P.kbt && u + len == u_end && !(CL && P.cluster_s > 1) && P.local_epi) {
+                if (etid == 0) {
+                    const long long uf0 = (long long)tile * P.kbt;
+                    const int nc = pk_owner(uf0 + P.kbt - 1, U, G) - pk_owner(uf0, U, G) + 1;
+                    int c;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(c) : "l"(P.counters + tile) : "memory");
+                    is_last_smem[seg & 1] = (c == nc - 1);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // also carries thread 0's acquire to the other threads' loads
+                solo = is_last_smem[seg & 1] != 0;
+            }
             if (!mbar_wait(&acc_full[buf], (seg >> 1) & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
             tc_fence_after();
             const bool scaled = P.ssq_in != nullptr;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
             const bool whole = (len == P.kbt);
-            if (whole) {
+            // A whole tile that is this CTA's last segment goes through shared memory (the stage ring is free: every MMA
+            // of the CTA has completed) and the vectorised epilogue below, whose stores are 8 or 16 bytes per thread and
+            // contiguous per token; earlier segments overlap the main loop and keep the row-per-thread epilogue.
+            const bool local = whole && (u + len == u_end) && P.local_epi;
+            if (whole && !local) {
                 // ---- the tile is complete in this CTA: epilogue straight from the accumulator
                 if (!P.paired) {
                     const int n = tile * 128 + row;
@@ -407,20 +428,35 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 const int slot = (int)blockIdx.x - c_first;
                 // aligned split: the contributors are the CTAs of this cluster and the partial goes to this CTA's own shared
                 // memory (the stage ring is free: every MMA of the CTA has completed); otherwise to its workspace slot
-                const bool cl = CL && P.cluster_s > 1;
+                const bool cl = CL && P.cluster_s > 1 && !local;
                 float* part_smem = reinterpret_cast<float*>(tiles);
                 float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * (size_t)P.T * 128;
+                const bool to_smem = cl || local || solo;
+                if (BN >= 32 && to_smem) {
+                    // 32 columns per round trip to tensor memory
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (c0 >= P.T) break;
-                    uint32_t r[16];
-                    tmem_ld16(acc_addr + c0, r);
-                    tmem_ld_wait();
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        if (c0 >= P.T) break;
+                        uint32_t r[32];
+                        tmem_ld32(acc_addr + c0, r);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < P.T) {
-                            if (cl) part_smem[(c0 + j) * 128 + row] = __uint_as_float(r[j]);
-                            else __stcg(wbase + (size_t)(c0 + j) * 128 + row, __uint_as_float(r[j]));
+                        for (int j = 0; j < 32; ++j)
+                            if (c0 + j < P.T) part_smem[(c0 + j) * 128 + row] = __uint_as_float(r[j]);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        if (c0 >= P.T) break;
+                        uint32_t r[16];
+                        tmem_ld16(acc_addr + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (c0 + j < P.T) {
+                                if (to_smem) part_smem[(c0 + j) * 128 + row] = __uint_as_float(r[j]);
+                                else __stcg(wbase + (size_t)(c0 + j) * 128 + row, __uint_as_float(r[j]));
+                            }
                         }
                     }
                 }
@@ -429,7 +465,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the MMA warp may reuse the buffer while the fold runs
                 int t_lo = 0, t_hi = P.T;
                 bool do_fold;
-                if (cl) {
+                if (local) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // the tile is in shared memory
+                    do_fold = true;
+                } else if (solo) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // own partial in shared memory, the others' in the workspace
+                    if (etid == 0) P.counters[tile] = 0;            // ready for the next launch
+                    do_fold = true;
+                } else if (cl) {
                     // first cluster barrier: every CTA's partial is in place.  CTA `slot` then folds its share of the tokens
                     // reading all partials in slot order; the second barrier keeps the shared memory alive until all have read.
                     cluster_sync_all();
@@ -474,6 +517,16 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             const int t = tb + TS * i;
                             if (P.epilogue == LIN_RESIDUAL && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
                         }
+                        if (valid && local) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int t = tb + TS * i;
+                                if (t < t_hi) {
+                                    g[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4);
+                                    if (P.paired) up[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
+                                }
+                            }
+                        }
                         if (valid && cl) {
                             // shared-memory partials of the cluster: short latency, four tokens in flight, adds in slot order
 #pragma unroll 4
@@ -494,7 +547,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 }
                             }
                         }
-                        if (valid && !cl) {
+                        if (valid && !cl && !local) {
                             // workspace partials (L2 round trips): slots in batches of four, two (few-token launches) or four tokens at a time; all loads of a
                             // batch are issued before the first add, so a batch costs one round trip; the adds run in slot order
                             constexpr int TOKB = BN >= 32 ? 4 : 2;  // more tokens in flight where the fold is long
@@ -512,9 +565,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                             a[zz][ii] = make_float4(0.f, 0.f, 0.f, 0.f);
                                             c[zz][ii] = a[zz][ii];
                                             if (t < t_hi && z < n_contrib) {
-                                                const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
-                                                a[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w));
-                                                if (P.paired) c[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                                if (solo && z == slot) {
+                                                    a[zz][ii] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4);
+                                                    if (P.paired) c[zz][ii] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
+                                                } else {
+                                                    const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
+                                                    a[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w));
+                                                    if (P.paired) c[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                                }
                                             }
                                         }
                                     }
@@ -530,11 +588,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 }
                             }
                         }
+                        float sc4[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) sc4[i] = (scaled && tb + TS * i < t_hi) ? row_scale[tb + TS * i] : 1.0f;
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int t = tb + TS * i;
                             if (t >= t_hi) break;
-                            const float sc = scaled ? row_scale[t] : 1.0f;
+                            const float sc = sc4[i];
                             float v[4] = {g[i].x * sc + bias4.x, g[i].y * sc + bias4.y, g[i].z * sc + bias4.z, g[i].w * sc + bias4.w};
                             const float uu[4] = {up[i].x * sc, up[i].y * sc, up[i].z * sc, up[i].w * sc};
                             if (P.epilogue == LIN_RESIDUAL) {
@@ -787,6 +848,14 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     PkParams P;
     P.T = a.T; P.N = a.N; P.K = a.K;
     pk_dims(a.N, a.K, paired, &P.n_tiles, &P.kbt);
+    {
+        static int local_epi = -1;
+        if (local_epi < 0) {
+            const char* e = getenv("JSM_PK_LOCAL_EPI");
+            local_epi = e ? atoi(e) : 1;
+        }
+        P.local_epi = local_epi;
+    }
     P.paired = paired; P.epilogue = a.epilogue; P.out_f32 = a.out_f32 ? 1 : 0;
     P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y; P.Wp = (const uint8_t*)a.Wp;
     const int grid = linear_packed_grid(a.N, a.K, paired, a.T);
@@ -821,9 +890,15 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     }
     const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
     // the cluster path lives in instantiations of its own: launches without a cluster run a kernel that carries none of it
+    static int one_kernel = -1;
+    if (one_kernel < 0) {
+        const char* e = getenv("JSM_PK_ONE_KERNEL");
+        one_kernel = e ? atoi(e) : 1;
+    }
+    const bool with_cl = cluster > 1 || (one_kernel && a.T >= 32);
 #define PK_GO(BN_)                                                                                  \
-    return cluster > 1 ? launch_packed<BN_, true>(mx, mx2, P, grid, cluster, a.chained, st)        \
-                       : launch_packed<BN_, false>(mx, mx2, P, grid, cluster, a.chained, st)
+    return with_cl ? launch_packed<BN_, true>(mx, mx2, P, grid, cluster, a.chained, st)            \
+                   : launch_packed<BN_, false>(mx, mx2, P, grid, cluster, a.chained, st)
     switch (bn) {
         case 16: PK_GO(16);
         case 32: PK_GO(32);

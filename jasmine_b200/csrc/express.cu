@@ -8,6 +8,7 @@
 // the whole row in registers between the reduction and the write, so each
 // operand is read once and the result written once.
 #include "common.cuh"
+#include "tc_utils.cuh"
 #include <stdlib.h>
 #include <math.h>
 #include <string.h>
@@ -432,6 +433,240 @@ __global__ void __launch_bounds__(256) rows_kernel(EvalParams P, RowsArgs A, int
     }
 }
 
+// ---- K2s: rows staged through shared memory by bulk copies -----------------------------
+// For f32 operands with contiguous rows of 1024, 2048 or 4096 columns and the programs x, x * imm + y and x + y.
+// A fixed grid of two CTAs per SM walks the rows.  One producer thread copies each row of the operands into a ring of
+// shared-memory stages with cp.async.bulk (completion on an mbarrier), so the bytes in flight per SM are set by the ring
+// (96 KB per CTA) and not by how many rows sit in registers; the 256 consumer threads take a row into registers, release
+// the stage at once and run the same arithmetic, in the same order, as rows_block<256, VPT>.  Every mbarrier wait is
+// bounded; after a timeout the CTA keeps its barrier counts, stores nothing more and records an error code.
+struct StagedArgs {
+    const float* a;  // leaf 0
+    const float* b;  // leaf 1 (programs with two operands)
+    long long rsa, rsb;
+    float imm;
+    int R;
+    const float* gain;
+    const float* bias;
+    float eps;
+    float* out;      // full rows (softmax, norms) or one value per row (reductions)
+    long long rso;
+    int n_stages;
+    int* err;
+};
+constexpr int RS_THREADS = 288;  // 8 consumer warps + 1 producer warp
+constexpr int RS_ERR_FULL = 51, RS_ERR_EMPTY = 52;
+
+__device__ __forceinline__ void rs_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(tc::smem_u32(smem_dst)),
+                 "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(tc::smem_u32(bar))
+                 : "memory");
+}
+// reductions over the 256 consumer threads, warps added in warp order like group_sum<256>; one named barrier each,
+// the caller alternates the scratch rows
+__device__ __forceinline__ float rs_sum(float v, float* red) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) s += red[w];
+    return s;
+}
+__device__ __forceinline__ float rs_max(float v, float* red) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    return m;
+}
+
+template <int VPT, int KIND, int PRO>
+__global__ void __launch_bounds__(RS_THREADS) rows_staged_kernel(StagedArgs A) {
+    using namespace tc;
+    constexpr int C = 1024 * VPT;
+    constexpr int NL = PRO == PRO_LEAF ? 1 : 2;
+    constexpr int STAGE_FLOATS = NL * C;
+    // plain reductions: every consumer warp owns whole rows (row k of the CTA goes to warp k % 8), so no CTA barrier is
+    // needed; a lane plays the threads l, 32 + l, .. 224 + l of the row-per-CTA layout to keep the order of the sums
+    constexpr bool WARP_ROWS = KIND == JSM_ROWS_SUM || KIND == JSM_ROWS_MEAN || KIND == JSM_ROWS_MAX;
+    extern __shared__ __align__(128) float rs_smem[];
+    __shared__ uint64_t full_bar[8], empty_bar[8];
+    __shared__ float red[2][8];
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_stages = A.n_stages;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], WARP_ROWS ? 1 : 8);
+        }
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == 8) {
+        if (lane == 0) {
+            int it = 0;
+            for (int row = blockIdx.x; row < A.R; row += gridDim.x, ++it) {
+                const int s = it % n_stages;
+                if (it >= n_stages && !mbar_wait(&empty_bar[s], ((it / n_stages) - 1) & 1, &abort_flag, A.err, RS_ERR_EMPTY)) break;
+                float* dst = rs_smem + (size_t)s * STAGE_FLOATS;
+                mbar_expect_tx(&full_bar[s], STAGE_FLOATS * 4);
+                rs_bulk_load(dst, A.a + (long long)row * A.rsa, C * 4, &full_bar[s]);
+                if (NL == 2) rs_bulk_load(dst + C, A.b + (long long)row * A.rsb, C * 4, &full_bar[s]);
+            }
+        }
+        return;
+    }
+    if (WARP_ROWS) {
+        for (int it = warp;; it += 8) {
+            const long long row = (long long)blockIdx.x + (long long)it * gridDim.x;
+            if (row >= A.R) break;
+            const int s = it % n_stages;
+            if (!mbar_wait(&full_bar[s], (it / n_stages) & 1, &abort_flag, A.err, RS_ERR_FULL)) break;
+            const float4* sa = reinterpret_cast<const float4*>(rs_smem + (size_t)s * STAGE_FLOATS);
+            float part[8];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                float acc = KIND == JSM_ROWS_MAX ? -INFINITY : 0.0f;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int q = i * 256 + w * 32 + lane;
+                    const float4 x = sa[q];
+                    float e[4] = {x.x, x.y, x.z, x.w};
+                    if (PRO != PRO_LEAF) {
+                        const float4 y = sa[C / 4 + q];
+                        if (PRO == PRO_AXPB) {
+                            e[0] = __fadd_rn(__fmul_rn(x.x, A.imm), y.x); e[1] = __fadd_rn(__fmul_rn(x.y, A.imm), y.y);
+                            e[2] = __fadd_rn(__fmul_rn(x.z, A.imm), y.z); e[3] = __fadd_rn(__fmul_rn(x.w, A.imm), y.w);
+                        } else {
+                            e[0] = x.x + y.x; e[1] = x.y + y.y; e[2] = x.z + y.z; e[3] = x.w + y.w;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc = KIND == JSM_ROWS_MAX ? fmaxf(acc, e[j]) : acc + e[j];
+                }
+                part[w] = acc;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+            float r;
+            if (KIND == JSM_ROWS_MAX) {
+                r = part[0];
+#pragma unroll
+                for (int w = 1; w < 8; ++w) r = fmaxf(r, part[w]);
+                r = warp_max(r);
+            } else {
+#pragma unroll
+                for (int w = 0; w < 8; ++w) part[w] = warp_sum(part[w]);
+                r = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) r += part[w];
+                if (KIND == JSM_ROWS_MEAN) r = r / (float)C;
+            }
+            if (lane == 0) A.out[row * A.rso] = r;
+        }
+        return;
+    }
+    const int t = threadIdx.x;  // 0..255
+    bool ok = true;
+    int it = 0, par = 0;
+    // the gain and the bias of a norm: the same columns for every row of this CTA
+    float4 gain4[VPT], bias4[VPT];
+    if (KIND == JSM_ROWS_LAYERNORM || KIND == JSM_ROWS_RMSNORM) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int c = (i * 256 + t) * 4;
+            gain4[i] = A.gain ? *reinterpret_cast<const float4*>(A.gain + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+            bias4[i] = (A.bias && KIND == JSM_ROWS_LAYERNORM) ? *reinterpret_cast<const float4*>(A.bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    for (int row = blockIdx.x; row < A.R; row += gridDim.x, ++it) {
+        const int s = it % n_stages;
+        if (!ok || !mbar_wait(&full_bar[s], (it / n_stages) & 1, &abort_flag, A.err, RS_ERR_FULL)) ok = false;
+        const float4* sa = reinterpret_cast<const float4*>(rs_smem + (size_t)s * STAGE_FLOATS);
+        float v[VPT][4];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const float4 x = sa[i * 256 + t];
+            if (PRO == PRO_LEAF) {
+                v[i][0] = x.x; v[i][1] = x.y; v[i][2] = x.z; v[i][3] = x.w;
+            } else {
+                const float4 y = sa[C / 4 + i * 256 + t];
+                if (PRO == PRO_AXPB) {
+                    v[i][0] = __fadd_rn(__fmul_rn(x.x, A.imm), y.x); v[i][1] = __fadd_rn(__fmul_rn(x.y, A.imm), y.y);
+                    v[i][2] = __fadd_rn(__fmul_rn(x.z, A.imm), y.z); v[i][3] = __fadd_rn(__fmul_rn(x.w, A.imm), y.w);
+                } else {
+                    v[i][0] = x.x + y.x; v[i][1] = x.y + y.y; v[i][2] = x.z + y.z; v[i][3] = x.w + y.w;
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);  // the row is in registers: the stage can be refilled
+        if (KIND == JSM_ROWS_SOFTMAX) {
+            float m = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) m = fmaxf(m, v[i][j]);
+            m = rs_max(m, red[0]);
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float e = exp2f((v[i][j] - m) * 1.4426950408889634f);
+                    v[i][j] = e;
+                    sum += e;
+                }
+            sum = rs_sum(sum, red[1]);
+            const float inv_s = 1.0f / sum;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[i][j] = v[i][j] * inv_s;
+        } else {  // LayerNorm, RMSNorm
+            float mean = 0.0f;
+            if (KIND == JSM_ROWS_LAYERNORM) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sum += v[i][j];
+                mean = rs_sum(sum, red[0]) / (float)C;
+            }
+            float q = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float d = v[i][j] - mean;
+                    v[i][j] = d;
+                    q += d * d;
+                }
+            q = rs_sum(q, KIND == JSM_ROWS_LAYERNORM ? red[1] : red[par]) / (float)C;
+            par ^= 1;
+            const float inv_sd = 1.0f / sqrtf(q + A.eps);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const float4 g = gain4[i], b = bias4[i];
+                v[i][0] = g.x * (v[i][0] * inv_sd) + b.x;
+                v[i][1] = g.y * (v[i][1] * inv_sd) + b.y;
+                v[i][2] = g.z * (v[i][2] * inv_sd) + b.z;
+                v[i][3] = g.w * (v[i][3] * inv_sd) + b.w;
+            }
+        }
+        if (ok) {
+            float4* dst = reinterpret_cast<float4*>(A.out + (long long)row * A.rso);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) __stcs(dst + i * 256 + t, make_float4(v[i][0], v[i][1], v[i][2], v[i][3]));
+        }
+    }
+}
+
 // ---- long rows (C > 8192) and the column axis: re-evaluating multi-pass kernels ----
 // One CTA of 256 threads per line.  `along_cols` = reduce over the columns of a row
 // (axis 1) else over the rows of a column (axis 0).
@@ -665,6 +900,91 @@ static void launch_rows(const Lowered& Lw, const RowsArgs& A, cudaStream_t st) {
     }
 }
 
+template <int VPT, int KIND>
+static cudaError_t launch_staged_pro(int pro, const StagedArgs& S, unsigned grid, size_t smem, cudaStream_t st) {
+#define JSM_RS(PRO_)                                                                                                      \
+    {                                                                                                                     \
+        static bool configured[64] = {false};                                                                             \
+        int dev = 0;                                                                                                      \
+        cudaGetDevice(&dev);                                                                                              \
+        if (dev >= 0 && dev < 64 && !configured[dev]) {                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(rows_staged_kernel<VPT, KIND, PRO_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return e;                                                                               \
+            configured[dev] = true;                                                                                       \
+        }                                                                                                                 \
+        rows_staged_kernel<VPT, KIND, PRO_><<<grid, RS_THREADS, smem, st>>>(S);                                           \
+        return cudaGetLastError();                                                                                        \
+    }
+    if (pro == PRO_LEAF) JSM_RS(PRO_LEAF)
+    if (pro == PRO_AXPB) JSM_RS(PRO_AXPB)
+    JSM_RS(PRO_ADD)
+#undef JSM_RS
+}
+template <int VPT>
+static cudaError_t launch_staged_kind(int kind, int pro, const StagedArgs& S, unsigned grid, size_t smem, cudaStream_t st) {
+    switch (kind) {
+        case JSM_ROWS_SUM: return launch_staged_pro<VPT, JSM_ROWS_SUM>(pro, S, grid, smem, st);
+        case JSM_ROWS_MEAN: return launch_staged_pro<VPT, JSM_ROWS_MEAN>(pro, S, grid, smem, st);
+        case JSM_ROWS_MAX: return launch_staged_pro<VPT, JSM_ROWS_MAX>(pro, S, grid, smem, st);
+        case JSM_ROWS_SOFTMAX: return launch_staged_pro<VPT, JSM_ROWS_SOFTMAX>(pro, S, grid, smem, st);
+        case JSM_ROWS_LAYERNORM: return launch_staged_pro<VPT, JSM_ROWS_LAYERNORM>(pro, S, grid, smem, st);
+        default: return launch_staged_pro<VPT, JSM_ROWS_RMSNORM>(pro, S, grid, smem, st);
+    }
+}
+
+// Rows staged through shared memory: f32 operands with contiguous, 16-byte aligned rows of 1024, 2048 or 4096 columns,
+// the programs x, x * imm + y and x + y, every kind but argmax.  Returns false when the call does not qualify.
+static bool try_rows_staged(const Lowered& Lw, const RowsArgs& A, cudaStream_t st, cudaError_t* err) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("JSM_ROWS_STAGED");
+        enabled = e ? atoi(e) : 1;
+    }
+    const EvalParams& P = Lw.P;
+    const int C = Lw.C;
+    if (!enabled || !Lw.vec || A.kind == JSM_ROWS_ARGMAX) return false;
+    if (C != 1024 && C != 2048 && C != 4096) return false;
+    if (P.pro != PRO_LEAF && P.pro != PRO_AXPB && P.pro != PRO_ADD) return false;
+    const int nl = P.pro == PRO_LEAF ? 1 : 2;
+    if (P.n_leaves < nl) return false;
+    for (int i = 0; i < nl; ++i)
+        if (P.leaf[i].kind != LK_FULL || P.leaf[i].dtype != JSM_F32) return false;
+    if (A.out.dtype != JSM_F32) return false;
+    const bool reduces = A.kind <= JSM_ROWS_ARGMAX;
+    if (!reduces && !A.out.vec) return false;
+    if ((A.gain && reinterpret_cast<uintptr_t>(A.gain) % 16) || (A.bias && reinterpret_cast<uintptr_t>(A.bias) % 16)) return false;
+    StagedArgs S;
+    S.a = reinterpret_cast<const float*>(P.leaf[0].p);
+    S.rsa = P.leaf[0].rs;
+    S.b = nl == 2 ? reinterpret_cast<const float*>(P.leaf[1].p) : nullptr;
+    S.rsb = nl == 2 ? P.leaf[1].rs : 0;
+    S.imm = P.pro_imm;
+    S.R = A.R;
+    S.gain = A.gain;
+    S.bias = A.bias;
+    S.eps = A.eps;
+    S.out = reinterpret_cast<float*>(A.out.p);
+    S.rso = A.out.rs;
+    S.err = tc_error_word();
+    const size_t stage_bytes = (size_t)nl * C * 4;
+    int n_stages = (int)(96 * 1024 / stage_bytes);
+    if (n_stages > 8) n_stages = 8;
+    if (reduces) {
+        // a warp per row: warp w must meet stage w in every phase (a parity wait tells consecutive phases apart only),
+        // so the ring has exactly as many stages as consumer warps
+        n_stages = 8;
+        if (8 * stage_bytes > 200 * 1024) return false;
+    }
+    S.n_stages = n_stages;
+    unsigned grid = (unsigned)((n_stages * stage_bytes > 100 * 1024 ? 1 : 2) * sm_count());
+    if ((int)grid > A.R) grid = (unsigned)A.R;
+    const size_t smem = (size_t)n_stages * stage_bytes;
+    if (C == 1024) *err = launch_staged_kind<1>(A.kind, P.pro, S, grid, smem, st);
+    else if (C == 2048) *err = launch_staged_kind<2>(A.kind, P.pro, S, grid, smem, st);
+    else *err = launch_staged_kind<4>(A.kind, P.pro, S, grid, smem, st);
+    return true;
+}
+
 }  // namespace jsm
 
 using namespace jsm;
@@ -717,6 +1037,12 @@ jsm_status jsm_eval_rows(int kind, int axis, const jsm_instr* prog, int n_instr,
     A.kind = kind; A.R = Lw.R; A.C = Lw.C; A.gain = d_gain; A.bias = d_bias; A.eps = eps; A.out = O;
     cudaStream_t st = as_stream(stream);
     const int C = Lw.C;
+    cudaError_t staged_err = cudaSuccess;
+    if (axis == 1 && try_rows_staged(Lw, A, st, &staged_err)) {
+        if (staged_err != cudaSuccess) JSM_FAIL(JSM_CUDA, "jsm_eval_rows: launch failed: %s", cudaGetErrorString(staged_err));
+        g_launches.fetch_add(1);
+        return JSM_OK;
+    }
     if (axis == 1 && C <= 8192) {
         if (C <= 128) launch_rows<32, 1>(Lw, A, st);
         else if (C <= 256) launch_rows<32, 2>(Lw, A, st);

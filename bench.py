@@ -182,14 +182,24 @@ def run_kernel_workload(args):
     K, W = max(args.steps, 1), max(args.warmup, 3)
 
     def timed(fn, sets=1):
-        """Mean milliseconds per call over K calls; `sets` rotating input sets keep the operands out of L2."""
+        """Mean milliseconds per call over K calls; `sets` rotating input sets keep the operands out of L2.  The K calls
+        are captured into one CUDA graph and replayed, so that the time between the events is device time and not the
+        rate at which Python can issue calls of a few tens of microseconds."""
         for i in range(W):
             fn(i % sets)
         torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(K):
+                    fn(i % sets)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(K):
-            fn(i % sets)
+        graph.replay()
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / K

@@ -73,6 +73,45 @@ __global__ void __launch_bounds__(256) rope_apply_bf16_vec_kernel(const __nv_bfl
     }
 }
 
+// The same for many heads per token: a thread keeps the four table entries of its group of pairs and walks the heads,
+// so the table (16 bytes per pair, four times the bytes of the bf16 data it rotates) is read once per token instead of
+// once per head.  Block = 16 groups of pairs x 16 head lanes (d = 128); one token per loop step.
+__global__ void __launch_bounds__(256) rope_apply_bf16_heads_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                                    const float4* __restrict__ table, int n_heads,
+                                                                    const int32_t* __restrict__ positions, int T_tokens,
+                                                                    long long row_stride) {
+    constexpr int D = 128;
+    const int qd = threadIdx.x & 15, hl = threadIdx.x >> 4;
+    for (int t = blockIdx.x; t < T_tokens; t += gridDim.x) {
+        const int m = positions ? positions[t] : t;
+        const float4* e = table + (long long)m * (D / 2) + qd * 4;
+        const float4 c0 = e[0], c1 = e[1], c2 = e[2], c3 = e[3];
+        const float4 c[4] = {c0, c1, c2, c3};
+        for (int h0 = hl; h0 < n_heads; h0 += 64) {
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int h = h0 + 16 * u;
+                if (h < n_heads) w[u] = __ldcs(reinterpret_cast<const uint4*>(x + (long long)t * row_stride + (long long)h * D + 8 * qd));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int h = h0 + 16 * u;
+                if (h >= n_heads) break;
+                const uint32_t in[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int p = 0; p < 4; ++p) {
+                    const float x0 = bf16lo(in[p]), x1 = bf16hi(in[p]);
+                    o[p] = pack_bf16x2(__fadd_rn(__fmul_rn(c[p].x, x0), __fmul_rn(-c[p].w, x1)),
+                                       __fadd_rn(__fmul_rn(c[p].y, x0), __fmul_rn(c[p].z, x1)));
+                }
+                *reinterpret_cast<uint4*>(out + (long long)t * row_stride + (long long)h * D + 8 * qd) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+}
+
 }  // namespace jsm
 
 using namespace jsm;
@@ -120,7 +159,12 @@ jsm_status jsm::rope_apply_strided(const void* d_x, void* d_out, jsm_dtype dtype
     if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
     const bool vec = dtype == JSM_BF16 && d % 8 == 0 && row_stride % 8 == 0 && !(reinterpret_cast<uintptr_t>(d_x) & 15) &&
                      !(reinterpret_cast<uintptr_t>(d_out) & 15);
-    if (vec) {
+    if (vec && d == 128 && n_heads >= 4 && T >= 64) {
+        unsigned hb = (unsigned)(T < sm_count() * 16 ? T : sm_count() * 16);
+        rope_apply_bf16_heads_kernel<<<hb, 256, 0, as_stream(stream)>>>(
+            reinterpret_cast<const __nv_bfloat16*>(d_x), reinterpret_cast<__nv_bfloat16*>(d_out),
+            reinterpret_cast<const float4*>(d_table), n_heads, d_positions, T, row_stride);
+    } else if (vec) {
         const long long work = (long long)T * n_heads * (d / 8);
         long long vb = (work + 255) / 256;
         if (vb > (long long)sm_count() * 16) vb = (long long)sm_count() * 16;

@@ -323,11 +323,27 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             // (the usual case: they hold the tile's later k-blocks as their FIRST segment), this CTA is the one that folds,
             // and its own partial need not travel through the workspace - it stays in shared memory.  The counter is read
             // while the accumulator is still being produced.
+            // Everything about the segment that does not need the accumulator is worked out before the wait for it: who
+            // shares the tile (two 64-bit divisions) and this thread's place in the vectorised epilogue.  The tail after
+            // the last MMA runs once per launch on four warps, so every instruction moved out of it shortens the launch.
+            const bool whole = (len == P.kbt);
+            const long long uf = (long long)tile * P.kbt;
+            const int c_first = whole ? (int)blockIdx.x : pk_owner(uf, U, G);
+            const int c_last = whole ? (int)blockIdx.x : pk_owner(uf + P.kbt - 1, U, G);
+            const int n_contrib = c_last - c_first + 1;
+            const int slot = (int)blockIdx.x - c_first;
+            const int gshift = P.paired ? 4 : 5;  // 16 or 32 groups of 4 features per tile
+            const int f4 = (etid & ((1 << gshift) - 1)) * 4, tsub = etid >> gshift, TS = 128 >> gshift;
+            const int n_f = (P.paired ? tile * 64 : tile * 128) + f4;
+            const bool valid_f = n_f < P.N;
+            const float4 bias4 = (P.bias && !P.paired && valid_f) ? *reinterpret_cast<const float4*>(P.bias + n_f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const size_t slot_stride = (size_t)P.T * 128;
+            const float* tbase = P.ws + (size_t)tile * P.max_slots * slot_stride;
+            float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * slot_stride;
             bool solo = false;
-            if (len != P.kbt && u + len == u_end && !(CL && P.cluster_s > 1) && P.local_epi) {
+            if (!whole && u + len == u_end && !(CL && P.cluster_s > 1) && P.local_epi) {
                 if (etid == 0) {
-                    const long long uf0 = (long long)tile * P.kbt;
-                    const int nc = pk_owner(uf0 + P.kbt - 1, U, G) - pk_owner(uf0, U, G) + 1;
+                    const int nc = n_contrib;
                     int c;
                     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(c) : "l"(P.counters + tile) : "memory");
                     is_last_smem[seg & 1] = (c == nc - 1);
@@ -339,7 +355,6 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             tc_fence_after();
             const bool scaled = P.ssq_in != nullptr;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
-            const bool whole = (len == P.kbt);
             // A whole tile that is this CTA's last segment goes through shared memory (the stage ring is free: every MMA
             // of the CTA has completed) and the vectorised epilogue below, whose stores are 8 or 16 bytes per thread and
             // contiguous per token; earlier segments overlap the main loop and keep the row-per-thread epilogue.
@@ -422,15 +437,10 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);
             } else {
                 // ---- shared tile: store the raw partial in this CTA's slot, the last contributor folds
-                const long long uf = (long long)tile * P.kbt;
-                const int c_first = pk_owner(uf, U, G), c_last = pk_owner(uf + P.kbt - 1, U, G);
-                const int n_contrib = c_last - c_first + 1;
-                const int slot = (int)blockIdx.x - c_first;
                 // aligned split: the contributors are the CTAs of this cluster and the partial goes to this CTA's own shared
                 // memory (the stage ring is free: every MMA of the CTA has completed); otherwise to its workspace slot
                 const bool cl = CL && P.cluster_s > 1 && !local;
                 float* part_smem = reinterpret_cast<float*>(tiles);
-                float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * (size_t)P.T * 128;
                 const bool to_smem = cl || local || solo;
                 if (BN >= 32 && to_smem) {
                     // 32 columns per round trip to tensor memory
@@ -498,13 +508,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                     // A thread owns 4 consecutive output features of every TS-th token; the partials of four tokens are in
                     // flight at once and the slots are added in slot order.  Plain tiles: a warp shares its tokens (32 groups
                     // of 4 features), so the per-token sum of squares is one warp reduction.
-                    const int groups = P.paired ? 16 : 32;  // groups of 4 features per tile
-                    const int f4 = (etid % groups) * 4, tsub = etid / groups, TS = 128 / groups;
-                    const int n = (P.paired ? tile * 64 : tile * 128) + f4;
-                    const bool valid = n < P.N;
-                    const float* tbase = P.ws + (size_t)tile * P.max_slots * (size_t)P.T * 128;
-                    const size_t slot_stride = (size_t)P.T * 128;
-                    const float4 bias4 = (P.bias && !P.paired && valid) ? *reinterpret_cast<const float4*>(P.bias + n) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const int n = n_f;
+                    const bool valid = valid_f;
                     const uint32_t part_addr = smem_u32(part_smem);
                     for (int tb = t_lo + tsub; tb < t_hi; tb += 4 * TS) {  // warp-uniform trip count for plain tiles
                         float4 g[4], up[4];

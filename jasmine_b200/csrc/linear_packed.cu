@@ -89,9 +89,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
     } while (0)
 
 // unit range of CTA c: [c*U/G, (c+1)*U/G)
-__host__ __device__ inline long long pk_begin(long long c, long long U, long long G) { return c * U / G; }
+// (32-bit division where the products fit: a 64-bit division is a routine of about a hundred instructions)
+__host__ __device__ inline long long pk_begin(long long c, long long U, long long G) {
+    if ((U + 1) * G < (1ll << 31)) return (long long)((unsigned)(c * U) / (unsigned)G);
+    return c * U / G;
+}
 // CTA that owns unit u: the largest c with c*U/G <= u
-__host__ __device__ inline int pk_owner(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
+__host__ __device__ inline int pk_owner(long long u, long long U, long long G) {
+    if ((U + 1) * G < (1ll << 31)) return (int)(((unsigned)((u + 1) * G) + (unsigned)U - 1u) / (unsigned)U) - 1;
+    return (int)(((u + 1) * G + U - 1) / U - 1);
+}
 
 // ---- thread-block cluster helpers: the CTAs that share a tile exchange their partials through distributed shared memory
 __device__ __forceinline__ void cluster_sync_all() {
@@ -172,33 +179,30 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             const uint8_t* wsrc = P.Wp + (size_t)u_begin * PK_TILE_BYTES;
             // weights first: the ring is filled with W before the predecessor kernel has finished (constant weights);
             // the X blocks of the same stages follow once it has
-            int pre = 0;
-            long long u = u_begin;
-            if (P.w_early) {
-                while (u < u_end && pre < stages) {
-                    const int kb0 = (int)(u % P.kbt);
-                    const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
-                    mbar_expect_tx(&full_bar[pre], (uint32_t)n * PK_TILE_BYTES);
-                    bulk_load(tiles + (size_t)pre * STAGE_BYTES, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES,
-                              &full_bar[pre]);
-                    u += n;
-                    ++pre;
-                }
-            }
-            PK_TRACE(1);  // first ring of W requested
-            int i = pre, issued = pre;
-            while (u < u_end) {
-                const int s = i % stages;
-                const uint32_t ph = (i / stages) & 1;
-                if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
-                const int kb0 = (int)(u % P.kbt);
-                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
+            // loop state kept incrementally (k-block within the tile, stage, phase): no division per request
+            int rem = (int)(u_end - u_begin), kb = (int)(u_begin % P.kbt);
+            int i = 0, s = 0;
+            uint32_t ph = 0;
+            const uint8_t* src = wsrc;
+            auto issue = [&]() {
+                const int n = pk_chunk(P.pair_ok, min(P.kbt - kb, rem));
                 mbar_expect_tx(&full_bar[s], (uint32_t)n * PK_TILE_BYTES);
-                bulk_load(tiles + (size_t)s * STAGE_BYTES, wsrc + (size_t)(u - u_begin) * PK_TILE_BYTES, (uint32_t)n * PK_TILE_BYTES, &full_bar[s]);
-                u += n;
+                bulk_load(tiles + (size_t)s * STAGE_BYTES, src, (uint32_t)n * PK_TILE_BYTES, &full_bar[s]);
+                src += (size_t)n * PK_TILE_BYTES;
+                rem -= n;
+                kb += n;
+                if (kb == P.kbt) kb = 0;
                 ++i;
-                issued = i;
+                if (++s == stages) { s = 0; ph ^= 1; }
+            };
+            if (P.w_early)
+                while (rem > 0 && i < stages) issue();
+            PK_TRACE(1);  // first ring of W requested
+            while (rem > 0) {
+                if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
+                issue();
             }
+            const int issued = i;
             if (abort_flag) {  // let the copies in flight land before the CTA exits (bounded)
                 const long long t_start = clock64();
                 for (int j = max(0, issued - stages); j < issued; ++j)
@@ -215,20 +219,21 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         if (lane == 0) {
             chain_wait();
             PK_TRACE(2);  // predecessor complete
-            long long u = u_begin;
-            int i = 0;
-            while (u < u_end) {
-                const int s = i % stages;
-                const uint32_t ph = (i / stages) & 1;
+            int rem = (int)(u_end - u_begin), kb = (int)(u_begin % P.kbt);
+            int i = 0, s = 0;
+            uint32_t ph = 0;
+            while (rem > 0) {
                 if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
-                const int kb0 = (int)(u % P.kbt);
-                const int n = pk_chunk(P.pair_ok, (int)min((long long)(P.kbt - kb0), u_end - u));
+                const int n = pk_chunk(P.pair_ok, min(P.kbt - kb, rem));
                 uint8_t* xs = tiles + (size_t)s * STAGE_BYTES + X_OFF;
                 mbar_expect_tx(&full_bar[s], (uint32_t)n * B_BYTES);
-                if (n == 2) tma_load_3d(xs, &tmap_x2, 0, 0, kb0, &full_bar[s]);
-                else tma_load_2d(xs, &tmap_x, kb0 * 64, 0, &full_bar[s]);
-                u += n;
+                if (n == 2) tma_load_3d(xs, &tmap_x2, 0, 0, kb, &full_bar[s]);
+                else tma_load_2d(xs, &tmap_x, kb * 64, 0, &full_bar[s]);
+                rem -= n;
+                kb += n;
+                if (kb == P.kbt) kb = 0;
                 ++i;
+                if (++s == stages) { s = 0; ph ^= 1; }
             }
         }
         if (CL && P.cluster_s > 1) {
@@ -241,11 +246,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc_bf16(128, BN);
             bool ok = true;
-            int it = 0, seg = 0;
-            long long u = u_begin;
-            while (u < u_end && ok) {
-                const int kb0 = (int)(u % P.kbt);
-                const int len = (int)min((long long)(P.kbt - kb0), u_end - u);
+            int it = 0, seg = 0, s = 0;
+            uint32_t ph = 0;
+            int rem = (int)(u_end - u_begin), kb0 = (int)(u_begin % P.kbt);
+            while (rem > 0 && ok) {
+                const int len = min(P.kbt - kb0, rem);
                 const int buf = seg & 1;
                 if (seg >= 2) {
                     // the epilogue must have drained this buffer's previous segment
@@ -255,8 +260,6 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                 for (int j = 0; j < len; ++it) {
                     const int n = pk_chunk(P.pair_ok, len - j);
-                    const int s = it % stages;
-                    const uint32_t ph = (it / stages) & 1;
                     if (!mbar_wait(&full_bar[s], ph, &abort_flag, P.err, TC_TIMEOUT_FULL)) { ok = false; break; }
                     if (it == 0) PK_TRACE(3);  // first stage landed
                     tc_fence_after();
@@ -270,10 +273,12 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                     }
                     mma_commit(&empty_bar[s]);
                     j += n;
+                    if (++s == stages) { s = 0; ph ^= 1; }
                 }
                 if (!ok) break;
                 mma_commit(&acc_full[buf]);
-                u += len;
+                rem -= len;
+                kb0 = 0;  // every segment after the first starts a tile
                 ++seg;
             }
             PK_TRACE(4);  // last MMA issued

@@ -91,11 +91,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     chain_trigger();
     chain_wait();
     const int chunk = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
-    const int ctx = context_lens[seq];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c_begin = chunk * chunk_len;
+    // The loads that do not depend on one another go out together: the context length, the page of the chunk's first
+    // keys (read before the length is known: the entry exists whatever it holds, it is used only if the chunk has keys)
+    // and the raw query heads.  One memory round trip instead of three on the way to the first K/V rows.
+    const int32_t* bt = block_table + (long long)seq * max_pages;
+    const int ks = lane >> 4;          // which of the two keys of a warp load
+    const int dsub = (lane & 15) * 8;  // this lane's 8 dims
+    const int first_base = c_begin + warp * (2 * DEC_UNROLL);
+    const int page_first = first_base / JSM_PAGE_SIZE < max_pages ? bt[first_base / JSM_PAGE_SIZE] : 0;
+    uint4 q_raw[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) q_raw[g] = *reinterpret_cast<const uint4*>(q + seq * q_stride + (long long)(hk * G + g) * D + dsub);
+    const int ctx = context_lens[seq];
     if (c_begin >= ctx) return;
     const int c_end = min(ctx, c_begin + chunk_len);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (FUSED && k_new && ctx - 1 >= c_begin) {  // ctx - 1 < c_end always: this CTA owns the newest position
         const int pos = ctx - 1;
         if (threadIdx.x < D / 2) {
@@ -114,15 +125,40 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
         }
         __syncthreads();  // the chunk loop below reads what was just written
     }
-    const int ks = lane >> 4;          // which of the two keys of a warp load
-    const int dsub = (lane & 15) * 8;  // this lane's 8 dims
+    const long long page_elems = 2ll * Hkv * JSM_PAGE_SIZE * D;
+    const long long v_off = (long long)Hkv * JSM_PAGE_SIZE * D;
+    constexpr int STEP = 2 * DEC_UNROLL;  // keys per warp step
+
+    // the K and V rows of one warp step (8 keys); the next step's rows are requested before this step's arithmetic so that
+    // the memory round trips of consecutive steps overlap
+    auto fetch_page = [&](int base, int page, uint4 (&kw)[DEC_UNROLL], uint4 (&vw)[DEC_UNROLL]) {
+        const __nv_bfloat16* kp = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + base % JSM_PAGE_SIZE) * D;
+#pragma unroll
+        for (int u = 0; u < DEC_UNROLL; ++u) {
+            const int key = base + 2 * u + ks;
+            if (key < c_end) {
+                kw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + (long long)(2 * u + ks) * D + dsub));
+                vw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + v_off + (long long)(2 * u + ks) * D + dsub));
+            } else {
+                kw[u] = make_uint4(0, 0, 0, 0);
+                vw[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto fetch = [&](int base, uint4 (&kw)[DEC_UNROLL], uint4 (&vw)[DEC_UNROLL]) {
+        if (base < c_end) fetch_page(base, bt[base / JSM_PAGE_SIZE], kw, vw);
+    };
+    uint4 kw[DEC_UNROLL], vw[DEC_UNROLL], kw_next[DEC_UNROLL], vw_next[DEC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) kw_next[u] = vw_next[u] = make_uint4(0, 0, 0, 0);
+    // the first rows are requested before the queries are rotated: the table entries of the rotation arrive meanwhile
+    if (first_base < c_end) fetch_page(first_base, page_first, kw_next, vw_next);
 
     // query heads of the group, this lane's 8 dims, pre-scaled into the log2 domain
     float qf[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-        const uint4 w = *reinterpret_cast<const uint4*>(q + seq * q_stride + (long long)(hk * G + g) * D + dsub);
-        unpack8(w, qf[g]);
+        unpack8(q_raw[g], qf[g]);
         if (rope) {
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
@@ -147,34 +183,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
     }
-    const long long page_elems = 2ll * Hkv * JSM_PAGE_SIZE * D;
-    const long long v_off = (long long)Hkv * JSM_PAGE_SIZE * D;
-    const int32_t* bt = block_table + (long long)seq * max_pages;
-    constexpr int STEP = 2 * DEC_UNROLL;  // keys per warp step
-
-    // the K and V rows of one warp step (8 keys); the next step's rows are requested before this step's arithmetic so that
-    // the memory round trips of consecutive steps overlap
-    auto fetch = [&](int base, uint4 (&kw)[DEC_UNROLL], uint4 (&vw)[DEC_UNROLL]) {
-        if (base < c_end) {
-            const int page = bt[base / JSM_PAGE_SIZE];
-            const __nv_bfloat16* kp = pool + page * page_elems + ((long long)hk * JSM_PAGE_SIZE + base % JSM_PAGE_SIZE) * D;
-#pragma unroll
-            for (int u = 0; u < DEC_UNROLL; ++u) {
-                const int key = base + 2 * u + ks;
-                if (key < c_end) {
-                    kw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + (long long)(2 * u + ks) * D + dsub));
-                    vw[u] = __ldcs(reinterpret_cast<const uint4*>(kp + v_off + (long long)(2 * u + ks) * D + dsub));
-                } else {
-                    kw[u] = make_uint4(0, 0, 0, 0);
-                    vw[u] = make_uint4(0, 0, 0, 0);
-                }
-            }
-        }
-    };
-    uint4 kw[DEC_UNROLL], vw[DEC_UNROLL], kw_next[DEC_UNROLL], vw_next[DEC_UNROLL];
-#pragma unroll
-    for (int u = 0; u < DEC_UNROLL; ++u) kw_next[u] = vw_next[u] = make_uint4(0, 0, 0, 0);
-    fetch(c_begin + warp * STEP, kw_next, vw_next);
     for (int base = c_begin + warp * STEP; base < c_end; base += DEC_WARPS * STEP) {
 #pragma unroll
         for (int u = 0; u < DEC_UNROLL; ++u) { kw[u] = kw_next[u]; vw[u] = vw_next[u]; }

@@ -391,7 +391,7 @@ __device__ __forceinline__ void rows_block(const EvalParams& P, const RowsArgs& 
             for (int j = 0; j < 4; ++j) {
                 float d = v[i][j] - mean;
                 v[i][j] = d;
-                q += (col_of(i, j) < C) ? d * d : 0.0f;
+                if (col_of(i, j) < C) q = __fmaf_rn(d, d, q);  // pinned: the staged kernel forms the same sums
             }
         q = group_sum<GROUP>(q, smem) / (float)C;
         const float inv_sd = 1.0f / sqrtf(q + A.eps);  // one division per row
@@ -403,7 +403,7 @@ __device__ __forceinline__ void rows_block(const EvalParams& P, const RowsArgs& 
                 if (c < C) {
                     float g = A.gain ? A.gain[c] : 1.0f;
                     float b = (A.bias && kind == JSM_ROWS_LAYERNORM) ? A.bias[c] : 0.0f;
-                    v[i][j] = g * (v[i][j] * inv_sd) + b;
+                    v[i][j] = __fmaf_rn(g, __fmul_rn(v[i][j], inv_sd), b);
                 }
             }
     }
@@ -645,7 +645,7 @@ __global__ void __launch_bounds__(RS_THREADS) rows_staged_kernel(StagedArgs A) {
                 for (int j = 0; j < 4; ++j) {
                     const float d = v[i][j] - mean;
                     v[i][j] = d;
-                    q += d * d;
+                    q = __fmaf_rn(d, d, q);
                 }
             q = rs_sum(q, KIND == JSM_ROWS_LAYERNORM ? red[1] : red[par]) / (float)C;
             par ^= 1;
@@ -653,10 +653,10 @@ __global__ void __launch_bounds__(RS_THREADS) rows_staged_kernel(StagedArgs A) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const float4 g = gain4[i], b = bias4[i];
-                v[i][0] = g.x * (v[i][0] * inv_sd) + b.x;
-                v[i][1] = g.y * (v[i][1] * inv_sd) + b.y;
-                v[i][2] = g.z * (v[i][2] * inv_sd) + b.z;
-                v[i][3] = g.w * (v[i][3] * inv_sd) + b.w;
+                v[i][0] = __fmaf_rn(g.x, __fmul_rn(v[i][0], inv_sd), b.x);
+                v[i][1] = __fmaf_rn(g.y, __fmul_rn(v[i][1], inv_sd), b.y);
+                v[i][2] = __fmaf_rn(g.z, __fmul_rn(v[i][2], inv_sd), b.z);
+                v[i][3] = __fmaf_rn(g.w, __fmul_rn(v[i][3], inv_sd), b.w);
             }
         }
         if (ok) {

@@ -166,6 +166,42 @@ def test_row_kernels_ragged_shapes(shape):
     assert np.array_equal(am.cpu().numpy().ravel(), A.argmax(axis=1))
 
 
+@pytest.mark.parametrize("cols", [1024, 2048, 4096])
+@pytest.mark.parametrize("rows", [1, 7, 300, 613])
+def test_staged_row_kernels_match_oracle_and_register_kernel(rows, cols):
+    """Contiguous f32 rows of 1024 / 2048 / 4096 columns with the programs x, x*imm+y and x+y run through the kernels
+    that stage rows in shared memory (a fixed grid: one row, fewer rows than CTAs, more rows than CTAs with a
+    remainder).  Checked against the oracle and, bit for bit, against the register kernel: the same program with
+    `+ 0.0` appended is not one of the staged forms, takes the register kernel and has the same values."""
+    A = cases.normal((rows, cols), 170, cols)
+    B = cases.normal((rows, cols), 171, cols)
+    g = cases.uniform((cols,), 172, 0, 0.5, 1.5)
+    bb = cases.normal((cols,), 173, 1) * np.float32(0.1)
+    a, b = dev(A), dev(B)
+    plus0 = [(jb.OP_IMM, 0.0), (jb.OP_ADD,)]
+    y, y2 = torch.empty_like(a), torch.empty_like(a)
+    axpb = program_for(8, 0.125)
+    add = [L0, L1, (jb.OP_ADD,)]
+    for name, kind, prog, leaves, kw, want in [
+        ("softmax", jb.ROWS_SOFTMAX, axpb, [a, b], {}, lambda: port.hsoftmax(A, B, 0.125)),
+        ("layernorm", jb.ROWS_LAYERNORM, add, [a, b], dict(gain=dev(g), bias=dev(bb), eps=1e-5), lambda: port.layer_norm(A, B, g, bb, 1e-5)),
+        ("rmsnorm", jb.ROWS_RMSNORM, [L0], [a], dict(gain=dev(g), eps=1e-5), lambda: port.rms_norm(A, g, 1e-5)),
+    ]:
+        jb.eval_rows(kind, 1, prog, leaves, y, **kw)
+        jb.eval_rows(kind, 1, prog + plus0, leaves, y2, **kw)
+        assert_close(host(y), want(), FP32_RTOL, f"staged {name} {rows}x{cols}")
+        assert torch.equal(y, y2), f"staged {name} differs from the register kernel ({rows}x{cols})"
+    s, s2 = torch.empty(rows, 1, device="cuda"), torch.empty(rows, 1, device="cuda")
+    for name, kind, prog, leaves in [("sum", jb.ROWS_SUM, [L0], [a]), ("mean", jb.ROWS_MEAN, [L0], [a]), ("max", jb.ROWS_MAX, [L0], [b]),
+                                     ("sum(a+b)", jb.ROWS_SUM, add, [a, b]), ("max(a*0.125+b)", jb.ROWS_MAX, axpb, [a, b])]:
+        jb.eval_rows(kind, 1, prog, leaves, s)
+        jb.eval_rows(kind, 1, prog + plus0, leaves, s2)
+        assert torch.equal(s, s2), f"staged row {name} differs from the register kernel ({rows}x{cols})"
+    jb.eval_rows(jb.ROWS_SUM, 1, [L0], [a], s)
+    assert float((s.ravel() - a.double().sum(dim=1).float()).abs().max()) < 1e-3
+    jb.check(jb.lib().jsm_check_device_errors(jb.stream_ptr()))
+
+
 def test_config2_full_size_properties():
     """Configuration 2 at 4096 x 4096: rows of the softmax sum to one, normalised rows have zero mean and
     unit variance, and 64 sampled rows equal the oracle."""

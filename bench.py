@@ -587,7 +587,7 @@ def main():
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (185.7e6 if (world == 1 and B <= 16) else None),
+                     "traffic": (185.3e6 if (world == 1 and B <= 16) else None),
                      "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape at 8 tokens "
                                      "from one ncu capture (profiles/linear_packed_gate_up_b8_ncu.md); algorithmic bytes_per_launch beside it",
                      "kernel": "linear_packed_kernel: gate/up projection weight stream (jsm_linear_bf16_packed, silu*up epilogue)",

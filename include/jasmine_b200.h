@@ -332,8 +332,19 @@ jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64);
 jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr);
 jsm_status jsm_ipc_close(void* d_ptr);
 
-/* Device pointer / element count of a named weight of this rank's shard ("layers.3.wqkv", "lm_head", ...). */
+/* Device pointer / element count of a named weight of this rank's shard ("layers.3.wqkv", "lm_head", ...).
+ * Projections come back row-major [out, in] bf16 (wgu: gate rows, then up rows) in their stored form, i.e. with the
+ * gain of the RMSNorm in front of them (wqkv: g1, wgu: g2, lm_head: gf) multiplied into their columns; gains are f32 [d]. */
 jsm_status jsm_llama_weight(jsm_model* m, const char* name, void** d_ptr, size_t* n_elems);
+/* Weight injection (the reference's init_t<tag>::cal, mat_init_t.hpp:10-118): replaces a named tensor of this rank's
+ * shard from device memory - "emb" bf16 [vocab, d]; "gf", "layers.L.g1|g2" f32 [d]; "lm_head", "layers.L.wqkv|wo|wgu|
+ * wdown" bf16 row-major [out, in] WITHOUT the gain folded in: the call multiplies the current gain of the norm in front
+ * of the projection into its columns, so set a gain before the projection that follows it. */
+jsm_status jsm_llama_set_weight(jsm_model* m, const char* name, const void* d_src, size_t n_elems, void* stream);
+/* Flat binary checkpoint of this rank's tensors in their stored form (the reference has no serialisation:
+ * mat_t.hpp:322-336 prints text only).  jsm_llama_load checks that shape and tensor-parallel rank match. */
+jsm_status jsm_llama_save(jsm_model* m, const char* path);
+jsm_status jsm_llama_load(jsm_model* m, const char* path);
 /* Prefill `T` prompt tokens of sequence `seq` (positions 0..T-1); writes the argmax of the last position to d_next[seq]. */
 jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T, int32_t* d_next, float* d_logits_last,
                              void* stream);

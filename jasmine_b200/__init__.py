@@ -103,6 +103,9 @@ SYMBOLS = {
     "jsm_ipc_import": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "jsm_ipc_close": (_i, [_vp]),
     "jsm_llama_weight": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(_sz)]),
+    "jsm_llama_set_weight": (_i, [_vp, C.c_char_p, _vp, _sz, _vp]),
+    "jsm_llama_save": (_i, [_vp, C.c_char_p]),
+    "jsm_llama_load": (_i, [_vp, C.c_char_p]),
     "jsm_llama_prefill": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "jsm_llama_decode_step": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "jsm_llama_set_context": (_i, [_vp, _i, _i]),

@@ -114,6 +114,16 @@ __global__ void __launch_bounds__(256) fill_packed_kernel(uint8_t* __restrict__ 
         reinterpret_cast<uint4*>(dst)[idx] = v;
     }
 }
+// dst[r, k] = bf16(src[r, k] * gain[k]): the fold of a norm's gain into the projection behind it, rounded like the
+// generated weights
+__global__ void __launch_bounds__(256) scale_cols_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                         long long rows, int K, const float* __restrict__ gain) {
+    const long long n = rows * K;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float g = gain ? gain[(int)(i % K)] : 1.0f;
+        dst[i] = __float2bfloat16_rn(__bfloat162float(src[i]) * g);
+    }
+}
 // row-major fill of a shard (the embedding table, which is gathered and not streamed)
 __global__ void fill_shard_kernel(__nv_bfloat16* dst, long long rows, long long cols, long long full_cols, long long row0,
                                   long long col0, uint64_t key, float std) {
@@ -630,6 +640,147 @@ jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions) {
         m->tp_regions[r] = p;
     }
     m->tp_connected = true;
+    return JSM_OK;
+}
+
+namespace {
+// a named tensor of the rank's shard: either plain (ptr, bytes) or a packed projection (packed, N, K, paired, gain in front)
+struct TensorRef {
+    void* plain = nullptr;
+    size_t plain_bytes = 0;
+    bool f32 = false;
+    uint8_t* packed = nullptr;
+    int N = 0, K = 0, paired = 0;
+    const float* gain = nullptr;
+};
+bool find_tensor(jsm_model* m, const char* name, TensorRef& t) {
+    const int d = m->c.d_model, D = m->c.head_dim;
+    std::string s(name);
+    if (s == "emb") { t.plain = m->emb; t.plain_bytes = (size_t)m->c.vocab * d * 2; return true; }
+    if (s == "gf") { t.plain = m->gf; t.plain_bytes = (size_t)d * 4; t.f32 = true; return true; }
+    if (s == "lm_head") { t.packed = m->lm_head; t.N = m->c.vocab; t.K = d; t.gain = m->gf; return true; }
+    int l = -1;
+    char field[32] = "";
+    if (sscanf(name, "layers.%d.%31s", &l, field) != 2 || l < 0 || l >= m->c.n_layers) return false;
+    jsm::LayerW& L = m->layers[l];
+    std::string f(field);
+    if (f == "g1") { t.plain = L.g1; t.plain_bytes = (size_t)d * 4; t.f32 = true; return true; }
+    if (f == "g2") { t.plain = L.g2; t.plain_bytes = (size_t)d * 4; t.f32 = true; return true; }
+    if (f == "wqkv") { t.packed = L.wqkv; t.N = m->qkv_dim; t.K = d; t.gain = L.g1; return true; }
+    if (f == "wo") { t.packed = L.wo; t.N = d; t.K = m->Hq_l * D; return true; }
+    if (f == "wgu") { t.packed = L.wgu; t.N = m->ffn_l; t.K = d; t.paired = 1; t.gain = L.g2; return true; }
+    if (f == "wdown") { t.packed = L.wdown; t.N = d; t.K = m->ffn_l; return true; }
+    return false;
+}
+jsm_status grow_unpack(jsm_model* m, size_t elems) {
+    if (elems <= m->unpack_elems) return JSM_OK;
+    JSM_CUDA_CHECK(cudaDeviceSynchronize());
+    if (m->unpack_buf) cudaFree(m->unpack_buf);
+    m->unpack_buf = nullptr; m->unpack_elems = 0;
+    JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&m->unpack_buf), elems * sizeof(__nv_bfloat16)));
+    m->unpack_elems = elems;
+    return JSM_OK;
+}
+std::vector<std::string> tensor_names(const jsm_model* m) {
+    std::vector<std::string> v = {"emb", "gf", "lm_head"};
+    for (int l = 0; l < m->c.n_layers; ++l)
+        for (const char* f : {"g1", "g2", "wqkv", "wo", "wgu", "wdown"}) v.push_back("layers." + std::to_string(l) + "." + f);
+    return v;
+}
+constexpr char CKPT_MAGIC[8] = {'J', 'S', 'M', 'C', 'K', 'P', 'T', '1'};
+}  // namespace
+
+// Weight injection: the reference takes weights through init_t<tag>::cal (mat_init_t.hpp:10-118); here a tensor of the
+// rank's shard is replaced from device memory.  Projections arrive row-major [out, in] in bf16 (wgu: gate rows then up
+// rows), are multiplied column-wise by the gain of the RMSNorm in front of them (wqkv: g1, wgu: g2, lm_head: gf - the
+// kernels apply that norm without a gain) and packed.  So: set a gain before the projection that follows it.
+jsm_status jsm_llama_set_weight(jsm_model* m, const char* name, const void* d_src, size_t n_elems, void* stream) {
+    if (!m || !name || !d_src) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_set_weight: null argument");
+    TensorRef t;
+    if (!find_tensor(m, name, t)) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_set_weight: unknown tensor '%s'", name);
+    cudaStream_t st = as_stream(stream);
+    if (t.plain) {
+        const size_t want = t.plain_bytes / (t.f32 ? 4 : 2);
+        if (n_elems != want) JSM_FAIL(JSM_SHAPE, "jsm_llama_set_weight: '%s' has %zu elements, got %zu", name, want, n_elems);
+        JSM_CUDA_CHECK(cudaMemcpyAsync(t.plain, d_src, t.plain_bytes, cudaMemcpyDeviceToDevice, st));
+        return JSM_OK;
+    }
+    const size_t rows = (size_t)(t.paired ? 2 * t.N : t.N), elems = rows * t.K;
+    if (n_elems != elems) JSM_FAIL(JSM_SHAPE, "jsm_llama_set_weight: '%s' has %zu elements, got %zu", name, elems, n_elems);
+    jsm_status s = grow_unpack(m, elems);
+    if (s != JSM_OK) return s;
+    scale_cols_kernel<<<(unsigned)std::min<size_t>((elems + 255) / 256, 148 * 16), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(d_src), m->unpack_buf, (long long)rows, t.K, t.gain);
+    JSM_LAUNCH_CHECK();
+    return linear_pack_launch(m->unpack_buf, t.N, t.K, t.paired, t.packed, false, st);
+}
+
+// Flat binary checkpoint of the rank's tensors in their stored form (packed projections with the gains folded in,
+// gains, embedding): magic, the model configuration, then per tensor {u32 name length, name, u64 bytes, bytes}.
+// The reference has no serialisation (mat_t.hpp:322-336 prints text only).  Loading checks the configuration.
+jsm_status jsm_llama_save(jsm_model* m, const char* path) {
+    if (!m || !path) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_save: null argument");
+    FILE* f = fopen(path, "wb");
+    if (!f) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_save: cannot open '%s'", path);
+    JSM_CUDA_CHECK(cudaDeviceSynchronize());
+    std::vector<uint8_t> host;
+    bool ok = fwrite(CKPT_MAGIC, 1, 8, f) == 8 && fwrite(&m->c, sizeof(m->c), 1, f) == 1;
+    for (const std::string& name : tensor_names(m)) {
+        if (!ok) break;
+        TensorRef t;
+        find_tensor(m, name.c_str(), t);
+        const void* src = t.plain ? t.plain : t.packed;
+        const uint64_t bytes = t.plain ? t.plain_bytes : linear_packed_bytes(t.N, t.K, t.paired);
+        host.resize(bytes);
+        if (cudaMemcpy(host.data(), src, bytes, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = false; break; }
+        const uint32_t nl = (uint32_t)name.size();
+        ok = fwrite(&nl, 4, 1, f) == 1 && fwrite(name.data(), 1, nl, f) == nl && fwrite(&bytes, 8, 1, f) == 1 &&
+             fwrite(host.data(), 1, bytes, f) == bytes;
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) JSM_FAIL(JSM_CUDA, "jsm_llama_save: writing '%s' failed", path);
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_load(jsm_model* m, const char* path) {
+    if (!m || !path) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: null argument");
+    FILE* f = fopen(path, "rb");
+    if (!f) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: cannot open '%s'", path);
+    char magic[8];
+    jsm_model_config c;
+    if (fread(magic, 1, 8, f) != 8 || memcmp(magic, CKPT_MAGIC, 8) != 0 || fread(&c, sizeof(c), 1, f) != 1) {
+        fclose(f);
+        JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: '%s' is not a checkpoint of this library", path);
+    }
+    const jsm_model_config& o = m->c;
+    if (c.n_layers != o.n_layers || c.d_model != o.d_model || c.n_heads != o.n_heads || c.n_kv_heads != o.n_kv_heads ||
+        c.head_dim != o.head_dim || c.d_ffn != o.d_ffn || c.vocab != o.vocab || c.tp_rank != o.tp_rank || c.tp_size != o.tp_size) {
+        fclose(f);
+        JSM_FAIL(JSM_SHAPE, "jsm_llama_load: the checkpoint was written by a model of another shape or another tensor-parallel rank");
+    }
+    JSM_CUDA_CHECK(cudaDeviceSynchronize());
+    std::vector<uint8_t> host;
+    std::vector<char> nm;
+    size_t seen = 0;
+    const size_t expect = tensor_names(m).size();
+    while (true) {
+        uint32_t nl = 0;
+        if (fread(&nl, 4, 1, f) != 1) break;  // end of file
+        uint64_t bytes = 0;
+        nm.assign(nl + 1, 0);
+        if (nl > 256 || fread(nm.data(), 1, nl, f) != nl || fread(&bytes, 8, 1, f) != 1) { fclose(f); JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: truncated record"); }
+        TensorRef t;
+        if (!find_tensor(m, nm.data(), t)) { fclose(f); JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: unknown tensor '%s'", nm.data()); }
+        const uint64_t want = t.plain ? t.plain_bytes : linear_packed_bytes(t.N, t.K, t.paired);
+        if (bytes != want) { fclose(f); JSM_FAIL(JSM_SHAPE, "jsm_llama_load: '%s' holds %llu bytes, the model %llu", nm.data(), (unsigned long long)bytes, (unsigned long long)want); }
+        host.resize(bytes);
+        if (fread(host.data(), 1, bytes, f) != bytes) { fclose(f); JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: truncated tensor '%s'", nm.data()); }
+        cudaError_t e = cudaMemcpy(t.plain ? t.plain : (void*)t.packed, host.data(), bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { fclose(f); JSM_FAIL(JSM_CUDA, "jsm_llama_load: upload of '%s': %s", nm.data(), cudaGetErrorString(e)); }
+        ++seen;
+    }
+    fclose(f);
+    if (seen != expect) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_load: %zu tensors in the file, the model has %zu", seen, expect);
     return JSM_OK;
 }
 

@@ -75,6 +75,16 @@ class Llama:
             return buf
         return (buf.astype(np.uint32) << 16).view(np.float32)
 
+    def set_weight(self, name: str, tensor):
+        """Replaces a tensor of this rank's shard from a CUDA tensor (bf16 row-major [out, in]; gains f32 [d])."""
+        check(lib().jsm_llama_set_weight(self._h, name.encode(), tensor.data_ptr(), tensor.numel(), stream_ptr()))
+
+    def save(self, path: str):
+        check(lib().jsm_llama_save(self._h, str(path).encode()))
+
+    def load(self, path: str):
+        check(lib().jsm_llama_load(self._h, str(path).encode()))
+
     def prefill(self, ids, seq: int, next_tokens=None, logits_last=None):
         check(lib().jsm_llama_prefill(self._h, ids.data_ptr(), seq, ids.numel(),
                                       next_tokens.data_ptr() if next_tokens is not None else None,

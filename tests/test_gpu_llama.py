@@ -90,3 +90,69 @@ def test_decode_step_is_replayable_in_a_cuda_graph():
         outs.append(toks)
         m.close()
     assert outs[0] == outs[1]
+
+
+def _greedy(m, prompts, n_gen, vocab):
+    batch = len(prompts)
+    nxt = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    for b in range(batch):
+        m.prefill(torch.from_numpy(prompts[b]).cuda(), b, nxt)
+    logits = torch.empty(batch, vocab, device="cuda")
+    toks = []
+    for _ in range(n_gen):
+        ids = nxt.clone()
+        toks.append(ids.cpu().numpy().copy())
+        m.decode_step(ids, nxt, logits)
+    return np.stack(toks), host(logits)
+
+
+def test_checkpoint_round_trip_and_weight_injection(tmp_path):
+    """(1) save / load: a model created from another seed generates the saved model's tokens and logits, bit for bit,
+    after loading its checkpoint; a checkpoint of another shape is refused.  (2) weight injection with gains that are
+    not one: the model with injected (g1, g2, gf, un-folded projections) matches the oracle run on the same tensors."""
+    cfg = dict(L=2, d=256, Hq=4, Hkv=2, D=128, ffn=512, vocab=1024, eps=1e-5, theta=10000.0)
+    mk = lambda seed, L=2: Llama(L, cfg["d"], cfg["Hq"], cfg["Hkv"], cfg["ffn"], cfg["vocab"], max_batch=2, max_context=128, seed=seed)
+    prompts = [cases.ints(24, 4, 300 + b, 0, cfg["vocab"]) for b in range(2)]
+    a, b = mk(11), mk(12)
+    ta, la = _greedy(a, prompts, 4, cfg["vocab"])
+    tb, _ = _greedy(b, prompts, 4, cfg["vocab"])
+    assert not np.array_equal(ta, tb)
+    path = tmp_path / "model.jsmckpt"
+    a.save(path)
+    b.reset()
+    b.load(path)
+    tb, lb = _greedy(b, prompts, 4, cfg["vocab"])
+    assert np.array_equal(ta, tb) and np.array_equal(la, lb)
+    other = mk(13, L=1)
+    with pytest.raises(jb.JsmError):
+        other.load(path)
+    other.close()
+    # ---- injection: tensors made here, gains in [0.5, 1.5]
+    d, D, ffn, V = cfg["d"], cfg["D"], cfg["ffn"], cfg["vocab"]
+    bf = lambda x: torch.from_numpy(x).cuda().to(torch.bfloat16)
+    wide = lambda t: t.float().cpu().numpy()
+    b.reset()
+    layers = []
+    emb = bf(cases.normal((V, d), 21, 0, 0.02)); b.set_weight("emb", emb)
+    gf = torch.from_numpy(cases.uniform((d,), 21, 1, 0.5, 1.5)).cuda(); b.set_weight("gf", gf)
+    wlm = bf(cases.normal((V, d), 21, 2, 0.02)); b.set_weight("lm_head", wlm)
+    for l in range(cfg["L"]):
+        g1 = torch.from_numpy(cases.uniform((d,), 22 + l, 0, 0.5, 1.5)).cuda()
+        g2 = torch.from_numpy(cases.uniform((d,), 22 + l, 1, 0.5, 1.5)).cuda()
+        wqkv = bf(cases.normal(((cfg["Hq"] + 2 * cfg["Hkv"]) * D, d), 22 + l, 2, 0.02))
+        wo = bf(cases.normal((d, cfg["Hq"] * D), 22 + l, 3, 0.02))
+        wgu = bf(cases.normal((2 * ffn, d), 22 + l, 4, 0.02))
+        wdown = bf(cases.normal((d, ffn), 22 + l, 5, 0.02))
+        b.set_weight(f"layers.{l}.g1", g1); b.set_weight(f"layers.{l}.g2", g2)   # gains first
+        b.set_weight(f"layers.{l}.wqkv", wqkv); b.set_weight(f"layers.{l}.wo", wo)
+        b.set_weight(f"layers.{l}.wgu", wgu); b.set_weight(f"layers.{l}.wdown", wdown)
+        q = wide(wqkv)
+        layers.append((g1.cpu().numpy(), q[:cfg["Hq"] * D], q[cfg["Hq"] * D:(cfg["Hq"] + cfg["Hkv"]) * D], q[(cfg["Hq"] + cfg["Hkv"]) * D:],
+                       wide(wo), g2.cpu().numpy(), wide(wgu)[:ffn], wide(wgu)[ffn:], wide(wdown)))
+    nxt = torch.zeros(2, dtype=torch.int32, device="cuda")
+    last = torch.empty(V, device="cuda")
+    for s in range(2):
+        b.prefill(torch.from_numpy(prompts[s]).cuda(), s, nxt, last)
+        want = ol.llama_forward(cfg, wide(emb), layers, gf.cpu().numpy(), wide(wlm), prompts[s])[-1]
+        assert_close(host(last), want, BF16_RTOL, f"injected weights, prefill logits of sequence {s}")
+    a.close(); b.close()

@@ -16,6 +16,7 @@
 // Every wait is bounded; on a timeout the CTA unwinds, frees its TMEM and records a code for the host.
 #include "attn.cuh"
 #include "tc_utils.cuh"
+#include <stdlib.h>
 #include <math.h>
 
 namespace jsm {
@@ -67,6 +68,30 @@ struct FlashParams {
     int* err;
 };
 
+// 2^x for a pair of scores without the special-function unit: x = n + f with n = round(x) taken from the mantissa of
+// x + 1.5 * 2^23, 2^f on [-0.5, 0.5] by a cubic (relative error 7.5e-5, far below the bf16 rounding of P), n added to
+// the exponent field.  The MUFU pipe (16 results per clock and SM) is what the softmax of a tile waits for once the
+// tensor pipe runs tcgen05 rates, so a share of the exponentials goes to the FMA pipe instead.
+__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x2, x0, x1);
+    x2 = pack2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic2 = pack2(12582912.0f, 12582912.0f), neg_magic2 = pack2(-12582912.0f, -12582912.0f);
+    const uint64_t r2 = fadd2(x2, magic2);
+    const uint64_t n2 = fadd2(r2, neg_magic2);
+    const uint64_t f2 = ffma2(n2, pack2(-1.0f, -1.0f), x2);
+    uint64_t q2 = ffma2(pack2(0.0551716685f, 0.0551716685f), f2, pack2(0.2426111251f, 0.2426111251f));
+    q2 = ffma2(q2, f2, pack2(0.6932609677f, 0.6932609677f));
+    q2 = ffma2(q2, f2, pack2(0.9999280572f, 0.9999280572f));
+    float q0, q1, r0, r1;
+    unpack2(q2, q0, q1);
+    unpack2(r2, r0, r1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(r0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(r1) << 23));
+}
+
+// POLY: of every four pairs of scores, this many take ex2_poly2 instead of ex2.approx
+template <int POLY>
 __global__ void __launch_bounds__(FA_THREADS, 1)
     flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, FlashParams P) {
@@ -292,9 +317,16 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float x0, x1;
-                    unpack2(ffma2(pack2(sv[2 * (c + i)], sv[2 * (c + i) + 1]), sc2, neg_m2), x0, x1);
-                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    const uint64_t x2 = ffma2(pack2(sv[2 * (c + i)], sv[2 * (c + i) + 1]), sc2, neg_m2);
+                    float p0, p1;
+                    if ((i & 3) < POLY) {
+                        ex2_poly2(x2, p0, p1);
+                    } else {
+                        float x0, x1;
+                        unpack2(x2, x0, x1);
+                        p0 = ex2_approx(x0);
+                        p1 = ex2_approx(x1);
+                    }
                     ls2[i & 3] = fadd2(ls2[i & 3], pack2(p0, p1));
                     w[i] = pack_bf16x2(p0, p1);
                 }
@@ -367,13 +399,23 @@ jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, voi
     P.out_rs = o_rs;
     P.err = tc_error_word();
     const size_t smem = (size_t)(2 + 2 * FA_KV_STAGES) * FA_TILE_BYTES + 1024;
+    static int poly = -1;
+    if (poly < 0) {
+        const char* e = getenv("JSM_FA_POLY");
+        poly = e ? atoi(e) : 1;
+        if (poly < 0 || poly > 2) poly = 1;
+    }
     static bool attr_done = false;
     if (!attr_done) {
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_done = true;
     }
     dim3 grid((Tq + 2 * FA_BM - 1) / (2 * FA_BM), Hq, batch);
-    flash_prefill_kernel<<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
+    if (poly == 0) flash_prefill_kernel<0><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
+    else if (poly == 1) flash_prefill_kernel<1><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
+    else flash_prefill_kernel<2><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }

@@ -279,6 +279,12 @@ jsm_status jsm_attn_decode_static_scratch(const void* d_q, int64_t q_row_stride,
                                           void* stream);
 
 /* ---- token-level helpers (not in the reference) ------------------------- */
+/* Sampling from F32 logits [n_rows, vocab] (row pitch row_stride elements): temperature, top-k (0 = 1024, the most the
+ * sampler considers) and top-p in (0, 1]; temperature <= 0 or top_k == 1 gives the arg-max (the reference's generation
+ * loop, transformer_test.hpp:231-239, always takes it).  The draw of row r is the uniform number of the counter-based
+ * generator for (seed, step, r): the same arguments give the same tokens. */
+jsm_status jsm_sample(const float* d_logits, int64_t row_stride, int n_rows, int vocab, float temperature, int top_k,
+                      float top_p, uint64_t seed, uint64_t step, int32_t* d_out, void* stream);
 /* out[t, :] = table[ids[t], :] (+ pos_table[positions[t], :]) */
 jsm_status jsm_embedding(const void* d_table, const void* d_pos_table, const int32_t* d_ids,
                          const int32_t* d_positions, void* d_out, jsm_dtype dtype, int T, int d, void* stream);

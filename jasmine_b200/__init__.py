@@ -102,6 +102,7 @@ SYMBOLS = {
     "jsm_ipc_export": (_i, [_vp, C.c_char_p]),
     "jsm_ipc_import": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "jsm_ipc_close": (_i, [_vp]),
+    "jsm_sample": (_i, [_vp, C.c_int64, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_uint64, C.c_uint64, _vp, _vp]),
     "jsm_llama_weight": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(_sz)]),
     "jsm_llama_set_weight": (_i, [_vp, C.c_char_p, _vp, _sz, _vp]),
     "jsm_llama_save": (_i, [_vp, C.c_char_p]),
@@ -358,6 +359,17 @@ def fill(t, seed: int, tensor_id: int, dist: int, a: float, b: float):
     else:
         check(lib().jsm_fill_host(t.data_ptr(), dtype_of(t), t.numel(), seed, tensor_id, dist, a, b))
     return t
+
+
+def sample(logits, temperature=1.0, top_k=0, top_p=1.0, seed=0, step=0, out=None):
+    """Tokens drawn from F32 logits [rows, vocab] (temperature, top-k, top-p); int32 [rows]."""
+    torch = _torch()
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    check(lib().jsm_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature, top_k, top_p, seed, step,
+                           out.data_ptr(), stream_ptr()))
+    return out
 
 
 def check_device_errors():

@@ -226,6 +226,42 @@ __global__ void __launch_bounds__(256) elementwise_kernel(EvalParams P, OutDesc 
     }
 }
 
+// ---- K1f: the programs x * imm + y and x + y over contiguous f32 matrices ---------------
+// Four vectors per operand and thread are requested before the first use: 128 bytes in flight per thread.
+template <int PRO>
+__global__ void __launch_bounds__(256) elementwise_fast_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float imm,
+                                                               float4* __restrict__ out, long long n_vec) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n_vec; i += 4 * stride) {
+        float4 x[4], y[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { x[u] = __ldcs(a + i + u * stride); y[u] = __ldcs(b + i + u * stride); }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float4 r;
+            if (PRO == PRO_AXPB) {
+                r.x = __fadd_rn(__fmul_rn(x[u].x, imm), y[u].x); r.y = __fadd_rn(__fmul_rn(x[u].y, imm), y[u].y);
+                r.z = __fadd_rn(__fmul_rn(x[u].z, imm), y[u].z); r.w = __fadd_rn(__fmul_rn(x[u].w, imm), y[u].w);
+            } else {
+                r.x = x[u].x + y[u].x; r.y = x[u].y + y[u].y; r.z = x[u].z + y[u].z; r.w = x[u].w + y[u].w;
+            }
+            __stcs(out + i + u * stride, r);
+        }
+    }
+    for (; i < n_vec; i += stride) {
+        const float4 x = a[i], y = b[i];
+        float4 r;
+        if (PRO == PRO_AXPB) {
+            r.x = __fadd_rn(__fmul_rn(x.x, imm), y.x); r.y = __fadd_rn(__fmul_rn(x.y, imm), y.y);
+            r.z = __fadd_rn(__fmul_rn(x.z, imm), y.z); r.w = __fadd_rn(__fmul_rn(x.w, imm), y.w);
+        } else {
+            r.x = x.x + y.x; r.y = x.y + y.y; r.z = x.z + y.z; r.w = x.w + y.w;
+        }
+        out[i] = r;
+    }
+}
+
 // ---- group reductions (GROUP = 32: one warp per row, 256: one CTA per row) -------
 template <int GROUP>
 __device__ __forceinline__ float group_sum(float v, float* smem) {
@@ -1007,6 +1043,22 @@ jsm_status jsm_eval_elementwise(const jsm_instr* prog, int n_instr, const jsm_ma
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     cudaStream_t st = as_stream(stream);
+    // two contiguous f32 operands of the output's shape, x * imm + y or x + y: the batched-load kernel
+    const EvalParams& P = Lw.P;
+    if (vec && (P.pro == PRO_AXPB || P.pro == PRO_ADD) && P.n_leaves >= 2 && out.dtype == JSM_F32 && O.rs == Lw.C &&
+        P.leaf[0].kind == LK_FULL && P.leaf[1].kind == LK_FULL && P.leaf[0].dtype == JSM_F32 && P.leaf[1].dtype == JSM_F32 &&
+        P.leaf[0].rs == Lw.C && P.leaf[1].rs == Lw.C) {
+        const long long n_vec = (long long)Lw.R * Lw.C / 4;
+        long long fb = (n_vec + 1023) / 1024;
+        if (fb > (long long)sm_count() * 8) fb = (long long)sm_count() * 8;
+        if (fb < 1) fb = 1;
+        const float4* pa = reinterpret_cast<const float4*>(P.leaf[0].p);
+        const float4* pb = reinterpret_cast<const float4*>(P.leaf[1].p);
+        if (P.pro == PRO_AXPB) elementwise_fast_kernel<PRO_AXPB><<<(unsigned)fb, 256, 0, st>>>(pa, pb, P.pro_imm, reinterpret_cast<float4*>(O.p), n_vec);
+        else elementwise_fast_kernel<PRO_ADD><<<(unsigned)fb, 256, 0, st>>>(pa, pb, 0.0f, reinterpret_cast<float4*>(O.p), n_vec);
+        JSM_LAUNCH_CHECK();
+        return JSM_OK;
+    }
     if (vec) {
         if (Lw.depth <= 4) elementwise_kernel<4, true><<<(unsigned)blocks, 256, 0, st>>>(Lw.P, O);
         else elementwise_kernel<8, true><<<(unsigned)blocks, 256, 0, st>>>(Lw.P, O);

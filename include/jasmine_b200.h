@@ -17,6 +17,9 @@
  *    Calls are asynchronous on that stream unless stated otherwise.
  *  - No call falls back to the CPU.  Without a usable device every compute call
  *    returns JSM_CUDA.
+ *  - The library reads one environment variable: JSM_PDL=0 launches the chained
+ *    kernels of a decode step in plain stream order instead of with programmatic
+ *    dependent launch (same results; for debugging launch-order problems).
  */
 #ifndef JASMINE_B200_H_
 #define JASMINE_B200_H_
@@ -179,9 +182,14 @@ jsm_status jsm_linear_bf16(const void* d_X, const void* d_W, const float* d_bias
  * epilogue 3 (silu(gate)*up), N being the number of gate rows.
  * jsm_linear_packed_bytes: size of the packed image.  jsm_linear_pack / jsm_linear_unpack convert between the
  * reference's [out, in] layout and the packed image.  jsm_linear_bf16_packed: any T (chunks of 256 tokens);
- * N % 4 == 0, K % 8 == 0; it keeps a grow-only per-device workspace (first call of a shape allocates: make it
- * outside stream capture) that overlapping calls on different streams would share. */
+ * N % 4 == 0, K % 8 == 0.  The tiles that several CTAs share are reduced through a per-device workspace that the calls
+ * on a device share (calls that overlap on different streams would race on it).  The compute call never allocates:
+ * jsm_linear_pack (or jsm_linear_packed_reserve, for a packed image that was loaded rather than packed here) sizes the
+ * workspace of the current device for that shape - both synchronise the device and may allocate, so call them at
+ * set-up time, outside any stream capture; jsm_linear_bf16_packed returns JSM_INVALID_ARG when the workspace of the
+ * current device was never reserved for a shape this large. */
 size_t jsm_linear_packed_bytes(int N, int K, int paired);
+jsm_status jsm_linear_packed_reserve(int N, int K, int paired);
 /* The work split of a packed projection: tiles of 128 packed rows, k-blocks of 64 per tile, CTAs in the grid
  * (CTA c streams units [c*U/G, (c+1)*U/G) of the U = n_tiles*kbt units) and the most CTAs that share one tile. */
 jsm_status jsm_linear_packed_plan(int N, int K, int paired, int* n_tiles, int* kbt, int* grid, int* max_slots);
@@ -236,8 +244,11 @@ jsm_status jsm_kv_append(void* d_pool, const int32_t* d_block_table, int max_pag
 /* One query token per sequence against its cached context (split-K over the
  * context, then a combine pass).  q:[n_seqs, Hq*D] bf16 (rotated here when a
  * rope table is given, at position context_len-1), out:[n_seqs, Hq*D] bf16.
- * d_scratch: F32, jsm_attn_decode_scratch_bytes() bytes. */
+ * d_scratch: F32, jsm_attn_decode_scratch_bytes() bytes for exactly this n_seqs.  The split of the context into chunks
+ * depends on n_seqs (few sequences get short chunks), so the bytes are NOT monotone in n_seqs: a buffer that is reused
+ * for every call of 1..max_seqs sequences must hold jsm_attn_decode_scratch_bytes_max(max_seqs, ...) bytes. */
 size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int max_context);
+size_t jsm_attn_decode_scratch_bytes_max(int max_seqs, int Hq, int D, int max_context);
 jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, const void* d_pool,
                            const int32_t* d_block_table, int max_pages, const int32_t* d_context_lens,
                            int n_seqs, int Hq, int Hkv, int D, float scale, const float* d_rope_table,
@@ -267,7 +278,9 @@ jsm_status jsm_attn_decode_append(const void* d_q, int64_t q_row_stride, const v
  *    JSM_ATTN_DECODE_STATIC_SCRATCH_BYTES (8 MiB, held by every GPU that loads the library until
  *    the process exits); larger problems are rejected with JSM_UNSUPPORTED.
  *  - The first call on each device looks up the device address of the array; make that first call
- *    outside any stream capture.
+ *    outside any stream capture.  The address is cached per device ordinal for the life of the
+ *    process: after the device's primary context has been reset (cudaDeviceReset) in the same
+ *    process the cached address is stale and this entry point must not be used any more.
  *  - All calls on a device share the array and it keeps the contents of the last call.  Nothing in
  *    it has to start at zero (every slot that is read is written first by the same call), but two
  *    calls that overlap on the GPU (different streams) race on it: serialise them. */
@@ -355,7 +368,10 @@ jsm_status jsm_llama_load(jsm_model* m, const char* path);
 jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T, int32_t* d_next, float* d_logits_last,
                              void* stream);
 /* One greedy decode step for sequences 0..batch-1: d_ids[b] is appended at the
- * sequence's current length; d_next[b] = argmax of the logits; d_logits (or NULL): F32 [batch, vocab]. */
+ * sequence's current length; d_next[b] = argmax of the logits; d_logits (or NULL): F32 [batch, vocab].
+ * A sequence whose context already holds max_context tokens cannot grow: its context length stays where it is, the new
+ * token overwrites the last cached position (no access outside the sequence's pages or the rope table), its outputs of
+ * this step are meaningless and the next jsm_check_device_errors returns JSM_SHAPE ("context overflow"). */
 jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, int32_t* d_next, float* d_logits,
                                  void* stream);
 /* Host-side bookkeeping of context lengths (advance after a captured step is replayed). */

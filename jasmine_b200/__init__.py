@@ -79,6 +79,7 @@ SYMBOLS = {
     "jsm_trace_begin": (_i, [_i]),
     "jsm_trace_end": (_i, [_vp, _i, C.POINTER(_i), C.POINTER(_i)]),
     "jsm_linear_pack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "jsm_linear_packed_reserve": (_i, [_i, _i, _i]),
     "jsm_linear_unpack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "jsm_linear_bf16_packed": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "jsm_rope_table": (_i, [_vp, _i, _i, _f, _i, _vp]),
@@ -86,6 +87,7 @@ SYMBOLS = {
     "jsm_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
     "jsm_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "jsm_attn_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
+    "jsm_attn_decode_scratch_bytes_max": (_sz, [_i, _i, _i, _i]),
     "jsm_attn_decode": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp]),
     "jsm_attn_decode_append": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp, _vp, _vp]),
     "jsm_attn_decode_static_scratch": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _vp]),

@@ -7,7 +7,6 @@ namespace jsm {
 jsm_status attn_simt_launch(const void* q, const void* k, const void* v, void* out, jsm_dtype dtype, int batch, int Tq, int Tk,
                             int Hq, int Hkv, int D, int causal, float scale, const float* rope, cudaStream_t st,
                             long long q_row_stride = 0, long long kv_row_stride = 0, long long out_row_stride = 0, int pos0 = 0);
-bool flash_available();
 jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, void* out, int batch, int Tq, int Tk, int Hq, int Hkv,
                                 int causal, float scale, const float* rope, cudaStream_t st, long long q_row_stride = 0,
                                 long long kv_row_stride = 0, long long out_row_stride = 0);

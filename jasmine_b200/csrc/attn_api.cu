@@ -29,7 +29,7 @@ extern "C" jsm_status jsm_attn_prefill(const void* d_q, const void* d_k, const v
     if (dtype != JSM_F32 && dtype != JSM_BF16) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_prefill: dtype %d", (int)dtype);
     if (causal && T_k < T_q) JSM_FAIL(JSM_SHAPE, "jsm_attn_prefill: causal attention needs T_k >= T_q");
     cudaStream_t st = as_stream(stream);
-    const bool flash_ok = dtype == JSM_BF16 && D == 128 && flash_available();
+    const bool flash_ok = dtype == JSM_BF16 && D == 128;
     if (impl == 2 && !flash_ok) JSM_FAIL(JSM_UNSUPPORTED, "jsm_attn_prefill: the tcgen05 kernel needs bf16 and head_dim 128");
     if (impl == 2 || (impl == 0 && flash_ok && T_q >= 128)) {
         if (!d_rope_table) return flash_prefill_launch(d_q, d_k, d_v, d_out, batch, T_q, T_k, Hq, Hkv, causal, scale, nullptr, st);

@@ -328,12 +328,7 @@ static jsm_status dm_launch(const CUtensorMap& map, dim3 grid, cudaStream_t st, 
 }
 
 bool attn_decode_mma_usable(int G, int chunk, const void* pool) {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* e = getenv("JSM_DEC_MMA");
-        enabled = e ? atoi(e) : 1;
-    }
-    return enabled && (G == 2 || G == 4 || G == 8) && chunk % DM_PAGE == 0 && (reinterpret_cast<uintptr_t>(pool) & 15) == 0;
+    return (G == 2 || G == 4 || G == 8) && chunk % DM_PAGE == 0 && (reinterpret_cast<uintptr_t>(pool) & 15) == 0;
 }
 
 jsm_status attn_decode_mma_launch(const DecodeMmaArgs& a, cudaStream_t st) {

@@ -971,14 +971,9 @@ static cudaError_t launch_staged_kind(int kind, int pro, const StagedArgs& S, un
 // Rows staged through shared memory: f32 operands with contiguous, 16-byte aligned rows of 1024, 2048 or 4096 columns,
 // the programs x, x * imm + y and x + y, every kind but argmax.  Returns false when the call does not qualify.
 static bool try_rows_staged(const Lowered& Lw, const RowsArgs& A, cudaStream_t st, cudaError_t* err) {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* e = getenv("JSM_ROWS_STAGED");
-        enabled = e ? atoi(e) : 1;
-    }
     const EvalParams& P = Lw.P;
     const int C = Lw.C;
-    if (!enabled || !Lw.vec || A.kind == JSM_ROWS_ARGMAX) return false;
+    if (!Lw.vec || A.kind == JSM_ROWS_ARGMAX) return false;
     if (C != 1024 && C != 2048 && C != 4096) return false;
     if (P.pro != PRO_LEAF && P.pro != PRO_AXPB && P.pro != PRO_ADD) return false;
     const int nl = P.pro == PRO_LEAF ? 1 : 2;

@@ -374,8 +374,6 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     }
 }
 
-bool flash_available() { return true; }
-
 jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, void* out, int batch, int Tq, int Tk, int Hq, int Hkv,
                                 int causal, float scale, const float* rope, cudaStream_t st, long long q_rs, long long kv_rs,
                                 long long o_rs) {
@@ -399,23 +397,14 @@ jsm_status flash_prefill_launch(const void* q, const void* k, const void* v, voi
     P.out_rs = o_rs;
     P.err = tc_error_word();
     const size_t smem = (size_t)(2 + 2 * FA_KV_STAGES) * FA_TILE_BYTES + 1024;
-    static int poly = -1;
-    if (poly < 0) {
-        const char* e = getenv("JSM_FA_POLY");
-        poly = e ? atoi(e) : 1;
-        if (poly < 0 || poly > 2) poly = 1;
-    }
     static bool attr_done = false;
     if (!attr_done) {
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(flash_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_done = true;
     }
     dim3 grid((Tq + 2 * FA_BM - 1) / (2 * FA_BM), Hq, batch);
-    if (poly == 0) flash_prefill_kernel<0><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
-    else if (poly == 1) flash_prefill_kernel<1><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
-    else flash_prefill_kernel<2><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
+    // a quarter of the exponentials on the FMA pipe: the measured optimum (none: MUFU-bound, half: issue-bound)
+    flash_prefill_kernel<1><<<grid, FA_THREADS, smem, st>>>(mq, mk, mv, P);
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }

@@ -29,12 +29,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 // Context positions per CTA: small batches get short chunks so that the grid still fills the GPU
 // (chunks x kv heads x sequences CTAs); always a multiple of the 32 positions a CTA covers per step.
 inline int decode_chunk(int n_seqs, int Hq) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("JSM_DEC_CHUNK");
-        forced = e ? atoi(e) : 0;
-    }
-    if (forced >= 32 && forced % 32 == 0) return forced;
     const int work = n_seqs * Hq;
     return work >= 512 ? DEC_CHUNK_MAX : work >= 128 ? 256 : work >= 32 ? 128 : 64;
 }
@@ -355,11 +349,22 @@ extern "C" size_t jsm_attn_decode_scratch_bytes(int n_seqs, int Hq, int D, int m
     return (size_t)n_seqs * Hq * n_chunks * (D + 2) * sizeof(float);
 }
 
+// The chunk length shrinks with the number of sequences of a call (short chunks keep the grid full), so the bytes a
+// call needs are not monotone in n_seqs: a buffer that serves every call of 1..max_seqs sequences takes the maximum.
+extern "C" size_t jsm_attn_decode_scratch_bytes_max(int max_seqs, int Hq, int D, int max_context) {
+    size_t need = 0;
+    for (int n = 1; n <= max_seqs; ++n) {
+        const size_t b = jsm_attn_decode_scratch_bytes(n, Hq, D, max_context);
+        if (b > need) need = b;
+    }
+    return need;
+}
+
 static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
                                      const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
                                      const float* d_rope_table, int max_context, void* d_scratch, void* d_out, const void* d_k_new,
                                      const void* d_v_new, int64_t kv_new_stride, int* d_counters, bool fused, void* stream,
-                                     const char* who) {
+                                     const char* who, size_t scratch_capacity) {
     if (n_seqs == 0) return JSM_OK;
     if (!d_q || !d_pool || !d_block_table || !d_context_lens || !d_scratch || !d_out) JSM_FAIL(JSM_INVALID_ARG, "%s: null pointer", who);
     if (D != 128) JSM_FAIL(JSM_UNSUPPORTED, "%s: head_dim %d (128 only)", who, D);
@@ -370,6 +375,10 @@ static jsm_status attn_decode_launch(const void* d_q, int64_t q_row_stride, void
     const int G = Hq / Hkv;
     const int chunk = decode_chunk(n_seqs, Hq);
     const int n_chunks = (max_context + chunk - 1) / chunk;
+    const size_t need = (size_t)n_seqs * Hq * n_chunks * (D + 2) * sizeof(float);
+    if (need > scratch_capacity)
+        JSM_FAIL(JSM_INVALID_ARG, "%s: %d sequences x %d heads x context %d write %zu bytes of partials, the scratch buffer holds %zu", who,
+                 n_seqs, Hq, max_context, need, scratch_capacity);
     dim3 grid(n_chunks, Hkv, n_seqs);
     cudaStream_t st = as_stream(stream);
     const float sl2 = scale * LOG2E;
@@ -418,8 +427,21 @@ extern "C" jsm_status jsm_attn_decode(const void* d_q, int64_t q_row_stride, con
                                       const float* d_rope_table, int max_context, void* d_scratch, void* d_out, void* stream) {
     return attn_decode_launch(d_q, q_row_stride, const_cast<void*>(d_pool), d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D,
                               scale, d_rope_table, max_context, d_scratch, d_out, nullptr, nullptr, 0, nullptr, false, stream,
-                              "jsm_attn_decode");
+                              "jsm_attn_decode", SIZE_MAX);
 }
+
+namespace jsm {
+// the decoder runner's call: the capacity of its scratch buffer is checked against what this batch size writes
+jsm_status attn_decode_append_checked(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
+                                      int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
+                                      const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                      const float* d_rope_table, int max_context, void* d_scratch, size_t scratch_bytes,
+                                      int32_t* d_counters, void* d_out, void* stream) {
+    return attn_decode_launch(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D, scale,
+                              d_rope_table, max_context, d_scratch, d_out, d_k_new, d_v_new, kv_new_stride, d_counters, true, stream,
+                              "jsm_llama_decode_step", scratch_bytes);
+}
+}  // namespace jsm
 
 extern "C" jsm_status jsm_attn_decode_append(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
                                              int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
@@ -428,7 +450,7 @@ extern "C" jsm_status jsm_attn_decode_append(const void* d_q, int64_t q_row_stri
                                              void* d_out, void* stream) {
     return attn_decode_launch(d_q, q_row_stride, d_pool, d_block_table, max_pages, d_context_lens, n_seqs, Hq, Hkv, D, scale,
                               d_rope_table, max_context, d_scratch, d_out, d_k_new, d_v_new, kv_new_stride, d_counters, true, stream,
-                              "jsm_attn_decode_append");
+                              "jsm_attn_decode_append", SIZE_MAX);
 }
 
 // ---- decode attention that allocates nothing ---------------------------------------------------------

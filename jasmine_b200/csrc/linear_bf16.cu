@@ -569,6 +569,7 @@ jsm_status tc_check_error(cudaStream_t st, const char* who) {
     JSM_CUDA_CHECK(cudaStreamSynchronize(st));
     if (h != 0) {
         cudaMemsetAsync(w, 0, sizeof(int), st);
+        if (h == 32) JSM_FAIL(JSM_SHAPE, "%s: context overflow: a decode step met a sequence that already holds max_context tokens", who);
         JSM_FAIL(JSM_TIMEOUT, "%s: a bounded device-side wait ran out (code %d)", who, h);
     }
     return JSM_OK;

@@ -740,17 +740,7 @@ int linear_packed_grid(int N, int K, int paired, int T) {
 // the launch has enough tokens for the exchange to matter: those CTAs are launched as one thread-block cluster and fold
 // their partials through distributed shared memory
 int linear_packed_cluster(int N, int K, int paired, int T) {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* e = getenv("JSM_PK_CLUSTER");
-        enabled = (e && e[0] == '0') ? 0 : 1;
-    }
-    static int min_t = -1;
-    if (min_t < 0) {
-        const char* e = getenv("JSM_PK_CLUSTER_MIN_T");
-        min_t = e ? atoi(e) : 32;
-    }
-    if (!enabled || T < min_t) return 0;
+    if (T < 32) return 0;
     int nt, kbt;
     pk_dims(N, K, paired, &nt, &kbt);
     const int G = linear_packed_grid(N, K, paired, T);
@@ -790,12 +780,7 @@ template <int BN, bool CL>
 static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
-    static int budget_kb = -1;
-    if (budget_kb < 0) {
-        const char* e = getenv("JSM_PK_BUDGET_KB");
-        budget_kb = e ? atoi(e) : 0;
-    }
-    const int budget = (budget_kb > 0 ? budget_kb : (BN <= 64 ? 150 : 200)) * 1024;
+    const int budget = (BN <= 64 ? 150 : 200) * 1024;
     int stages = budget / STAGE_BYTES;
     if (stages > PK_MAX_STAGES) stages = PK_MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -858,14 +843,7 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     PkParams P;
     P.T = a.T; P.N = a.N; P.K = a.K;
     pk_dims(a.N, a.K, paired, &P.n_tiles, &P.kbt);
-    {
-        static int local_epi = -1;
-        if (local_epi < 0) {
-            const char* e = getenv("JSM_PK_LOCAL_EPI");
-            local_epi = e ? atoi(e) : 1;
-        }
-        P.local_epi = local_epi;
-    }
+    P.local_epi = 1;
     P.paired = paired; P.epilogue = a.epilogue; P.out_f32 = a.out_f32 ? 1 : 0;
     P.bias = a.bias; P.R = (const __nv_bfloat16*)a.R; P.Y = a.Y; P.Wp = (const uint8_t*)a.Wp;
     const int grid = linear_packed_grid(a.N, a.K, paired, a.T);
@@ -873,7 +851,8 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     const long long U = (long long)P.n_tiles * P.kbt;
     const bool shared_tiles = (U % grid) != 0 || ((U / grid) % P.kbt) != 0;
     if (shared_tiles) {
-        if (!a.ws || !a.counters) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace and counters are required");
+        if (!a.ws || !a.counters)
+            JSM_FAIL(JSM_INVALID_ARG, "linear_packed: no workspace on this device (jsm_linear_pack / jsm_linear_packed_reserve size it at set-up time)");
         if ((size_t)P.n_tiles * P.max_slots * (size_t)a.T * 128 > a.ws_floats)
             JSM_FAIL(JSM_INVALID_ARG, "linear_packed: workspace of %zu floats, %zu needed", a.ws_floats,
                      linear_packed_ws_floats(a.T, a.N, a.K, paired));
@@ -900,12 +879,9 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     }
     const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
     // the cluster path lives in instantiations of its own: launches without a cluster run a kernel that carries none of it
-    static int one_kernel = -1;
-    if (one_kernel < 0) {
-        const char* e = getenv("JSM_PK_ONE_KERNEL");
-        one_kernel = e ? atoi(e) : 1;
-    }
-    const bool with_cl = cluster > 1 || (one_kernel && a.T >= 32);
+    // (from 32 tokens on every launch runs the cluster-capable image, with cluster size 1 where no cluster forms: one
+    // kernel image per token block keeps the once-per-launch tail code warm in the instruction cache)
+    const bool with_cl = cluster > 1 || a.T >= 32;
 #define PK_GO(BN_)                                                                                  \
     return with_cl ? launch_packed<BN_, true>(mx, mx2, P, grid, cluster, a.chained, st)            \
                    : launch_packed<BN_, false>(mx, mx2, P, grid, cluster, a.chained, st)
@@ -973,8 +949,43 @@ extern "C" size_t jsm_linear_packed_bytes(int N, int K, int paired) {
     return linear_packed_bytes(N, K, paired ? 1 : 0);
 }
 
+// Grows the workspace of the current device so that any launch of this shape (up to 256 tokens per launch) finds room.
+// Set-up time only: synchronises the device when it has to reallocate.
+extern "C" jsm_status jsm_linear_packed_reserve(int N, int K, int paired) {
+    if (N <= 0 || K <= 0) JSM_FAIL(JSM_INVALID_ARG, "jsm_linear_packed_reserve: N %d, K %d", N, K);
+    int dev = -1;
+    JSM_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_packed_reserve: device index %d", dev);
+    paired = paired ? 1 : 0;
+    std::lock_guard<std::mutex> lock(g_pk_mu);
+    PkWorkspace& w = g_pk_ws[dev];
+    size_t need = 0;
+    for (int T : {16, 32, 64, 128, 256}) need = std::max(need, linear_packed_ws_floats(T, N, K, paired));
+    int nt, kbt;
+    pk_dims(N, K, paired, &nt, &kbt);
+    if (need > w.ws_floats) {
+        JSM_CUDA_CHECK(cudaDeviceSynchronize());
+        if (w.ws) cudaFree(w.ws);
+        w.ws = nullptr; w.ws_floats = 0;
+        JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.ws), need * sizeof(float)));
+        w.ws_floats = need;
+    }
+    if (nt > w.n_counters) {
+        JSM_CUDA_CHECK(cudaDeviceSynchronize());
+        if (w.counters) cudaFree(w.counters);
+        w.counters = nullptr; w.n_counters = 0;
+        const int n = nt < 1024 ? 1024 : nt;
+        JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.counters), n * sizeof(int)));
+        JSM_CUDA_CHECK(cudaMemset(w.counters, 0, n * sizeof(int)));
+        w.n_counters = n;
+    }
+    return JSM_OK;
+}
+
 extern "C" jsm_status jsm_linear_pack(const void* d_W, int N, int K, int paired, void* d_packed, void* stream) {
-    return linear_pack_launch(d_W, N, K, paired ? 1 : 0, d_packed, false, as_stream(stream));
+    jsm_status s = linear_pack_launch(d_W, N, K, paired ? 1 : 0, d_packed, false, as_stream(stream));
+    if (s != JSM_OK) return s;
+    return jsm_linear_packed_reserve(N, K, paired);
 }
 
 extern "C" jsm_status jsm_linear_unpack(const void* d_packed, int N, int K, int paired, void* d_W, void* stream) {
@@ -994,29 +1005,10 @@ extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_pack
     a.X = d_X; a.Wp = d_packed; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.out_f32 = out_dtype == JSM_F32;
     a.N = N; a.K = K; a.x_row_stride = 0; a.chained = false;
     {
-        // grow-only workspace shared by the calls on this device (they are ordered by their streams' users; two
-        // calls that overlap on the GPU would race on it, like any scratch buffer)
+        // the workspace of this device, sized at set-up time (jsm_linear_pack / jsm_linear_packed_reserve); the launch
+        // checks its capacity and fails rather than allocate
         std::lock_guard<std::mutex> lock(g_pk_mu);
-        PkWorkspace& w = g_pk_ws[dev];
-        const size_t need = linear_packed_ws_floats(T < 256 ? T : 256, N, K, paired);
-        int nt, kbt;
-        pk_dims(N, K, paired, &nt, &kbt);
-        if (need > w.ws_floats) {
-            JSM_CUDA_CHECK(cudaDeviceSynchronize());
-            if (w.ws) cudaFree(w.ws);
-            w.ws = nullptr; w.ws_floats = 0;
-            JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.ws), need * sizeof(float)));
-            w.ws_floats = need;
-        }
-        if (nt > w.n_counters) {
-            JSM_CUDA_CHECK(cudaDeviceSynchronize());
-            if (w.counters) cudaFree(w.counters);
-            w.counters = nullptr; w.n_counters = 0;
-            const int n = nt < 1024 ? 1024 : nt;
-            JSM_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&w.counters), n * sizeof(int)));
-            JSM_CUDA_CHECK(cudaMemset(w.counters, 0, n * sizeof(int)));
-            w.n_counters = n;
-        }
+        const PkWorkspace& w = g_pk_ws[dev];
         a.ws = w.ws; a.ws_floats = w.ws_floats; a.counters = w.counters; a.n_counters = w.n_counters;
     }
     // more than 256 tokens: token chunks, each streaming the weights once

@@ -24,6 +24,13 @@ namespace jsm {
 
 size_t tp_region_bytes(int max_tokens, int d);
 size_t tp_buffer_offset(int which, int max_tokens, int d);
+jsm_status attn_decode_append_checked(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
+                                      int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
+                                      const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
+                                      const float* d_rope_table, int max_context, void* d_scratch, size_t scratch_bytes,
+                                      int32_t* d_counters, void* d_out, void* stream);
+int* tc_error_word();
+constexpr int TC_CONTEXT_OVERFLOW = 32;  // error word code: a decode step met a sequence that already holds max_context tokens
 jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, const int* pass, int site,
                                         int n_sites, void* h, void* xn, float eps, int T, int d, cudaStream_t st);
 
@@ -59,6 +66,7 @@ struct jsm_model {
     float* partial = nullptr;
     float* logits = nullptr;
     float* dec_scratch = nullptr;
+    size_t dec_scratch_bytes = 0;
     float *ssq0 = nullptr, *ssq_a = nullptr, *ssq_b = nullptr;  // row statistics: after the embedding, after wo, after down
     size_t ws_floats = 0;        // capacity of `partial`: fp32 partials of the tiles that several CTAs share
     int* counters = nullptr;     // one arrival counter per tile (self-resetting)
@@ -146,11 +154,22 @@ __global__ void iota_kernel(int32_t* pos, int32_t* seq_ids, int T, int seq, int 
 __global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = value; }
 // decode bookkeeping on the device so that a captured step can be replayed: the new token of
 // sequence b goes to position ctx[b], then the context grows by one
-__global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch, int32_t* pass) {
+// A sequence that already holds max_context tokens does not grow: its new token overwrites the last position (every
+// later access stays inside the sequence's pages and the rope table) and the error word records the overflow.
+__global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch, int32_t* pass, int max_context, int* err) {
     chain_trigger();
     chain_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < batch) { pos[b] = ctx[b]; seq_ids[b] = b; ctx[b] = ctx[b] + 1; }
+    if (b < batch) {
+        int c = ctx[b];
+        if (c >= max_context) {
+            c = max_context - 1;
+            if (err) atomicCAS(err, 0, TC_CONTEXT_OVERFLOW);
+        }
+        pos[b] = c;
+        seq_ids[b] = b;
+        ctx[b] = c + 1;
+    }
     if (b == 0 && pass) *pass = *pass + 1;
 }
 
@@ -392,15 +411,9 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
         const __nv_bfloat16* vv = kk + (long long)m->Hkv_l * D;
         if (decode) {
             // the new token: one launch rotates K into the cache, stores V, rotates q and attends over the context
-            static const bool unfused = getenv("JSM_ATTN_UNFUSED") != nullptr;
-            if (unfused) {
-                s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, m->rope, st);
-                if (s != JSM_OK) return s;
-                s = jsm_attn_decode(m->qkv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch, m->Hq_l, m->Hkv_l, D, scale,
-                                    m->rope, c.max_context, m->dec_scratch, m->attn, st);
-            } else
-            s = jsm_attn_decode_append(m->qkv, m->qkv_dim, kk, vv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch,
-                                       m->Hq_l, m->Hkv_l, D, scale, m->rope, c.max_context, m->dec_scratch, m->attn_counters, m->attn, st);
+            s = attn_decode_append_checked(m->qkv, m->qkv_dim, kk, vv, m->qkv_dim, L.pool, m->block_table, m->pages_per_seq, m->ctx, batch,
+                                           m->Hq_l, m->Hkv_l, D, scale, m->rope, c.max_context, m->dec_scratch, m->dec_scratch_bytes,
+                                           m->attn_counters, m->attn, st);
         } else {
             // prompt of one sequence starting at position 0: rotate q and k in place (the first Hq + Hkv heads of every
             // fused row), cache K and V, then causal attention over the fresh q, k, v
@@ -408,7 +421,7 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
             if (s != JSM_OK) return s;
             s = jsm_kv_append(L.pool, m->block_table, m->pages_per_seq, kk, vv, m->qkv_dim, m->seq_ids, m->pos, T, m->Hkv_l, D, nullptr, st);
             if (s != JSM_OK) return s;
-            if (flash_available() && T >= 128)
+            if (T >= 128)
                 s = flash_prefill_launch(m->qkv, kk, vv, m->attn, 1, T, T, m->Hq_l, m->Hkv_l, 1, scale, nullptr, st, m->qkv_dim,
                                          m->qkv_dim, (long long)m->Hq_l * D);
             else
@@ -547,7 +560,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
         f.gain = m->gf;
         fill_packed(m->lm_head, c.vocab, d, 0, f, st);
     }
-    wbytes += 2ull * (uint64_t)c.vocab * d + 4ull * d;
+    wbytes += 2ull * (uint64_t)c.vocab * d + 4ull * d;  // lm_head (streamed every step) and the final gain
     m->weight_bytes = wbytes;
     JSM_TRY(dev_alloc(m, &m->rope, (size_t)c.max_context * (D / 2) * 4));
     JSM_TRY(jsm_rope_table(m->rope, 1, D, c.rope_theta, c.max_context, st));
@@ -598,7 +611,9 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
-    JSM_TRY(dev_alloc(m, &m->dec_scratch, jsm_attn_decode_scratch_bytes(c.max_batch, m->Hq_l, D, c.max_context) / sizeof(float) + 4));
+    // the chunk length of the decode attention depends on the batch of the step: room for the largest need over 1..max_batch
+    m->dec_scratch_bytes = jsm_attn_decode_scratch_bytes_max(c.max_batch, m->Hq_l, D, c.max_context);
+    JSM_TRY(dev_alloc(m, &m->dec_scratch, m->dec_scratch_bytes / sizeof(float) + 4));
     cudaError_t e = cudaMemset(m->ctx, 0, sizeof(int32_t) * c.max_batch);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: initialisation failed: %s", cudaGetErrorString(e)); }
@@ -842,7 +857,8 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step: null argument");
     if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step: batch %d (1..%d)", batch, m->c.max_batch);
     cudaStream_t st = as_stream(stream);
-    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch, m->tp_state));
+    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch, m->tp_state,
+                                  m->c.max_context, tc_error_word()));
     JSM_LAUNCH_CHECK();
     jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
     if (s != JSM_OK) return s;
@@ -864,8 +880,9 @@ jsm_status jsm_llama_reset(jsm_model* m) {
 
 jsm_status jsm_llama_step_bytes(jsm_model* m, uint64_t* weight_bytes, uint64_t* kv_bytes_per_token) {
     if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_step_bytes: null model");
-    // the embedding table is gathered, not streamed: one row per token
-    if (weight_bytes) *weight_bytes = m->weight_bytes - 2ull * (uint64_t)m->c.vocab * m->c.d_model;
+    // every projection including lm_head is streamed once per step; the embedding table is gathered (one row per token)
+    // and is not part of the count
+    if (weight_bytes) *weight_bytes = m->weight_bytes;
     if (kv_bytes_per_token) *kv_bytes_per_token = (uint64_t)m->c.n_layers * 2ull * m->Hkv_l * m->c.head_dim * 2ull;
     return JSM_OK;
 }

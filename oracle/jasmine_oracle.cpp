@@ -201,7 +201,37 @@ API int orc_dot(const float* A, int M, int K, const float* B, int K2, int N, flo
     return 0;
 }
 // a9: weight_net_t::forward (mat_net_t.hpp:38-43), token-major: Y[t,n] = (sum_k W[n,k]*X[t,k]) + b[n]
+// With several tokens the same sums are formed for a block of tokens at a time: X is transposed once so that the tokens
+// of one k are contiguous, and every accumulator still receives its products in ascending k with separately rounded
+// multiply and add (no contraction: -ffp-contract=off), so the results are bit-identical to the scalar loop - the
+// compiler may merely keep several tokens in one vector register.
+__attribute__((target_clones("avx2", "default")))
+static void linear_rows_block(const float* XT, const float* W, const float* b, int T, int Tp, int N, int K, float* Y, int n0, int n1) {
+    std::vector<float> acc(Tp);
+    for (int n = n0; n < n1; ++n) {
+        const float* w = W + (long)n * K;
+        float* a = acc.data();
+        for (int t = 0; t < Tp; ++t) a[t] = 0.0f;
+        for (int k = 0; k < K; ++k) {
+            const float wk = w[k];
+            const float* x = XT + (long)k * Tp;
+#pragma omp simd
+            for (int t = 0; t < Tp; ++t) { float p = wk * x[t]; a[t] += p; }
+        }
+        for (int t = 0; t < T; ++t) Y[(long)t * N + n] = b ? a[t] + b[n] : a[t];
+    }
+}
 static void linear(const float* X, const float* W, const float* b, int T, int N, int K, float* Y) {
+    if (T >= 4) {
+        const int Tp = (T + 7) / 8 * 8;
+        std::vector<float> XT((long)K * Tp, 0.0f);
+        for (int t = 0; t < T; ++t)
+            for (int k = 0; k < K; ++k) XT[(long)k * Tp + t] = X[(long)t * K + k];
+        const int NB = 16;
+#pragma omp parallel for schedule(dynamic)
+        for (int n0 = 0; n0 < N; n0 += NB) linear_rows_block(XT.data(), W, b, T, Tp, N, K, Y, n0, n0 + NB < N ? n0 + NB : N);
+        return;
+    }
 #pragma omp parallel for
     for (int t = 0; t < T; ++t)
         for (int n = 0; n < N; ++n) {
@@ -428,7 +458,8 @@ API int orc_gpt(const float* weights, int L, int d, int H, int ffn, int vocab, i
 // rounded to bf16 where the device stores bf16 (after every projection, norm and activation product).
 struct llama_cfg { int L, d, Hq, Hkv, D, ffn, vocab; float eps, theta; };
 API int orc_llama_forward(const llama_cfg* c, const float* emb, const float* const* layer_w /* per layer: g1,wq,wk,wv,wo,g2,wgate,wup,wdown */,
-                          const float* gf, const float* wlm, const int* ids, int T, int round_act, float* logits /*[T,vocab]*/) {
+                          const float* gf, const float* wlm, const int* ids, int T, int round_act, float* logits /*[T,vocab]*/,
+                          int last_rows /* > 0: only the logits of the last `last_rows` tokens are computed (rows T-last_rows..T-1 of `logits`) */) {
     const int d = c->d, D = c->D, Hq = c->Hq, Hkv = c->Hkv, ffn = c->ffn;
     auto R = [&](std::vector<float>& v) { if (round_act) for (auto& x : v) x = bf16_round(x); };
     std::vector<float> h((long)T * d), a((long)T * d), q((long)T * Hq * D), k((long)T * Hkv * D), v((long)T * Hkv * D),
@@ -458,7 +489,8 @@ API int orc_llama_forward(const llama_cfg* c, const float* emb, const float* con
         R(h);
     }
     orc_rms_norm_rows(h.data(), T, d, gf, c->eps, a.data()); R(a);
-    linear(a.data(), wlm, nullptr, T, c->vocab, d, logits);
+    const int r0 = (last_rows > 0 && last_rows < T) ? T - last_rows : 0;
+    linear(a.data() + (long)r0 * d, wlm, nullptr, T - r0, c->vocab, d, logits + (long)r0 * c->vocab);
     return 0;
 }
 

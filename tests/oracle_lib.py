@@ -277,8 +277,10 @@ class LlamaCfg(C.Structure):
                 ("vocab", C.c_int), ("eps", C.c_float), ("theta", C.c_float)]
 
 
-def llama_forward(cfg: dict, emb, layers, gf, wlm, ids, round_act=True):
-    """layers: list of 9-tuples (g1, wq, wk, wv, wo, g2, wgate, wup, wdown) of float32 arrays."""
+def llama_forward(cfg: dict, emb, layers, gf, wlm, ids, round_act=True, last_rows=0):
+    """layers: list of 9-tuples (g1, wq, wk, wv, wo, g2, wgate, wup, wdown) of float32 arrays.
+    last_rows > 0: only the logits of the last `last_rows` tokens are computed (the other rows of the result are
+    meaningless) - the lm_head over every prompt position is most of the work at a 32000-word vocabulary."""
     c = LlamaCfg(cfg["L"], cfg["d"], cfg["Hq"], cfg["Hkv"], cfg["D"], cfg["ffn"], cfg["vocab"], cfg["eps"], cfg["theta"])
     keep = [f32(a) for lw in layers for a in lw]
     ptrs = (_fp * len(keep))(*[P(a) for a in keep])
@@ -286,5 +288,5 @@ def llama_forward(cfg: dict, emb, layers, gf, wlm, ids, round_act=True):
     T = ids.shape[0]
     logits = np.empty((T, cfg["vocab"]), np.float32)
     emb, gf, wlm = f32(emb), f32(gf), f32(wlm)
-    assert port().orc_llama_forward(C.byref(c), P(emb), ptrs, P(gf), P(wlm), PI(ids), T, int(round_act), P(logits)) == 0
+    assert port().orc_llama_forward(C.byref(c), P(emb), ptrs, P(gf), P(wlm), PI(ids), T, int(round_act), P(logits), int(last_rows)) == 0
     return logits

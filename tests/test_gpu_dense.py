@@ -131,6 +131,34 @@ def test_linear_packed(T, N, K):
     assert_close(host(Yb), want, BF16_RTOL, "bf16 output")
 
 
+@pytest.mark.parametrize("T,N,K", [(8, 11008, 4096), (64, 4096, 11008), (8, 12288, 4096)])
+def test_linear_packed_against_the_oracle(T, N, K):
+    """The projection shapes of the 7B decoder against the CPU oracle's weight_net_t::forward restatement (k-ascending
+    fp32 sums of the same bf16 inputs), not only against torch."""
+    X, W = make_xw(T, N, K, 170 + T)
+    Y = torch.empty(T, N, device="cuda", dtype=torch.float32)
+    jb.linear_bf16_packed(X, jb.linear_pack(W, N), Y)
+    jb.check_device_errors()
+    want = port.linear(host(X), host(W), np.zeros(N, np.float32))
+    assert_close(host(Y), want, 2e-3, f"packed vs oracle T={T} N={N} K={K}")
+
+
+def test_linear_packed_needs_a_reserved_workspace():
+    """The compute call never allocates: a packed image that did not come from jsm_linear_pack on this device (loaded
+    from a file, say) needs jsm_linear_packed_reserve once, at set-up time; without it the call is refused."""
+    T, N, K = 8, 1100 * 128, 64                  # more tiles (arrival counters) than any shape another test packs
+    Wp = torch.zeros(jb.lib().jsm_linear_packed_bytes(N, K, 0), dtype=torch.uint8, device="cuda")
+    X = torch.zeros(T, K, device="cuda", dtype=torch.bfloat16)
+    Y = torch.empty(T, N, device="cuda", dtype=torch.float32)
+    with pytest.raises(jb.JsmError) as e:
+        jb.linear_bf16_packed(X, Wp, Y)
+    assert e.value.status == jb.INVALID_ARG
+    jb.check(jb.lib().jsm_linear_packed_reserve(N, K, 0))
+    jb.linear_bf16_packed(X, Wp, Y)
+    jb.check_device_errors()
+    assert float(Y.abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("T,N,K", [(1, 256, 512), (8, 11008, 4096), (32, 1376, 512), (64, 704, 1024), (130, 320, 256)])
 def test_linear_packed_epilogues(T, N, K):
     X, W = make_xw(T, N, K, 160 + T, rows=2 * N)

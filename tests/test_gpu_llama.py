@@ -156,3 +156,101 @@ def test_checkpoint_round_trip_and_weight_injection(tmp_path):
         want = ol.llama_forward(cfg, wide(emb), layers, gf.cpu().numpy(), wide(wlm), prompts[s])[-1]
         assert_close(host(last), want, BF16_RTOL, f"injected weights, prefill logits of sequence {s}")
     a.close(); b.close()
+
+
+def test_full_width_layers_match_oracle():
+    """Configuration 5 at full width: two decoder layers of the 7B shape (d 4096, 32 x 128 heads, SwiGLU 11008, vocabulary
+    32000), batch 8, prompts of 136 tokens (the prefill takes the tensor-core flash kernel), then three decode steps
+    against the paged cache.  Logits against the oracle's full-prefix recompute within the bf16 bar; the greedy token
+    must be the oracle's wherever its top-2 margin is clear."""
+    cfg = dict(L=2, d=4096, Hq=32, Hkv=32, D=128, ffn=11008, vocab=32000, eps=1e-5, theta=10000.0)
+    batch, T, n_gen = 8, 136, 3
+    m = Llama(cfg["L"], cfg["d"], cfg["Hq"], cfg["Hkv"], cfg["ffn"], cfg["vocab"], max_batch=batch, max_context=192, seed=4)
+    emb, layers, gf, wlm = oracle_weights(m, cfg)
+    prompts = [cases.ints(T, 4, 700 + b, 0, cfg["vocab"]) for b in range(batch)]
+    nxt = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    last_logits = torch.empty(cfg["vocab"], device="cuda")
+    seqs = [list(p) for p in prompts]
+
+    def check(got, seq_tokens, what, token=None):
+        want = ol.llama_forward(cfg, emb, layers, gf, wlm, np.array(seq_tokens, np.int32), last_rows=1)[-1]
+        assert_close(got, want, BF16_RTOL, what)
+        top = np.sort(want)[-2:]
+        if token is not None and top[1] - top[0] > 2 * BF16_RTOL * float(np.abs(want).max()):
+            assert token == int(np.argmax(want)), f"{what}: greedy token differs"
+
+    for b in range(batch):
+        m.prefill(torch.from_numpy(prompts[b]).cuda(), b, nxt, last_logits)
+        if b in (0, 3, 7):
+            check(host(last_logits), seqs[b], f"prefill logits of sequence {b}", int(nxt[b]))
+    jb.check_device_errors()
+    logits = torch.empty(batch, cfg["vocab"], device="cuda")
+    for step in range(n_gen):
+        tokens = nxt.clone()
+        for b in range(batch):
+            seqs[b].append(int(tokens[b]))
+        m.decode_step(tokens, nxt, logits)
+        got = host(logits)
+        for b in (range(batch) if step == n_gen - 1 else (0,)):
+            check(got[b], seqs[b], f"decode step {step} sequence {b}", int(nxt[b]))
+    jb.check_device_errors()
+    m.close()
+
+
+def test_decode_with_fewer_sequences_than_max_batch():
+    """The split of the context into chunks depends on the batch of the step (fewer sequences: shorter chunks, more
+    partials per head), so a step with fewer sequences than max_batch can need MORE scratch than a full one: 32 heads,
+    max_batch 4, a step of 3 sequences over a context beyond 128 positions.  Checked against the oracle."""
+    cfg = dict(L=1, d=256, Hq=32, Hkv=32, D=128, ffn=512, vocab=1024, eps=1e-5, theta=10000.0)
+    assert jb.lib().jsm_attn_decode_scratch_bytes(3, 32, 128, 320) > jb.lib().jsm_attn_decode_scratch_bytes(4, 32, 128, 320)
+    assert jb.lib().jsm_attn_decode_scratch_bytes_max(4, 32, 128, 320) >= jb.lib().jsm_attn_decode_scratch_bytes(3, 32, 128, 320)
+    m = Llama(cfg["L"], cfg["d"], cfg["Hq"], cfg["Hkv"], cfg["ffn"], cfg["vocab"], max_batch=4, max_context=320, seed=4)
+    emb, layers, gf, wlm = oracle_weights(m, cfg)
+    batch, T = 3, 200
+    prompts = [cases.ints(T, 4, 800 + b, 0, cfg["vocab"]) for b in range(batch)]
+    nxt = torch.zeros(4, dtype=torch.int32, device="cuda")
+    seqs = [list(p) for p in prompts]
+    for b in range(batch):
+        m.prefill(torch.from_numpy(prompts[b]).cuda(), b, nxt)
+    logits = torch.empty(batch, cfg["vocab"], device="cuda")
+    for step in range(2):
+        tokens = nxt[:batch].clone()
+        for b in range(batch):
+            seqs[b].append(int(tokens[b]))
+        m.decode_step(tokens, nxt, logits)
+        got = host(logits)
+        for b in range(batch):
+            want = ol.llama_forward(cfg, emb, layers, gf, wlm, np.array(seqs[b], np.int32), last_rows=1)[-1]
+            assert_close(got[b], want, BF16_RTOL, f"step {step}, sequence {b} of 3 (max_batch 4)")
+    jb.check_device_errors()
+    m.close()
+
+
+def test_decode_past_max_context_is_reported_not_faulted():
+    """A sequence that already fills max_context cannot grow: the step stays inside the sequence's pages and the rope
+    table, and the host reads JSM_SHAPE at the next error check; the neighbouring sequence's cache is left alone."""
+    cfg = dict(L=1, d=256, Hq=2, Hkv=2, D=128, ffn=512, vocab=1024, eps=1e-5, theta=10000.0)
+    m = Llama(cfg["L"], cfg["d"], 2, 2, cfg["ffn"], cfg["vocab"], max_batch=2, max_context=64, seed=4)
+    emb, layers, gf, wlm = oracle_weights(m, cfg)
+    p0, p1 = cases.ints(62, 4, 810, 0, 1024), cases.ints(20, 4, 811, 0, 1024)
+    nxt = torch.zeros(2, dtype=torch.int32, device="cuda")
+    m.prefill(torch.from_numpy(p0).cuda(), 0, nxt)
+    m.prefill(torch.from_numpy(p1).cuda(), 1, nxt)
+    logits = torch.empty(2, 1024, device="cuda")
+    s1 = list(p1)
+    for step in range(4):   # sequence 0 reaches 64 cached tokens after two steps; steps 2 and 3 overflow it
+        tokens = nxt.clone()
+        s1.append(int(tokens[1]))
+        m.decode_step(tokens, nxt, logits)
+        if step < 2:
+            jb.check_device_errors()
+        else:
+            with pytest.raises(jb.JsmError) as e:
+                jb.check_device_errors()
+            assert e.value.status == jb.SHAPE
+        # the sequence that still has room is unaffected by its neighbour's overflow
+        want = ol.llama_forward(cfg, emb, layers, gf, wlm, np.array(s1, np.int32), last_rows=1)[-1]
+        assert_close(host(logits)[1], want, BF16_RTOL, f"sequence 1 at step {step}")
+    jb.check_device_errors()
+    assert int(torch.ones(4, device="cuda").sum()) == 4
+    m.close()

@@ -152,7 +152,8 @@ def run_reference_arm(args):
     dt = (time.perf_counter() - t0) / args.steps
     macs = cores * rows * d
     tok_s = 1.0 / (dt * per_token_macs(PROMPT + GEN // 2) / macs)
-    sample = (f"per step: {cores} concurrent weight_net_t::forward calls ({rows}x{d} rows each, 1 token) through the "
+    sample = (f"projection-only sample (no attention, no norms, no per-token prefix recompute); per step: {cores} concurrent "
+              f"weight_net_t::forward calls ({rows}x{d} rows each, 1 token) through the "
               f"{'jasmine headers (oracle/_ref)' if kind == 'reference' else 'CPU oracle port'}; tok/s extrapolated by "
               f"multiply-accumulate count to one token of the 7B model at context {PROMPT + GEN // 2}")
     line = {"impl": "reference", "metric": "llama7b_decode_tokens_per_s", "value": tok_s, "unit": "tok/s",
@@ -172,7 +173,9 @@ def workload_config(args, n):
 
 
 # ---- kernel-level workloads: configurations 2, 3 and 4 of the baseline ------------------------------------
-def run_kernel_workload(args):
+def run_kernel_workload(args, collect=False):
+    """One JSON line per kernel; with collect=True the records are returned instead of printed."""
+    records = []
     import torch
     import jasmine_b200 as jb
     torch.cuda.set_device(0)
@@ -206,10 +209,14 @@ def run_kernel_workload(args):
 
     def emit(name, ms, bound, work, peak, unit, config):
         ach = work / (ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
-        print(json.dumps({"metric": name, "value": ach, "unit": unit, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+        rec = ({"metric": name, "value": ach, "unit": unit, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
                           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic", "config": config,
                           "roofline": {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-                                       "traffic": None, "peak_source": f"{peak_kind}"}}), flush=True)
+                                       "traffic": None, "peak_source": f"{peak_kind}"}})
+        if collect:
+            records.append(rec)
+        else:
+            print(json.dumps(rec), flush=True)
 
     L0, L1 = (jb.OP_LEAF, 0), (jb.OP_LEAF, 1)
     if args.workload == "expr":
@@ -295,6 +302,7 @@ def run_kernel_workload(args):
         kv_bytes = sum(lens) * Hkv * D * 2 * 2
         cfg = {"workload": "kv_decode_b64_q32_kv8_d128_ctx512-8192", "sum_context": sum(lens), "l2": f"{kv_bytes / 2**20:.0f} MiB of K/V > L2"}
         emit("kv_decode_attention_GBps", timed(lambda _: jb.attn_decode(q, pool, bt, ctx, Hq, Hkv, D, max_ctx, scratch=scratch, out=out)), "hbm", kv_bytes, hbm, "GB/s", cfg)
+    return records
 
 
 def run_timeline(args):
@@ -359,6 +367,67 @@ def run_timeline(args):
 
 
 # ---- the GPU arm --------------------------------------------------------------------------------------
+def tp_parity_check(world, rank, local, dist):
+    """TP-N == TP-1 on the GPUs of this run, before anything is timed: a full-width model of a few layers is built as
+    the live tensor-parallel group (exchange over peer memory, the product path) and, on rank 0, once more as a single
+    rank; both prefill the same prompts (128 tokens: the flash kernel) and run decode steps against the paged cache.
+    Returns (on rank 0) the largest logit difference relative to the largest logit, and whether the greedy tokens agree
+    wherever the one-rank model's top-2 margin is clear."""
+    import torch
+    import jasmine_b200 as jb
+    from jasmine_b200.model import Llama
+    L, B, T, steps = 2, 4, 128, 2
+    c = LLAMA7B
+
+    def run(tp_rank, tp_size, connect):
+        m = Llama(L, c["d_model"], c["n_heads"], c["n_kv_heads"], c["d_ffn"], c["vocab"], max_batch=B, max_context=T + 16,
+                  seed=SEED, tp_rank=tp_rank, tp_size=tp_size)
+        if connect:
+            m.connect_peers(dist)
+        nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+        pre = torch.empty(B, c["vocab"], device="cuda")
+        for b in range(B):
+            ids = torch.empty(T, dtype=torch.int32, device="cuda")
+            jb.fill(ids, SEED, 6000 + b, 2, 0, c["vocab"])
+            m.prefill(ids, b, nxt, pre[b])
+        out = [pre.clone()]
+        lg = torch.empty(B, c["vocab"], device="cuda")
+        toks = [nxt.clone()]
+        for _ in range(steps):
+            ids = nxt.clone()
+            m.decode_step(ids, nxt, lg)
+            out.append(lg.clone())
+            toks.append(nxt.clone())
+        jb.check_device_errors()
+        torch.cuda.synchronize()
+        if connect:
+            dist.barrier()
+        m.close()
+        return out, toks
+
+    out_n, tok_n = run(rank, world, True)
+    if rank != 0:
+        return None
+    out_1, tok_1 = run(0, 1, False)
+    worst, clear_equal, n_clear = 0.0, True, 0
+    prefix_same = True
+    for i, (a, b) in enumerate(zip(out_n, out_1)):
+        if not prefix_same:
+            break  # the two runs decode different prefixes from here on: nothing to compare
+        scale = float(b.abs().max())
+        worst = max(worst, float((a - b).abs().max()) / scale)
+        top2 = torch.topk(b, 2, dim=1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 2 * 2e-2 * scale
+        n_clear += int(clear.sum())
+        if bool((tok_n[i][clear] != tok_1[i][clear]).any()):
+            clear_equal = False
+        prefix_same = bool((tok_n[i] == tok_1[i]).all())
+    return {"max_rel_logit_diff": worst, "top1_equal_where_margin_clear": clear_equal, "rows_with_clear_margin": n_clear,
+            "layers": L, "batch": B, "prompt_len": T, "decode_steps": steps, "tolerance": 2e-2,
+            "what": f"logits of a {L}-layer full-width model (d 4096, 32x128 heads, ffn 11008, vocab 32000): the live tp{world} "
+                    "group over peer memory against a single rank on rank 0's GPU; prefill + decode steps"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -368,6 +437,7 @@ def main():
     ap.add_argument("--impl", default="jasmine_b200")
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers (the result is then not a bench value)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: skip the batch-1/64 legs, the kernel-level legs and the tp parity check")
     ap.add_argument("--workload", default="decode", choices=["decode", "expr", "flash", "kvdecode", "gateup", "timeline"],
                     help="decode = the headline; expr / flash / kvdecode = configurations 2 / 3 / 4 of the baseline "
                          "(kernel-level lines, one JSON line per kernel)")
@@ -400,10 +470,35 @@ def main():
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     B, K, W = args.batch, args.steps, args.warmup
-    max_ctx = PROMPT + W + 2 * K + 8
+    extras = not args.no_extras and args.layers == 32 and args.profile_steps == 0
+    use_nccl = os.environ.get("JSM_TP_NCCL", "0") == "1"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    parity = None
+    if world > 1 and extras and not use_nccl:
+        parity = tp_parity_check(world, rank, local, dist)
+        barrier()
+
+    # One model serves every leg: the headline batch, and (extras) batch 1 and batch 64 on the same weights and cache.
+    reps = 5 if K < 64 else 1                       # short runs are repeated and the median is reported
+    other_batches = [b for b in (1, 64) if b != B] if extras else []
+    Ke, Kb = min(K, 64), 32
+    max_batch = max([B] + other_batches)
+    max_ctx = PROMPT + (W + 2 + reps * K) + (Ke + 2) + len(other_batches) * (W + 2 + Kb) + 24
     cfg = dict(LLAMA7B, n_layers=args.layers)
     model = Llama(cfg["n_layers"], cfg["d_model"], cfg["n_heads"], cfg["n_kv_heads"], cfg["d_ffn"], cfg["vocab"],
-                  max_batch=B, max_context=max_ctx, seed=SEED, tp_rank=rank, tp_size=world)
+                  max_batch=max_batch, max_context=max_ctx, seed=SEED, tp_rank=rank, tp_size=world)
     if world > 1:
         def allreduce(ptr, count, dtype, stream):
             iface = {"shape": (count,), "typestr": "<u2" if dtype == jb.BF16 else "<f4", "data": (ptr, False), "version": 2}
@@ -413,112 +508,142 @@ def main():
                 t = t.view(torch.bfloat16)
             dist.all_reduce(t)
         model.set_allreduce(allreduce)
-        if os.environ.get("JSM_TP_NCCL", "0") != "1":
+        if not use_nccl:
             # the product path: the model's own exchange over peer memory (NCCL stays as the plumbing and, with
             # JSM_TP_NCCL=1, as the comparison)
             model.connect_peers(dist)
 
-    # synthetic prompt: B sequences of PROMPT token ids, uniform in [0, vocab)
-    nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+    # synthetic prompts: max_batch sequences of PROMPT token ids, uniform in [0, vocab)
+    nxt = torch.zeros(max_batch, dtype=torch.int32, device="cuda")
     t_pre0 = time.perf_counter()
-    for b in range(B):
+    for b in range(max_batch):
         ids = torch.empty(PROMPT, dtype=torch.int32, device="cuda")
         jb.fill(ids, SEED, 5000 + b, 2, 0, cfg["vocab"])
         model.prefill(ids, b, nxt)
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t_pre0
     ids = nxt.clone()
+    ctx = [PROMPT] * max_batch                      # host copy of the context lengths (the device keeps its own)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def timed_decode(Bt, Kt, Wt, n_reps, sample_clocks):
+        """Wt eager warm-up steps, then n_reps times Kt replays of the captured step of batch Bt; device time (CUDA events,
+        max over ranks) of the median repetition, the mean context length of that repetition, launches per step."""
+        ids_b, nxt_b = ids[:Bt], nxt[:Bt]
+        launches0 = jb.launch_count()
+        for i in range(Wt):
+            model.decode_step(ids_b, nxt_b)
+            ids_b.copy_(nxt_b)
+            if i == 0:
+                jb.check_device_errors()  # a bounded device-side wait that ran out (a peer that never arrived) stops the run here
         torch.cuda.synchronize()
+        per_step = (jb.launch_count() - launches0) // Wt
+        graph = None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    model.decode_step(ids_b, nxt_b)
+                    ids_b.copy_(nxt_b)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = g
+        except Exception as e:  # multi-rank capture of the collective can be refused: run the step eagerly
+            if rank == 0:
+                print(f"# graph capture failed ({type(e).__name__}: {e}); timing eager steps", file=sys.stderr)
+            torch.cuda.synchronize()
 
-    # warm-up steps (eager: first-use set-up happens here), then capture one step
-    launches0 = jb.launch_count()
-    for i in range(W):
-        model.decode_step(ids, nxt)
-        ids.copy_(nxt)
-        if i == 0:
-            jb.check_device_errors()  # a bounded device-side wait that ran out (a peer that never arrived) stops the run here
-    torch.cuda.synchronize()
-    launches_per_step = (jb.launch_count() - launches0) // W
+        def one_step():
+            if graph is not None:
+                graph.replay()
+            else:
+                model.decode_step(ids_b, nxt_b)
+                ids_b.copy_(nxt_b)
+        one_step()  # one replay outside the timed region
+        for b in range(Bt):
+            ctx[b] += Wt + 1
+        clocks = ClockSampler(local) if sample_clocks else None
+        barrier()
+        if clocks is not None and rank == 0:
+            clocks.start()
+        runs = []
+        for _ in range(n_reps):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            ev0.record()
+            for _ in range(Kt):
+                one_step()
+            ev1.record()
+            barrier()
+            runs.append((max_over_ranks(ev0.elapsed_time(ev1)), sum(ctx[:Bt]) / Bt + (Kt + 1) / 2.0))
+            for b in range(Bt):
+                ctx[b] += Kt
+        clock_info = clocks.stop() if (clocks is not None and rank == 0) else None
+        jb.check_device_errors()
+        runs_sorted = sorted(runs)
+        ms, ctx_mid = runs_sorted[len(runs_sorted) // 2]
+        return {"ms": ms, "ctx_mid": ctx_mid, "launches_per_step": per_step, "graph": graph, "clocks": clock_info,
+                "all_ms_per_step": [r[0] / Kt for r in runs]}
+
     if args.profile_steps > 0:
+        for _ in range(W):
+            model.decode_step(ids[:B], nxt[:B])
+            ids[:B].copy_(nxt[:B])
+        torch.cuda.synchronize()
         torch.cuda.profiler.start()
         for _ in range(args.profile_steps):
-            model.decode_step(ids, nxt)
-            ids.copy_(nxt)
+            model.decode_step(ids[:B], nxt[:B])
+            ids[:B].copy_(nxt[:B])
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
-        print(f"# profiled {args.profile_steps} eager decode steps, {launches_per_step} launches per step", file=sys.stderr)
+        print(f"# profiled {args.profile_steps} eager decode steps", file=sys.stderr)
         return
-    graph = None
-    try:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                model.decode_step(ids, nxt)
-                ids.copy_(nxt)
-        torch.cuda.current_stream().wait_stream(side)
-        graph = g
-    except Exception as e:  # multi-rank capture of the collective can be refused: run the step eagerly
-        if rank == 0:
-            print(f"# graph capture failed ({type(e).__name__}: {e}); timing eager steps", file=sys.stderr)
-        torch.cuda.synchronize()
 
-    def one_step():
-        if graph is not None:
-            graph.replay()
-        else:
-            model.decode_step(ids, nxt)
-            ids.copy_(nxt)
+    peak, peak_kind = measured_peaks()
+    wbytes, kv_per_tok = model.step_bytes()
 
-    one_step()  # one replay outside the timed region
-    clocks = ClockSampler(local)
-    barrier()
-    if rank == 0:
-        clocks.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(K):
-        one_step()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    last_tokens = nxt[:8].tolist()
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    clock_info = clocks.stop() if rank == 0 else None
+    def step_roofline(Bt, ms_per_step, ctx_mid):
+        nbytes = wbytes + Bt * ctx_mid * kv_per_tok
+        gbs = nbytes / (ms_per_step * 1e-3) / 1e9
+        return {"bytes_per_step": nbytes, "achieved_gbs": gbs, "frac": gbs / peak}
+
+    head = timed_decode(B, K, W, reps, True)
+    ms = head["ms"]
+    graph = head["graph"]
     tok_s = B * K / (ms / 1e3)
-    ctx_mid = PROMPT + W + 1 + K // 2  # mean context length over the timed steps
+    last_tokens = nxt[:min(B, 8)].tolist()
 
-    # end-to-end through the C ABI with host buffers: ids from pinned memory in, next tokens out, every step
+    # end to end through the C ABI with HOST buffers: jsm_llama_decode_step_host takes the ids from (pinned) host memory,
+    # replays the graph the library captured for this batch size and hands the next tokens back to host memory, every step
     h_ids = torch.empty(B, dtype=torch.int32).pin_memory()
     h_next = torch.empty(B, dtype=torch.int32).pin_memory()
-    h_ids.copy_(ids.cpu())
-    Ke = min(K, 64)
+    h_ids.copy_(ids[:B].cpu())
+    e2e_stream = torch.cuda.Stream()
+    with torch.cuda.stream(e2e_stream):
+        for _ in range(2):  # the first call captures
+            model.decode_step_host(h_ids, h_next)
+            h_ids.copy_(h_next)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(Ke):
+            model.decode_step_host(h_ids, h_next)
+            h_ids.copy_(h_next)
+        e2e_s = time.perf_counter() - t0
     barrier()
-    t0 = time.perf_counter()
-    for _ in range(Ke):
-        ids.copy_(h_ids, non_blocking=True)
-        if graph is not None:
-            graph.replay()
-        else:
-            model.decode_step(ids, nxt)
-        h_next.copy_(nxt, non_blocking=True)
-        torch.cuda.synchronize()
-        h_ids.copy_(h_next)
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    for b in range(B):
+        ctx[b] += Ke + 2
+    e2e_s = max_over_ranks(e2e_s)
     e2e_tok_s = B * Ke / e2e_s
+    ids[:B].copy_(h_ids)
+
+    batches = {}
+    for ob in other_batches:
+        r = timed_decode(ob, Kb, W, 1, False)
+        r.pop("graph")
+        ms_b = r["ms"] / Kb
+        batches[str(ob)] = {"tok_s": ob * Kb / (r["ms"] / 1e3), "ms_per_step": ms_b, "steps": Kb,
+                            "launches_per_step": r["launches_per_step"], "mean_context": r["ctx_mid"],
+                            "step_roofline": step_roofline(ob, ms_b, r["ctx_mid"])}
 
     if rank != 0:
         shutdown(graph)
@@ -526,7 +651,6 @@ def main():
 
     # roofline of the dominant kernel, timed alone: the SwiGLU gate/up weight stream of one layer
     # (2 x 11008 x 4096 bf16 = 180 MB per launch over packed weights, 4 rotating weight sets: larger than L2)
-    peak, peak_kind = measured_peaks()
     d, ffn_l = cfg["d_model"], cfg["d_ffn"] // world
     x = torch.empty(B, d, device="cuda", dtype=torch.bfloat16)
     jb.fill(x, SEED, 7000, 0, 0.0, 1.0)
@@ -544,14 +668,14 @@ def main():
     for i in range(4):
         stream_once(i)
     torch.cuda.synchronize()
-    reps = 96
+    n_launch = 96
     r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     r0.record()
-    for i in range(reps):
+    for i in range(n_launch):
         stream_once(i % 4)
     r1.record()
     torch.cuda.synchronize()
-    k_ms = r0.elapsed_time(r1) / reps
+    k_ms = r0.elapsed_time(r1) / n_launch
     alg_bytes = 2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
     # the same kernel inside the step (chained launches: its ring is full of weights when its predecessor ends): device
@@ -561,7 +685,7 @@ def main():
         import numpy as np
         n_max = 4 * cfg["n_layers"] + 1
         jb.check(jb.lib().jsm_trace_begin(n_max))
-        model.decode_step(ids, nxt)
+        model.decode_step(ids[:B], nxt[:B])
         torch.cuda.synchronize()
         buf = np.zeros((n_max, 148, 8), np.uint64)
         n_tr, n_ctas = C.c_int(), C.c_int()
@@ -574,44 +698,78 @@ def main():
                 spans.append((v[:, 7].max() - v[:, 2].min()) / 1e6)
         if spans:
             ms_in = float(np.mean(spans))
-            in_step = {"ms_per_launch": ms_in, "achieved": (2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2) / (ms_in * 1e-3) / 1e9,
+            in_step = {"ms_per_launch": ms_in, "achieved": alg_bytes / (ms_in * 1e-3) / 1e9,
                        "how": "device time stamps (globaltimer) of one eager decode step: predecessor kernel finished -> last "
                               "CTA of the gate/up projection done, mean over the layers"}
             in_step["frac"] = in_step["achieved"] / peak
-    wbytes, kv_per_tok = model.step_bytes()
-    step_bytes = wbytes + B * ctx_mid * kv_per_tok
-    step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
+    del packed_sets
 
+    # DRAM traffic of one launch of this kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum): the
+    # capture is of the 8-token, one-GPU shape only; any other run reports none
+    traffic = 185.3e6 if (world == 1 and B == 8) else None
     line = {
         "metric": "llama7b_decode_tokens_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, world),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (185.3e6 if (world == 1 and B <= 16) else None),
-                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape at 8 tokens "
-                                     "from one ncu capture (profiles/linear_packed_gate_up_b8_ncu.md); algorithmic bytes_per_launch beside it",
+                     "traffic": traffic,
+                     "traffic_note": "measured under ncu for one launch of this kernel at 8 tokens on one GPU; null for any other shape",
                      "kernel": "linear_packed_kernel: gate/up projection weight stream (jsm_linear_bf16_packed, silu*up epilogue)",
                      "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes,
                      "timed": "isolated launches of the kernel (CUDA events, 96 launches over 4 rotating weight sets)",
                      "in_step": in_step},
-        "step_roofline": {"bytes_per_step": step_bytes, "achieved_gbs": step_gbs, "frac": step_gbs / peak,
-                          "note": "all weights + cached K/V of the step over the measured step time"},
-        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "steps": Ke},
-        "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "cuda_graph": graph is not None,
-        "prefill_s": prefill_s, "clocks": clock_info,
-        # greedy tokens of the last timed step (first 8 sequences): the same at every GPU count unless two logits tie
+        "step_roofline": dict(step_roofline(B, ms / K, head["ctx_mid"]),
+                              note="all streamed weights (every projection and lm_head) + cached K/V of the step over the measured step time"),
+        "repetitions": {"n": reps, "ms_per_step": head["all_ms_per_step"], "reported": "median"},
+        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B, "steps": Ke,
+                "how": "jsm_llama_decode_step_host: ids from pinned host memory, library-owned CUDA graph of the step, next tokens "
+                       "back to host memory and a stream synchronisation, every step"},
+        "gpu_launches": head["launches_per_step"] * K, "launches_per_step": head["launches_per_step"], "cuda_graph": graph is not None,
+        "prefill_s": prefill_s, "clocks": head["clocks"],
+        # greedy tokens of the last timed step (first 8 sequences).  Random-init logits are nearly flat, so after dozens of
+        # steps these differ between GPU counts through bf16 summation order alone: they identify a run, they prove no
+        # parity.  Parity across GPU counts is what `tp_parity` measures.
         "last_tokens": last_tokens,
     }
+    if batches:
+        line["batches"] = batches
+    if parity is not None:
+        line["tp_parity"] = parity
     if args.layers != 32:
         line["invalid"] = "debug run with fewer layers"
+    if extras and world == 1:
+        # configurations 2, 3 and 4 of the baseline as kernel-level legs (a few seconds): the model's memory is released first
+        shutdown_model = model
+        del graph
+        head["graph"] = None
+        shutdown_model.close()
+        torch.cuda.empty_cache()
+        kernels = {}
+        for wl in ("expr", "flash", "kvdecode"):
+            sub = argparse.Namespace(**vars(args))
+            sub.workload, sub.steps, sub.warmup = wl, 20, 3
+            try:
+                for rec in run_kernel_workload(sub, collect=True):
+                    kernels[rec["metric"]] = {"value": rec["value"], "unit": rec["unit"], "ms": rec["ms_per_step"],
+                                              "frac_of_peak": rec["roofline"]["frac"], "peak": rec["roofline"]["peak"],
+                                              "workload": rec["config"]["workload"]}
+            except Exception as e:
+                kernels[wl] = {"failed": f"{type(e).__name__}: {e}"}
+        line["kernels"] = kernels
+        graph = None
     if not args.no_cpu and world == 1:
         try:
             line["cpu_baseline"] = cpu_port_baseline()
         except Exception as e:
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {type(e).__name__}: {e}"}
+    bad_parity = parity is not None and (parity["max_rel_logit_diff"] > parity["tolerance"] or not parity["top1_equal_where_margin_clear"])
+    if bad_parity:
+        line["invalid"] = "tensor-parallel parity check failed"
     print(json.dumps(line), flush=True)
     shutdown(graph)
+    if bad_parity:
+        sys.exit(3)
 
 
 def shutdown(graph):

@@ -374,6 +374,14 @@ jsm_status jsm_llama_prefill(jsm_model* m, const int32_t* d_ids, int seq, int T,
  * this step are meaningless and the next jsm_check_device_errors returns JSM_SHAPE ("context overflow"). */
 jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, int32_t* d_next, float* d_logits,
                                  void* stream);
+/* The same step for callers whose tokens live in HOST memory (the reference's generation loop is host code,
+ * transformer_test.hpp:227-241): h_ids[batch] in, h_next[batch] out, h_logits (or NULL) F32 [batch, vocab] out; the
+ * copies run on `stream` (a non-default stream), pinned host buffers make them asynchronous up to the final
+ * synchronisation, after which the outputs are valid.  The model captures the step once per batch size into a CUDA
+ * graph of its own and replays it (the first call of a batch size captures: slower, and it must not itself run inside
+ * a stream capture).  A tensor-parallel model that still uses the host all-reduce hook runs the step eagerly. */
+jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int batch, int32_t* h_next, float* h_logits,
+                                      void* stream);
 /* Host-side bookkeeping of context lengths (advance after a captured step is replayed). */
 jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len);
 jsm_status jsm_llama_reset(jsm_model* m);

@@ -111,6 +111,7 @@ SYMBOLS = {
     "jsm_llama_load": (_i, [_vp, C.c_char_p]),
     "jsm_llama_prefill": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "jsm_llama_decode_step": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
+    "jsm_llama_decode_step_host": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "jsm_llama_set_context": (_i, [_vp, _i, _i]),
     "jsm_llama_reset": (_i, [_vp]),
     "jsm_llama_step_bytes": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),

@@ -18,6 +18,7 @@
 #include <stdlib.h>
 #include <string>
 #include <vector>
+#include <map>
 #include <algorithm>
 
 namespace jsm {
@@ -81,6 +82,9 @@ struct jsm_model {
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
     uint64_t weight_bytes = 0;
+    // host-buffer decode step (jsm_llama_decode_step_host): staging buffers and one instantiated graph per batch size
+    int32_t *ids_dev = nullptr, *next_dev = nullptr;
+    std::map<int, cudaGraphExec_t> step_graphs;
 };
 
 namespace jsm {
@@ -611,6 +615,9 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
+    JSM_TRY(dev_alloc(m, &m->ids_dev, (size_t)c.max_batch));
+    JSM_TRY(dev_alloc(m, &m->next_dev, (size_t)c.max_batch));
+    tc_error_word();  // first use allocates the device's error word: do it here, not inside a captured step
     // the chunk length of the decode attention depends on the batch of the step: room for the largest need over 1..max_batch
     m->dec_scratch_bytes = jsm_attn_decode_scratch_bytes_max(c.max_batch, m->Hq_l, D, c.max_context);
     JSM_TRY(dev_alloc(m, &m->dec_scratch, m->dec_scratch_bytes / sizeof(float) + 4));
@@ -625,6 +632,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
 jsm_status jsm_llama_destroy(jsm_model* m) {
     if (!m) return JSM_OK;
     cudaDeviceSynchronize();
+    for (auto& g : m->step_graphs) cudaGraphExecDestroy(g.second);
     for (void* p : m->allocs) cudaFree(p);
     if (m->unpack_buf) cudaFree(m->unpack_buf);
     delete m;
@@ -863,6 +871,43 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
     if (s != JSM_OK) return s;
     return logits_and_argmax(m, 0, batch, batch, d_next, d_logits, st);
+}
+
+// The decode step for callers that hold their tokens in HOST memory (the reference's generation loop keeps everything
+// on the host, transformer_test.hpp:227-241): ids in, next tokens (and optionally logits) out.  The step itself is
+// captured once per batch size into a CUDA graph that the model owns (positions and context lengths live on the device,
+// so the same graph serves every step) and replayed: one graph launch instead of ~165 kernel launches per step.
+jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int batch, int32_t* h_next, float* h_logits, void* stream) {
+    if (!m || !h_ids || !h_next) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step_host: null argument");
+    if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step_host: batch %d (1..%d)", batch, m->c.max_batch);
+    cudaStream_t st = as_stream(stream);
+    if (!st) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step_host: needs a stream of its own (the legacy default stream cannot be captured)");
+    JSM_CUDA_CHECK(cudaMemcpyAsync(m->ids_dev, h_ids, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, st));
+    const bool host_allreduce = m->c.tp_size > 1 && !m->tp_connected;  // the hook belongs to the host: run such a step eagerly
+    if (host_allreduce) {
+        jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, m->logits, st);
+        if (s != JSM_OK) return s;
+    } else {
+        auto it = m->step_graphs.find(batch);
+        if (it == m->step_graphs.end()) {
+            cudaGraph_t graph = nullptr;
+            JSM_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+            jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, m->logits, st);
+            cudaError_t e = cudaStreamEndCapture(st, &graph);
+            if (s != JSM_OK) { if (graph) cudaGraphDestroy(graph); return s; }
+            if (e != cudaSuccess) { cudaGetLastError(); JSM_FAIL(JSM_CUDA, "jsm_llama_decode_step_host: stream capture failed: %s", cudaGetErrorString(e)); }
+            cudaGraphExec_t exec = nullptr;
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) { cudaGetLastError(); JSM_FAIL(JSM_CUDA, "jsm_llama_decode_step_host: graph instantiation failed: %s", cudaGetErrorString(e)); }
+            it = m->step_graphs.emplace(batch, exec).first;
+        }
+        JSM_CUDA_CHECK(cudaGraphLaunch(it->second, st));
+    }
+    JSM_CUDA_CHECK(cudaMemcpyAsync(h_next, m->next_dev, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, st));
+    if (h_logits) JSM_CUDA_CHECK(cudaMemcpyAsync(h_logits, m->logits, sizeof(float) * (size_t)batch * m->c.vocab, cudaMemcpyDeviceToHost, st));
+    JSM_CUDA_CHECK(cudaStreamSynchronize(st));
+    return JSM_OK;
 }
 
 jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len) {

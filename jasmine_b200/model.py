@@ -94,6 +94,12 @@ class Llama:
         check(lib().jsm_llama_decode_step(self._h, ids.data_ptr(), ids.numel(), next_tokens.data_ptr(),
                                           logits.data_ptr() if logits is not None else None, stream_ptr()))
 
+    def decode_step_host(self, h_ids, h_next, h_logits=None):
+        """jsm_llama_decode_step_host: token ids from a host tensor (pinned for speed), next tokens into a host tensor;
+        returns after the outputs are valid."""
+        check(lib().jsm_llama_decode_step_host(self._h, h_ids.data_ptr(), h_ids.numel(), h_next.data_ptr(),
+                                               h_logits.data_ptr() if h_logits is not None else None, stream_ptr()))
+
     def set_context(self, seq: int, n: int):
         check(lib().jsm_llama_set_context(self._h, seq, n))
 

@@ -254,3 +254,34 @@ def test_decode_past_max_context_is_reported_not_faulted():
     jb.check_device_errors()
     assert int(torch.ones(4, device="cuda").sum()) == 4
     m.close()
+
+
+def test_host_buffer_step_equals_device_step():
+    """jsm_llama_decode_step_host (ids from host memory, the library's own CUDA graph of the step, tokens and logits back
+    to host memory) generates what the device-pointer step generates, for two batch sizes on one model."""
+    cfg = dict(L=2, d=256, Hq=4, Hkv=2, D=128, ffn=512, vocab=1024)
+    mk = lambda: Llama(cfg["L"], cfg["d"], cfg["Hq"], cfg["Hkv"], cfg["ffn"], cfg["vocab"], max_batch=3, max_context=128, seed=4)
+    prompts = [cases.ints(30, 4, 820 + b, 0, 1024) for b in range(3)]
+    a, b = mk(), mk()
+    nxt_a = torch.zeros(3, dtype=torch.int32, device="cuda")
+    nxt_b = torch.zeros(3, dtype=torch.int32, device="cuda")
+    for s in range(3):
+        a.prefill(torch.from_numpy(prompts[s]).cuda(), s, nxt_a)
+        b.prefill(torch.from_numpy(prompts[s]).cuda(), s, nxt_b)
+    assert torch.equal(nxt_a, nxt_b)
+    h_ids = nxt_b.cpu().pin_memory()
+    h_next = torch.empty(3, dtype=torch.int32).pin_memory()
+    h_logits = torch.empty(3, 1024).pin_memory()
+    logits = torch.empty(3, 1024, device="cuda")
+    with torch.cuda.stream(torch.cuda.Stream()):
+        for step in range(5):
+            n = 3 if step < 3 else 2          # the last steps run a smaller batch: a second graph of the same model
+            ids = nxt_a[:n].clone()
+            a.decode_step(ids, nxt_a[:n], logits[:n])
+            b.decode_step_host(h_ids[:n], h_next[:n], h_logits[:n])
+            torch.cuda.current_stream().synchronize()
+            assert torch.equal(nxt_a[:n].cpu(), h_next[:n]), f"step {step}"
+            assert torch.equal(logits[:n].cpu(), h_logits[:n]), f"logits of step {step}"
+            h_ids[:n].copy_(h_next[:n])
+    jb.check_device_errors()
+    a.close(); b.close()

@@ -328,8 +328,9 @@ def run_timeline(args):
         ptrs[0] = p.value
         for r in range(1, tp):
             ptrs[r] = fakes[r - 1].data_ptr()
-        flags = torch.full((16,), 1 << 30, dtype=torch.int32)
-        jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 64, jb.stream_ptr()))
+        flags = torch.full((32,), 1 << 30, dtype=torch.int32)   # the flag words of both exchange protocols: peers "arrived"
+        flags[16] = 0                                            # ... but this rank's own push flag is set by its own kernels
+        jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 128, jb.stream_ptr()))
         torch.cuda.synchronize()
         jb.check(jb.lib().jsm_llama_tp_connect(m._h, ptrs))
     nxt = torch.zeros(B, dtype=torch.int32, device="cuda")

@@ -326,12 +326,15 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
 jsm_status jsm_llama_destroy(jsm_model* m);
 jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user);
 /* Tensor-parallel exchange over peer memory (no counterpart in the reference, which has no parallelism).
- * Every rank owns a region [flags | buffer A | buffer B] in its own memory (jsm_llama_tp_region); the host makes the
+ * Every rank owns a region [flags | buffer A | buffer B | two push buffers of 8 slots] in its own memory
+ * (jsm_llama_tp_region); the host makes the
  * peers' regions addressable (jsm_ipc_export / jsm_ipc_import between processes of one node) and hands them to
  * jsm_llama_tp_connect ([tp_size] device pointers, the entry of the own rank is ignored).  From then on the model sums
  * the rank-local outputs of the attention output projection and of the FFN down projection itself: one kernel per
  * exchange that signals the peers, waits (bounded) for them, adds all ranks' buffers in rank order, adds the sum into
- * the residual stream and normalises.  Without a connection the all-reduce hook (jsm_llama_set_allreduce) is used. */
+ * the residual stream and normalises; calls of at most 64 tokens (every decode step) fuse the exchange into the
+ * projections instead (jsm_tp_linear_push / jsm_tp_linear_reduce below).  Without a connection the all-reduce hook
+ * (jsm_llama_set_allreduce) is used. */
 jsm_status jsm_llama_tp_region(jsm_model* m, void** d_region, size_t* bytes);
 jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions);
 /* The exchange kernel on its own.  d_regions: [size] regions of jsm_tp_region_bytes(max_tokens, d) bytes, zero before
@@ -346,6 +349,29 @@ jsm_status jsm_tp_set_wait_limit_ms(int ms);
 jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
                                      const int32_t* d_pass, int site, int n_sites, void* d_h, void* d_xn, float eps,
                                      int T, int d, void* stream);
+/* The exchange fused into the projections around it, which is what a decode step (at most 64 tokens) runs instead of the
+ * kernel above - no launch of its own, one NVLink traversal between producer and consumer:
+ * jsm_tp_linear_push   Y = X . W^T (packed W [N, K], N = d_model) is not stored locally: every finished tile goes,
+ *                      as bf16, straight into slot `rank` of push buffer `which_buffer` of EVERY region (peer stores
+ *                      from the epilogue), and the CTA that completes the launch releases the epoch
+ *                      d_state[0] * n_sites + site + 1 to every peer's push flag for this rank.
+ * jsm_tp_linear_reduce the projection that reads the residual stream next: while all CTAs stream their weights, one CTA
+ *                      per 128-column tile of h waits (bounded) for the peers' flags of that epoch, forms
+ *                      h += sum of the size slots in rank order (local loads only), stores h and its per-tile sums
+ *                      of squares (d_ssq: F32 [ceil(d/128)][T]); then Y = (h . W'^T) / sqrt(mean(h^2) + eps) with the
+ *                      epilogue of jsm_linear_bf16_packed (the RMSNorm gain folded into W').
+ * d_state: I32 [8] of the calling rank, zero before the first call: word 0 is the number of the forward pass (the
+ * caller bumps it between passes, before any kernel of the pass can run), the rest belongs to the kernels (counters
+ * of finished CTAs and reduced tiles, the epoch up to which h is reduced).  The ranks must run the same
+ * sequence of (which_buffer alternating, site), epochs growing from call to call.  Workspace: as for
+ * jsm_linear_bf16_packed (jsm_linear_pack / jsm_linear_packed_reserve).  A peer that does not arrive within the wait
+ * limit leaves h as it is and raises JSM_TIMEOUT at the next jsm_check_device_errors. */
+jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
+                              int32_t* d_state, int site, int n_sites, const void* d_X, const void* d_packed, int T,
+                              int N, int K, void* stream);
+jsm_status jsm_tp_linear_reduce(void* d_region, int rank, int size, int which_buffer, int max_tokens, int32_t* d_state,
+                                int site, int n_sites, void* d_h, float* d_ssq, const void* d_packed, int epilogue,
+                                void* d_Y, int out_dtype, int T, int N, int d, float eps, void* stream);
 /* CUDA IPC plumbing for regions that live in another process of the same node (64-byte handles). */
 jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64);
 jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr);

@@ -101,6 +101,8 @@ SYMBOLS = {
     "jsm_tp_region_bytes": (_sz, [_i, _i]),
     "jsm_tp_set_wait_limit_ms": (_i, [_i]),
     "jsm_tp_allreduce_add_norm": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _f, _i, _i, _vp]),
+    "jsm_tp_linear_push": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "jsm_tp_linear_reduce": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp]),
     "jsm_ipc_export": (_i, [_vp, C.c_char_p]),
     "jsm_ipc_import": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "jsm_ipc_close": (_i, [_vp]),

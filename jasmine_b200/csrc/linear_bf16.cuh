@@ -49,6 +49,34 @@ struct PackedArgs {
     int ssq_stride = 0;       // 0 = T
     float eps = 0.0f;
     float* ssq_out = nullptr;
+    // Tensor-parallel exchange fused into the projection (tp_comm.cu describes the protocol).
+    // push: the bf16 outputs are stored into this rank's slot of EVERY rank's exchange buffer (peer stores) instead of
+    // Y, and the CTA that finishes last releases the call's epoch to every peer's flag word.
+    // reduce: before the token operand X (= the residual stream h) is read, the launch waits for the peers' flags, forms
+    // h += sum over the ranks' slots (rank order, local loads only), leaves the per-tile sums of squares of the new h in
+    // ssq_in's place and only then streams X; Y = (h . W'^T) / rms(h) as with ssq_in.
+    const struct TpFuse* tp = nullptr;
+};
+
+constexpr int TP_PUSH_MAX_T = 64;  // launches of at most this many tokens exchange by push; longer ones by the exchange kernel
+struct TpFuse {
+    int n_ranks = 0, rank = 0;
+    const int* pass = nullptr;     // device: number of the forward pass
+    int site = 0, n_sites = 1;     // the exchange's place in the pass: epoch = pass * n_sites + site + 1
+    int* state = nullptr;          // device, local, 4 words, zero at first: [0] folding CTAs of a pushing launch done, [1] tiles of h
+                                   // reduced (both self-resetting), [2] epoch up to which h is completely reduced
+    // push
+    bool push = false;
+    void* push_dst[8] = {nullptr};   // per rank: where this rank's [T, N] block goes in that rank's memory
+    int* push_flag[8] = {nullptr};   // per rank: that rank's flag word for this rank
+    // reduce
+    bool reduce = false;
+    const void* slots = nullptr;     // local: rank r's block at slots + r * slot_stride bytes
+    size_t slot_stride = 0;
+    const int* flags = nullptr;      // local: flag word per source rank
+    void* h = nullptr;               // [T, d] bf16 rows to update (d = K of the launch)
+    float* ssq = nullptr;            // [ceil(d/128)][ssq_stride] sums of squares of the new h (becomes ssq_in)
+    long long wait_limit = 0;        // cycles
 };
 // Row of the logical (stacked) weight matrix that packed row r of tile j holds; -1 = padding.
 // plain : rows j*128 .. j*128+127 of an [N, K] matrix.
@@ -69,6 +97,15 @@ size_t linear_packed_ws_floats(int T, int N, int K, int paired);
 // packs (or, with unpack, rebuilds) a row-major [N, K] matrix ([2N, K] gate rows then up rows when paired)
 jsm_status linear_pack_launch(const void* W, int N, int K, int paired, void* packed, bool unpack, cudaStream_t st);
 jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st);
+// exchange regions (tp_comm.cu): [flags | buffer A | buffer B | push buffer 0 | push buffer 1]
+size_t tp_region_bytes(int max_tokens, int d);
+size_t tp_buffer_offset(int which, int max_tokens, int d);
+size_t tp_push_offset(int which, int max_tokens, int d);
+size_t tp_slot_bytes(int d);
+int tp_push_flag_word();
+long long tp_wait_limit_cycles();
+// whether a plain bf16 projection of this shape and token count can push its outputs (TpFuse::push)
+bool linear_packed_can_push(int N, int K, int T);
 // dimensions of the packed image
 void pk_dims(int N, int K, int paired, int* n_tiles, int* kbt);
 // reads (and clears) the device error word of the tensor-core kernels; synchronises the stream

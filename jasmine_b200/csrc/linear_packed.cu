@@ -76,7 +76,53 @@ struct PkParams {
     float inv_d, eps;     // 1 / (features of X), epsilon under the square root
     float* ssq_out;       // [n_tiles][ssq_stride]: sums of squares of this launch's outputs per tile and token, or null
     unsigned long long* trace;  // optional timeline: 8 time stamps (globaltimer, ns) per CTA of this launch
+    // tensor-parallel exchange fused into the launch (TpFuse in linear_bf16.cuh; protocol in tp_comm.cu)
+    int tp_mode;                // 0 none, 1 push the outputs to every rank's slot, 2 reduce the slots into h before X is read
+    int tp_n, tp_rank;
+    int tp_site, tp_n_sites;
+    const int* tp_pass;
+    int* tp_state;              // local: [0] folding CTAs done, [1] tiles of h reduced (self-resetting); [2] epoch up to which h is reduced
+    int tp_expect;              // push: folding CTAs of this launch
+    uint8_t* tp_dst[8];
+    int* tp_flag[8];
+    const uint8_t* tp_slots;
+    size_t tp_slot_stride;
+    const int* tp_flags;
+    __nv_bfloat16* tp_h;
+    float* tp_ssq;
+    long long tp_wait;
 };
+
+constexpr int TP_TIMEOUT_CODE = 16;  // error word code of an exchange whose peers did not arrive in time (as in tp_comm.cu)
+__device__ __forceinline__ void pk_st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int pk_ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int pk_ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 pk_ld_cg_v4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+// generic-proxy writes to global memory (other CTAs' stores of h) before the copy engine's reads of the same bytes
+__device__ __forceinline__ void pk_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// One thread waits (bounded) until the word *p has reached epoch E; epochs only grow, the comparison is wrap-safe.  The
+// polls are spaced out: thousands of spinning threads would slow down the very kernels they wait for.  A wait that runs out
+// records the error and returns.
+__device__ __forceinline__ void pk_wait_epoch(const int* p, int E, long long limit, int* err) {
+    const long long t0 = clock64();
+    while ((int)(pk_ld_acquire_gpu(p) - E) < 0) {
+        __nanosleep(64);
+        if (clock64() - t0 > limit) {
+            if (err) atomicCAS(err, 0, TP_TIMEOUT_CODE);
+            break;
+        }
+    }
+}
+// local state words of the fused exchange: [0] folding CTAs of a pushing launch done, [1] tiles of h reduced (both
+// self-resetting), [2] epoch up to which h is completely reduced
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -142,6 +188,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     __shared__ float pair_smem[64 * 17];  // paired epilogue: up values of 16 token columns, padded rows
     __shared__ float row_scale[256];      // 1 / rms of every token when the RMSNorm is fused into this projection
     __shared__ float ssq_part[4 * 256];   // per-warp sums of squares of a whole tile's outputs
+    __shared__ int tp_ok_smem;            // reduce: every peer's flag arrived in time
 
     chain_trigger();
     if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
@@ -217,8 +264,16 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     } else if (warp == 6) {
         // ---- X producer: the token blocks of every stage, once the predecessor kernel has written them --------------
         if (lane == 0) {
-            chain_wait();
-            PK_TRACE(2);  // predecessor complete
+            if (P.tp_mode == 2) {
+                // X is the residual stream that the first CTAs of this launch are completing (h += the ranks' slots).  Its
+                // readiness is announced through an epoch word, not by the end of the predecessor kernel; then the generic
+                // writes of the reducing CTAs are ordered before the copy engine's reads.  Nothing else the X producer
+                // touches belongs to another kernel, so it does not wait for the predecessor.
+                const int E = *reinterpret_cast<const volatile int*>(P.tp_pass) * P.tp_n_sites + P.tp_site + 1;
+                pk_wait_epoch(P.tp_state + 2, E, P.tp_wait, P.err);
+                pk_fence_proxy_async();
+            } else chain_wait();
+            PK_TRACE(2);  // predecessor complete (fused exchange: h complete)
             int rem = (int)(u_end - u_begin), kb = (int)(u_begin % P.kbt);
             int i = 0, s = 0;
             uint32_t ph = 0;
@@ -298,6 +353,97 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         int seg = 0, cl_syncs = 0;
         // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
         // predecessor now (the MMA warp is busy with the weight stream meanwhile) and prepare what does not need the accumulator.
+        if (P.tp_mode == 2) {
+            // ---- tensor-parallel exchange, consumer side.  Every rank (this one included) has pushed its block of the
+            // previous projection's output into its slot of this rank's buffer and released the exchange's epoch to this
+            // rank's flag word for it.  The first CTAs of the launch (one per 128-column tile of h, while all CTAs stream
+            // their weights) wait for the flags - not for the end of the predecessor kernel: its own flag says that its
+            // block is complete - add the slots in rank order to h (local loads only), store h and the tile's sums of
+            // squares and publish the tile's epoch; every CTA waits for all tiles before it reads the statistics.
+            const int red_tiles = (P.K + 127) / 128;
+            const int E = *reinterpret_cast<const volatile int*>(P.tp_pass) * P.tp_n_sites + P.tp_site + 1;
+            if ((int)blockIdx.x < red_tiles) {
+                if (etid == 0) tp_ok_smem = 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid < P.tp_n) {
+                    const int* flag = P.tp_flags + etid;
+                    const long long t0 = clock64();
+                    while ((int)(pk_ld_acquire_sys(flag) - E) < 0) {
+                        __nanosleep(64);
+                        if (clock64() - t0 > P.tp_wait) {
+                            tp_ok_smem = 0;
+                            if (P.err) atomicCAS(P.err, 0, TP_TIMEOUT_CODE);
+                            break;
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool tp_ok = tp_ok_smem != 0;  // a rank that never arrived: h stays as it is, the error word says so
+                const int n_vec = P.T * 16;  // 16-byte vectors of one tile: 16 per token
+                int handled = 0;
+                for (int j = blockIdx.x; j < red_tiles; j += gridDim.x, ++handled) {
+                    for (int v0 = 0; v0 < n_vec; v0 += 128) {  // warp-uniform trip count: the shuffles below need every lane
+                        const int v = v0 + etid;
+                        const int t = v >> 4, c = j * 128 + (v & 15) * 8;
+                        const bool in_range = v < n_vec && c < P.K;
+                        float sq = 0.0f;
+                        if (in_range) {
+                            const size_t off = ((size_t)t * P.K + c) * 2;
+                            uint4 o = pk_ld_cg_v4(reinterpret_cast<const uint8_t*>(P.tp_h) + off);
+                            if (tp_ok) {
+                                uint4 w[8];
+#pragma unroll
+                                for (int r = 0; r < 8; ++r)
+                                    if (r < P.tp_n) w[r] = pk_ld_cg_v4(P.tp_slots + (size_t)r * P.tp_slot_stride + off);
+                                float sm[8];
+#pragma unroll
+                                for (int q = 0; q < 8; ++q) sm[q] = 0.0f;
+#pragma unroll
+                                for (int r = 0; r < 8; ++r) {
+                                    if (r < P.tp_n) {
+                                        sm[0] += bf16lo(w[r].x); sm[1] += bf16hi(w[r].x); sm[2] += bf16lo(w[r].y); sm[3] += bf16hi(w[r].y);
+                                        sm[4] += bf16lo(w[r].z); sm[5] += bf16hi(w[r].z); sm[6] += bf16lo(w[r].w); sm[7] += bf16hi(w[r].w);
+                                    }
+                                }
+                                // the rank-local products were rounded to bf16 when they were pushed; their sum is rounded once
+                                // more (the all-reduce of a bf16 buffer) and then added to the residual stream
+                                uint32_t sb[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) sb[q] = pack_bf16x2(sm[2 * q], sm[2 * q + 1]);
+                                const uint4 hw = o;
+                                o.x = pack_bf16x2(bf16lo(hw.x) + bf16lo(sb[0]), bf16hi(hw.x) + bf16hi(sb[0]));
+                                o.y = pack_bf16x2(bf16lo(hw.y) + bf16lo(sb[1]), bf16hi(hw.y) + bf16hi(sb[1]));
+                                o.z = pack_bf16x2(bf16lo(hw.z) + bf16lo(sb[2]), bf16hi(hw.z) + bf16hi(sb[2]));
+                                o.w = pack_bf16x2(bf16lo(hw.w) + bf16lo(sb[3]), bf16hi(hw.w) + bf16hi(sb[3]));
+                                __stcg(reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.tp_h) + off), o);
+                            }
+                            const float f[8] = {bf16lo(o.x), bf16hi(o.x), bf16lo(o.y), bf16hi(o.y), bf16lo(o.z), bf16hi(o.z), bf16lo(o.w), bf16hi(o.w)};
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) sq += f[q] * f[q];
+                        }
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // the 16 lanes of a token
+                        if (v < n_vec && (lane & 15) == 0) __stcg(P.tp_ssq + (size_t)j * P.ssq_stride + t, sq);
+                    }
+                }
+                // the barrier orders every thread's stores before thread 0, whose fences (cumulative) order them before its
+                // count; the CTA that completes h publishes the epoch: for the other CTAs' loads and, through the proxy
+                // fences, for their copy engines' reads of h
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) {
+                    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                    pk_fence_proxy_async();
+                    int old;
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(P.tp_state + 1), "r"(handled) : "memory");
+                    if (old + handled == red_tiles) {
+                        P.tp_state[1] = 0;  // ready for the next exchange
+                        asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(P.tp_state + 2), "r"(E) : "memory");
+                    }
+                }
+            }
+            if (etid == 0) pk_wait_epoch(P.tp_state + 2, E, P.tp_wait, P.err);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         chain_wait();
         // Row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into the packed
         // weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile sums of squares that
@@ -624,7 +770,15 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             } else {
                                 uint2 o;
                                 o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-                                if (valid) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
+                                if (P.tp_mode == 1) {
+                                    // this rank's block of every rank's exchange buffer (plain stores; peers over NVLink)
+                                    if (valid) {
+                                        const size_t off = ((size_t)t * P.N + n) * 2;
+#pragma unroll
+                                        for (int r = 0; r < 8; ++r)
+                                            if (r < P.tp_n) *reinterpret_cast<uint2*>(P.tp_dst[r] + off) = o;
+                                    }
+                                } else if (valid) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(P.Y) + (size_t)t * P.N + n) = o;
                                 const float s0 = bf16lo(o.x), s1 = bf16hi(o.x), s2 = bf16lo(o.y), s3 = bf16hi(o.y);
                                 sq = (s0 * s0 + s1 * s1) + (s2 * s2 + s3 * s3);
                             }
@@ -632,6 +786,26 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 sq = warp_sum(valid ? sq : 0.0f);
                                 if (lane == 0) P.ssq_out[(size_t)tile * P.ssq_stride + t] = sq;
                             }
+                        }
+                    }
+                }
+                if (do_fold && P.tp_mode == 1) {
+                    // The barrier orders every thread's slot stores before thread 0, which releases them (device scope) through
+                    // the launch's counter.  The CTA that completes the launch has thereby acquired every other CTA's stores;
+                    // ONE system-scope fence then orders all of them before the epoch it stores (relaxed) into every rank's
+                    // flag word for this rank - its own included: the consumer on this GPU waits for flags, not for the end of
+                    // this kernel.  (A system-scope fence costs microseconds: one per launch, not one per CTA or per flag.)
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (etid == 0) {
+                        int old;
+                        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(P.tp_state) : "memory");
+                        if (old == P.tp_expect - 1) {
+                            P.tp_state[0] = 0;  // ready for the next launch
+                            const int E = *reinterpret_cast<const volatile int*>(P.tp_pass) * P.tp_n_sites + P.tp_site + 1;
+                            asm volatile("fence.acq_rel.sys;" ::: "memory");
+#pragma unroll
+                            for (int r = 0; r < 8; ++r)
+                                if (r < P.tp_n) asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(P.tp_flag[r]), "r"(E) : "memory");
                         }
                     }
                 }
@@ -751,6 +925,15 @@ int linear_packed_cluster(int N, int K, int paired, int T) {
     return S;
 }
 
+// The outputs of a launch can be pushed to the ranks' exchange buffers when every finished tile leaves through the
+// vectorised (folding) epilogue: the aligned split, where a CTA holds exactly one segment of exactly one tile.
+bool linear_packed_can_push(int N, int K, int T) {
+    int nt, kbt;
+    pk_dims(N, K, 0, &nt, &kbt);
+    const int G = linear_packed_grid(N, K, 0, T);
+    return T <= TP_PUSH_MAX_T && G % nt == 0 && N % 4 == 0;
+}
+
 static int slots_for_grid(int nt, int kbt, long long G) {
     const long long U = (long long)nt * kbt;
     // a tile of kbt units is covered by at most ceil(kbt / floor(U/G)) + 1 consecutive CTA ranges
@@ -831,7 +1014,8 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
 
 jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     if (a.T <= 0 || a.N <= 0) return JSM_OK;
-    if (!a.X || !a.Wp || !a.Y) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: null pointer");
+    const bool tp_push = a.tp && a.tp->push, tp_reduce = a.tp && a.tp->reduce;
+    if (!a.X || !a.Wp || (!a.Y && !tp_push)) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: null pointer");
     if (a.K <= 0 || a.K % 8) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: K (%d) must be a positive multiple of 8", a.K);
     if (a.N % 4) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: N (%d) must be a multiple of 4", a.N);
     if (a.T > 256) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: at most 256 tokens per launch (%d)", a.T);
@@ -878,6 +1062,36 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         if (a.K / 64 < 2) P.pair_ok = 0;
     }
     const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
+    P.tp_mode = 0;
+    if (tp_push || tp_reduce) {
+        const TpFuse& f = *a.tp;
+        if (tp_push && tp_reduce) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: a launch either pushes or reduces");
+        if (f.n_ranks < 2 || f.n_ranks > 8 || f.rank < 0 || f.rank >= f.n_ranks || !f.pass || !f.state || f.wait_limit <= 0)
+            JSM_FAIL(JSM_INVALID_ARG, "linear_packed: tensor-parallel exchange of rank %d of %d", f.rank, f.n_ranks);
+        if (a.T > TP_PUSH_MAX_T) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: the fused exchange takes at most %d tokens (%d)", TP_PUSH_MAX_T, a.T);
+        P.tp_n = f.n_ranks; P.tp_rank = f.rank; P.tp_site = f.site; P.tp_n_sites = f.n_sites; P.tp_pass = f.pass; P.tp_state = f.state;
+        P.tp_wait = f.wait_limit;
+        for (int r = 0; r < 8; ++r) { P.tp_dst[r] = nullptr; P.tp_flag[r] = nullptr; }
+        P.tp_slots = nullptr; P.tp_slot_stride = 0; P.tp_flags = nullptr; P.tp_h = nullptr; P.tp_ssq = nullptr; P.tp_expect = 0;
+        if (tp_push) {
+            if (!linear_packed_can_push(a.N, a.K, a.T) || paired || a.out_f32 || a.bias || a.epilogue != LIN_NONE || a.ssq_out)
+                JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: this launch cannot push its outputs (plain bf16 projection on an aligned split only)");
+            for (int r = 0; r < f.n_ranks; ++r) {
+                if (!f.push_dst[r] || !f.push_flag[r]) JSM_FAIL(JSM_INVALID_ARG, "linear_packed: no exchange buffer for rank %d", r);
+                P.tp_dst[r] = reinterpret_cast<uint8_t*>(f.push_dst[r]);
+                P.tp_flag[r] = f.push_flag[r];
+            }
+            P.tp_expect = cluster > 1 ? grid : P.n_tiles;
+            P.tp_mode = 1;
+        } else {
+            if (!f.slots || !f.flags || !f.h || !f.ssq || a.ssq_in != f.ssq || a.ssq_in_tiles != (a.K + 127) / 128 ||
+                (a.x_row_stride > 0 && a.x_row_stride != a.K) || a.X != f.h)
+                JSM_FAIL(JSM_INVALID_ARG, "linear_packed: the reducing launch reads X = h with the statistics the reduction writes");
+            P.tp_slots = reinterpret_cast<const uint8_t*>(f.slots); P.tp_slot_stride = f.slot_stride; P.tp_flags = f.flags;
+            P.tp_h = reinterpret_cast<__nv_bfloat16*>(f.h); P.tp_ssq = f.ssq;
+            P.tp_mode = 2;
+        }
+    }
     // the cluster path lives in instantiations of its own: launches without a cluster run a kernel that carries none of it
     // (from 32 tokens on every launch runs the cluster-capable image, with cluster size 1 where no cluster forms: one
     // kernel image per token block keeps the once-per-launch tail code warm in the instruction cache)
@@ -1023,4 +1237,63 @@ extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_pack
         if (s != JSM_OK) return s;
     }
     return JSM_OK;
+}
+
+// ---- the fused exchange on its own (what the decoder runner composes; also how the protocol is tested on one GPU) ----
+static jsm_status device_workspace(PackedArgs& a) {
+    int dev = -1;
+    JSM_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: device index %d", dev);
+    std::lock_guard<std::mutex> lock(g_pk_mu);
+    const PkWorkspace& w = g_pk_ws[dev];
+    a.ws = w.ws; a.ws_floats = w.ws_floats; a.counters = w.counters; a.n_counters = w.n_counters;
+    return JSM_OK;
+}
+
+extern "C" jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens, int32_t* d_state,
+                                         int site, int n_sites, const void* d_X, const void* d_packed, int T, int N, int K, void* stream) {
+    if (!d_regions || !d_state || !d_X || !d_packed) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_push: null argument");
+    if (size < 2 || size > 8 || rank < 0 || rank >= size) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_push: rank %d of %d", rank, size);
+    if (T <= 0 || T > TP_PUSH_MAX_T || T > max_tokens) JSM_FAIL(JSM_SHAPE, "jsm_tp_linear_push: %d tokens (1..%d)", T, TP_PUSH_MAX_T);
+    if (!linear_packed_can_push(N, K, T)) JSM_FAIL(JSM_UNSUPPORTED, "jsm_tp_linear_push: a [%d x %d] projection over %d tokens has no aligned split", N, K, T);
+    TpFuse f;
+    f.n_ranks = size; f.rank = rank; f.pass = d_state; f.state = d_state + 1; f.site = site; f.n_sites = n_sites;
+    f.wait_limit = tp_wait_limit_cycles();
+    f.push = true;
+    const size_t off = tp_push_offset(which_buffer, max_tokens, N) + (size_t)rank * tp_slot_bytes(N);
+    for (int r = 0; r < size; ++r) {
+        if (!d_regions[r]) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_push: no region for rank %d", r);
+        f.push_dst[r] = static_cast<uint8_t*>(d_regions[r]) + off;
+        f.push_flag[r] = static_cast<int*>(d_regions[r]) + tp_push_flag_word() + rank;
+    }
+    PackedArgs a;
+    a.X = d_X; a.Wp = d_packed; a.bias = nullptr; a.epilogue = LIN_NONE; a.R = nullptr; a.Y = nullptr; a.out_f32 = false;
+    a.T = T; a.N = N; a.K = K; a.x_row_stride = 0; a.chained = false; a.tp = &f;
+    jsm_status s = device_workspace(a);
+    if (s != JSM_OK) return s;
+    return linear_packed_launch(a, as_stream(stream));
+}
+
+extern "C" jsm_status jsm_tp_linear_reduce(void* d_region, int rank, int size, int which_buffer, int max_tokens, int32_t* d_state, int site,
+                                           int n_sites, void* d_h, float* d_ssq, const void* d_packed, int epilogue, void* d_Y,
+                                           int out_dtype, int T, int N, int d, float eps, void* stream) {
+    if (!d_region || !d_state || !d_h || !d_ssq || !d_packed || !d_Y) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_reduce: null argument");
+    if (size < 2 || size > 8 || rank < 0 || rank >= size) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_reduce: rank %d of %d", rank, size);
+    if (T <= 0 || T > TP_PUSH_MAX_T || T > max_tokens) JSM_FAIL(JSM_SHAPE, "jsm_tp_linear_reduce: %d tokens (1..%d)", T, TP_PUSH_MAX_T);
+    if (out_dtype != JSM_BF16 && out_dtype != JSM_F32) JSM_FAIL(JSM_UNSUPPORTED, "jsm_tp_linear_reduce: out dtype %d", out_dtype);
+    TpFuse f;
+    f.n_ranks = size; f.rank = rank; f.pass = d_state; f.state = d_state + 1; f.site = site; f.n_sites = n_sites;
+    f.wait_limit = tp_wait_limit_cycles();
+    f.reduce = true;
+    f.slots = static_cast<const uint8_t*>(d_region) + tp_push_offset(which_buffer, max_tokens, d);
+    f.slot_stride = tp_slot_bytes(d);
+    f.flags = static_cast<const int*>(d_region) + tp_push_flag_word();
+    f.h = d_h; f.ssq = d_ssq;
+    PackedArgs a;
+    a.X = d_h; a.Wp = d_packed; a.bias = nullptr; a.epilogue = epilogue; a.R = nullptr; a.Y = d_Y; a.out_f32 = out_dtype == JSM_F32;
+    a.T = T; a.N = N; a.K = d; a.x_row_stride = 0; a.chained = false;
+    a.ssq_in = d_ssq; a.ssq_in_tiles = (d + 127) / 128; a.ssq_stride = T; a.eps = eps; a.tp = &f;
+    jsm_status s = device_workspace(a);
+    if (s != JSM_OK) return s;
+    return linear_packed_launch(a, as_stream(stream));
 }

@@ -23,8 +23,6 @@
 
 namespace jsm {
 
-size_t tp_region_bytes(int max_tokens, int d);
-size_t tp_buffer_offset(int which, int max_tokens, int d);
 jsm_status attn_decode_append_checked(const void* d_q, int64_t q_row_stride, const void* d_k_new, const void* d_v_new,
                                       int64_t kv_new_stride, void* d_pool, const int32_t* d_block_table, int max_pages,
                                       const int32_t* d_context_lens, int n_seqs, int Hq, int Hkv, int D, float scale,
@@ -79,6 +77,7 @@ struct jsm_model {
     void* tp_regions[8] = {nullptr};
     int32_t* tp_state = nullptr;
     bool tp_connected = false;
+    bool last_push = false;  // the last forward call exchanged by push (its final exchange is consumed by the logits projection)
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
     uint64_t weight_bytes = 0;
@@ -149,11 +148,18 @@ __global__ void fill_shard_kernel(__nv_bfloat16* dst, long long rows, long long 
 __global__ void fill_const_kernel(float* dst, long long n, float v) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] = v;
 }
-// pass: number of the forward pass (the epoch base of the tensor-parallel exchanges), bumped by the first kernel of a pass
+// pass: number of the forward pass (the epoch base of the tensor-parallel exchanges), bumped by the first kernel of a pass.
+// That kernel lets its dependents start only after the new number has reached memory: the fused exchanges of the pass
+// read it while their predecessors may still be running, so it must be in place before ANY later kernel of the chain can
+// become resident (a kernel starts only after every CTA of its predecessor has passed its chain_trigger).
 __global__ void iota_kernel(int32_t* pos, int32_t* seq_ids, int T, int seq, int pos0, int32_t* pass) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < T) { pos[i] = pos0 + i; seq_ids[i] = seq; }
-    if (i == 0 && pass) *pass = *pass + 1;
+    if (i == 0 && pass) {
+        *pass = *pass + 1;
+        __threadfence();
+    }
+    chain_trigger();
 }
 __global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = value; }
 // decode bookkeeping on the device so that a captured step can be replayed: the new token of
@@ -161,7 +167,6 @@ __global__ void set_ctx_kernel(int32_t* ctx, int seq, int value) { ctx[seq] = va
 // A sequence that already holds max_context tokens does not grow: its new token overwrites the last position (every
 // later access stays inside the sequence's pages and the rope table) and the error word records the overflow.
 __global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int batch, int32_t* pass, int max_context, int* err) {
-    chain_trigger();
     chain_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch) {
@@ -174,7 +179,11 @@ __global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int
         seq_ids[b] = b;
         ctx[b] = c + 1;
     }
-    if (b == 0 && pass) *pass = *pass + 1;
+    if (b == 0 && pass) {
+        *pass = *pass + 1;
+        __threadfence();
+    }
+    chain_trigger();  // after the pass number is in memory (see iota_kernel)
 }
 
 __device__ __forceinline__ float block_sum_256(float v, float* smem) {
@@ -335,7 +344,7 @@ struct RowStats {
 // One projection over packed weights for any number of tokens: chunks of 256 tokens, each streaming the weights once.
 static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_stride, const uint8_t* Wp, int N, int K, int epilogue,
                              const __nv_bfloat16* R, void* Y, bool out_f32, int T, cudaStream_t st, RowStats rs = RowStats(),
-                             int stats_stride = 0) {
+                             int stats_stride = 0, const TpFuse* tp = nullptr) {
     PackedArgs a;
     a.Wp = Wp; a.bias = nullptr; a.epilogue = epilogue; a.out_f32 = out_f32; a.N = N; a.K = K; a.x_row_stride = x_stride;
     a.ws = m->partial; a.ws_floats = m->ws_floats; a.counters = m->counters; a.n_counters = m->n_counters;
@@ -343,6 +352,7 @@ static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_s
     a.eps = m->c.norm_eps;
     a.ssq_in_tiles = rs.in_tiles;
     a.ssq_stride = stats_stride > 0 ? stats_stride : T;
+    a.tp = tp;  // fused exchanges come with at most TP_PUSH_MAX_T tokens: one chunk
     for (int t0 = 0; t0 < T; t0 += 256) {
         a.T = T - t0 < 256 ? T - t0 : 256;
         a.X = X + (long long)t0 * x_stride;
@@ -361,13 +371,47 @@ static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_s
 // statistics of the new h in `stats_out` for the projection that reads h next (which applies the RMSNorm itself).
 // Tensor parallel: the rank-local product goes through the all-reduce, then h += sum and xn = RMSNorm(h) (the gain is
 // folded into the next projection's weights) unless `normalise` is false.
+static TpFuse exchange_base(jsm_model* m, int site) {
+    TpFuse f;
+    f.n_ranks = m->c.tp_size; f.rank = m->c.tp_rank;
+    f.pass = m->tp_state; f.site = site; f.n_sites = 2 * m->c.n_layers;
+    f.state = m->tp_state + 4;
+    f.wait_limit = tp_wait_limit_cycles();
+    return f;
+}
+// The consumer side of a pushed exchange: the projection that reads rows [first, first + rows) of the residual stream
+// adds the ranks' slots of push buffer `which` to them first and writes their row statistics to `stats`.
+static TpFuse consume_exchange(jsm_model* m, int which, int site, float* stats, int first) {
+    TpFuse f = exchange_base(m, site);
+    const int d = m->c.d_model;
+    f.reduce = true;
+    f.slots = m->tp_region + tp_push_offset(which, m->max_tokens, d) + (size_t)first * d * sizeof(__nv_bfloat16);
+    f.slot_stride = tp_slot_bytes(d);
+    f.flags = reinterpret_cast<const int*>(m->tp_region) + tp_push_flag_word();
+    f.h = m->h + (size_t)first * d;
+    f.ssq = stats + first;
+    return f;
+}
+
 static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, const uint8_t* Wp, int T, int N, int K, float* stats_out,
-                                        bool normalise, int which, int site, cudaStream_t st) {
+                                        bool normalise, int which, int site, cudaStream_t st, bool push) {
     const int d = m->c.d_model;
     if (m->c.tp_size == 1) {
         RowStats rs;
         rs.out = stats_out;
         return run_linear(m, X, K, Wp, N, K, LIN_RESIDUAL, m->h, m->h, false, T, st, rs);
+    }
+    if (m->tp_connected && push) {
+        // the projection stores its product straight into this rank's slot of every rank's push buffer and releases the
+        // exchange's epoch; the projection that reads h next adds the slots to h in its prologue (consume_exchange)
+        TpFuse f = exchange_base(m, site);
+        f.push = true;
+        const size_t off = tp_push_offset(which, m->max_tokens, d) + (size_t)m->c.tp_rank * tp_slot_bytes(d);
+        for (int r = 0; r < m->c.tp_size; ++r) {
+            f.push_dst[r] = static_cast<uint8_t*>(m->tp_regions[r]) + off;
+            f.push_flag[r] = static_cast<int*>(m->tp_regions[r]) + tp_push_flag_word() + m->c.tp_rank;
+        }
+        return run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, nullptr, false, T, st, RowStats(), 0, &f);
     }
     if (m->tp_connected) {
         // the rank-local product goes into this call site's exchange buffer; one kernel then sums the ranks' buffers
@@ -394,21 +438,31 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
     const int d = c.d_model, D = c.head_dim;
     const bool tp = c.tp_size > 1;
     const int d_tiles = (d + 127) / 128;
+    // few tokens (every decode step): the two exchanges of a layer are fused into the projections around them and the
+    // step runs the one-GPU pipeline (un-normalised h + row statistics); otherwise the exchange kernel and a normalised copy
+    const bool push = tp && m->tp_connected && T <= TP_PUSH_MAX_T && linear_packed_can_push(d, m->Hq_l * D, T) &&
+                      linear_packed_can_push(d, m->ffn_l, T);
+    m->last_push = push;
+    const bool stats = !tp || push;  // h carries row statistics instead of a normalised copy
     jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
     if (s != JSM_OK) return s;
-    if (tp) {
+    if (!stats) {
         JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, nullptr,
                                       c.norm_eps, m->xn, d));
     } else {
         JSM_CUDA_CHECK(launch_chained(row_ssq_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)m->h, m->ssq0, d));
     }
     JSM_LAUNCH_CHECK();
-    const __nv_bfloat16* x_in = tp ? m->xn : m->h;  // what the projections after a norm read
+    const __nv_bfloat16* x_in = stats ? m->h : m->xn;  // what the projections after a norm read
     const float scale = 1.0f / sqrtf((float)D);
     RowStats after_down;  // statistics of h as the previous layer (or the embedding) left it
-    if (!tp) { after_down.in = m->ssq0; after_down.in_tiles = 1; }
+    if (stats) { after_down.in = m->ssq0; after_down.in_tiles = 1; }
     for (int l = 0; l < c.n_layers; ++l) {
         LayerW& L = m->layers[l];
+        if (push && l > 0) {
+            const TpFuse f = consume_exchange(m, 1, 2 * (l - 1) + 1, m->ssq_b, 0);  // the previous layer's down projection
+            s = run_linear(m, x_in, d, L.wqkv, m->qkv_dim, d, LIN_NONE, nullptr, m->qkv, false, T, st, after_down, 0, &f);
+        } else
         s = run_linear(m, x_in, d, L.wqkv, m->qkv_dim, d, LIN_NONE, nullptr, m->qkv, false, T, st, after_down);
         if (s != JSM_OK) return s;
         const __nv_bfloat16* kk = m->qkv + (long long)m->Hq_l * D;
@@ -433,15 +487,19 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
                                      m->qkv_dim, m->qkv_dim, (long long)m->Hq_l * D, 0);
         }
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, 0, 2 * l, st);
+        s = project_into_residual(m, m->attn, L.wo, T, d, m->Hq_l * D, m->ssq_a, true, 0, 2 * l, st, push);
         if (s != JSM_OK) return s;
         RowStats after_wo;
-        if (!tp) { after_wo.in = m->ssq_a; after_wo.in_tiles = d_tiles; }
+        if (stats) { after_wo.in = m->ssq_a; after_wo.in_tiles = d_tiles; }
+        if (push) {
+            const TpFuse f = consume_exchange(m, 0, 2 * l, m->ssq_a, 0);
+            s = run_linear(m, x_in, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st, after_wo, 0, &f);
+        } else
         s = run_linear(m, x_in, d, L.wgu, m->ffn_l, d, LIN_SILU_MUL, nullptr, m->act, false, T, st, after_wo);
         if (s != JSM_OK) return s;
-        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, 1, 2 * l + 1, st);
+        s = project_into_residual(m, m->act, L.wdown, T, d, m->ffn_l, m->ssq_b, true, 1, 2 * l + 1, st, push);
         if (s != JSM_OK) return s;
-        if (!tp) { after_down.in = m->ssq_b; after_down.in_tiles = d_tiles; }
+        if (stats) { after_down.in = m->ssq_b; after_down.in_tiles = d_tiles; }
     }
     (void)prefill_seq;
     return JSM_OK;
@@ -452,10 +510,13 @@ static jsm_status logits_and_argmax(jsm_model* m, int first, int rows, int T, in
     float* lg = d_logits ? d_logits : m->logits;
     const int d = m->c.d_model;
     const bool tp = m->c.tp_size > 1;
+    const bool push = tp && m->last_push;  // the forward call that just ran pushed its exchanges: the last one is still to be consumed
     RowStats rs;
-    if (!tp) { rs.in = m->ssq_b + first; rs.in_tiles = (d + 127) / 128; }
-    const __nv_bfloat16* x = (tp ? m->xn : m->h) + (long long)first * d;
-    jsm_status s = run_linear(m, x, d, m->lm_head, m->c.vocab, d, LIN_NONE, nullptr, lg, true, rows, st, rs, T);
+    if (!tp || push) { rs.in = m->ssq_b + first; rs.in_tiles = (d + 127) / 128; }
+    const __nv_bfloat16* x = ((tp && !push) ? m->xn : m->h) + (long long)first * d;
+    TpFuse f;
+    if (push) f = consume_exchange(m, 1, 2 * (m->c.n_layers - 1) + 1, m->ssq_b, first);
+    jsm_status s = run_linear(m, x, d, m->lm_head, m->c.vocab, d, LIN_NONE, nullptr, lg, true, rows, st, rs, T, push ? &f : nullptr);
     if (s != JSM_OK) return s;
     if (d_next) {
         JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
@@ -606,8 +667,8 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     if (c.tp_size > 1) {
         const size_t rb = tp_region_bytes(m->max_tokens, d);
         JSM_TRY(dev_alloc(m, &m->tp_region, rb));
-        JSM_TRY(dev_alloc(m, &m->tp_state, (size_t)2));
-        if (cudaMemset(m->tp_region, 0, rb) != cudaSuccess || cudaMemset(m->tp_state, 0, 2 * sizeof(int32_t)) != cudaSuccess) {
+        JSM_TRY(dev_alloc(m, &m->tp_state, (size_t)128));  // [0] forward passes; [4..] state of the fused exchanges (a counter, tile epochs)
+        if (cudaMemset(m->tp_region, 0, rb) != cudaSuccess || cudaMemset(m->tp_state, 0, 128 * sizeof(int32_t)) != cudaSuccess) {
             jsm_llama_destroy(m);
             JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset of the exchange region failed");
         }

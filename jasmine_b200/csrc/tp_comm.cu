@@ -20,7 +20,24 @@
 // A wait that runs out (a peer that never arrives) records an error code and the kernel returns without touching h;
 // the host sees it through jsm_check_device_errors.  No in-switch reduction and no multicast objects are involved:
 // a rank that leaves cannot fault its peers' GPUs.
+//
+// Launches of at most TP_PUSH_MAX_T tokens (every decode step) do not run this kernel at all: the exchange is fused
+// into the projections on either side of it (linear_packed.cu, TpFuse).
+//   push    The projection whose output is to be summed (attention output, FFN down) stores its finished bf16 tiles
+//           straight into its rank's SLOT of every rank's push buffer - plain peer stores from the epilogue, no local copy
+//           first - and the CTA that completes the launch releases the exchange's epoch to every peer's push flag.
+//   reduce  The projection that reads the residual stream next (gate/up, the next layer's qkv, lm_head) becomes
+//           resident while its predecessor still runs and streams its weights; one CTA per 128-column tile of h waits
+//           for the peers' flags, adds the slots in rank order to h - LOCAL loads only: the data crossed NVLink once, as
+//           stores, off the critical path of the consumer - and leaves h and the tile's sums of squares behind; all CTAs
+//           then read h as their token operand with the RMSNorm applied as a row scale.
+// One NVLink traversal (store + flag) lies between the two projections instead of signal -> wait -> remote load, and no
+// kernel launch.  Region layout: [flags | buffer A | buffer B | push buffer 0: 8 slots | push buffer 1: 8 slots]; the
+// push flags are the words TP_PUSH_FLAG_WORD.. of the flag block.  The same two-buffer argument holds: a rank pushes
+// into buffer 0 again only after it has consumed the exchange over buffer 1, which every peer pushed only after it had
+// finished reading buffer 0.
 #include "tc_utils.cuh"
+#include "linear_bf16.cuh"
 #include <math.h>
 
 namespace jsm {
@@ -74,7 +91,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
         if (r != a.rank) {
             const int* flag = reinterpret_cast<const int*>(a.regions[a.rank]) + r;
             const long long t0 = clock64();
-            while (ld_acquire_sys(flag) < E) {
+            while ((int)(ld_acquire_sys(flag) - E) < 0) {  // wrap-safe: epochs only ever grow
                 if (clock64() - t0 > a.wait_limit) {
                     ok_s = 0;
                     if (a.err) atomicCAS(a.err, 0, TP_TIMEOUT_CODE);
@@ -154,8 +171,18 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
     }
 }
 
-size_t tp_region_bytes(int max_tokens, int d) { return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16); }
+constexpr int TP_PUSH_FLAG_WORD = 16;  // first push flag inside the flag block (one word per source rank)
+size_t tp_slot_bytes(int d) { return (size_t)TP_PUSH_MAX_T * d * sizeof(__nv_bfloat16); }
+size_t tp_region_bytes(int max_tokens, int d) {
+    return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + 2 * (size_t)TP_MAX_RANKS * tp_slot_bytes(d);
+}
 size_t tp_buffer_offset(int which, int max_tokens, int d) { return TP_FLAG_BYTES + (size_t)(which & 1) * max_tokens * d * sizeof(__nv_bfloat16); }
+// slot 0 of push buffer `which`; rank r's slot follows at r * tp_slot_bytes(d)
+size_t tp_push_offset(int which, int max_tokens, int d) {
+    return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + (size_t)(which & 1) * TP_MAX_RANKS * tp_slot_bytes(d);
+}
+int tp_push_flag_word() { return TP_PUSH_FLAG_WORD; }
+long long tp_wait_limit_cycles() { return g_tp_wait_limit_cycles; }
 
 jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, const int* pass, int site,
                                         int n_sites, void* h, void* xn, float eps, int T, int d, cudaStream_t st) {

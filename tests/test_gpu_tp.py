@@ -85,3 +85,81 @@ def test_exchange_gives_up_when_a_peer_never_arrives():
         assert int(torch.ones(4, device="cuda").sum()) == 4
     finally:
         jb.check(jb.lib().jsm_tp_set_wait_limit_ms(1000))
+
+
+# ---- the exchange fused into the projections (push from the producer's epilogue, reduce in the consumer's prologue) ----
+def _rms_rows(h, eps):
+    return h.float() / torch.sqrt((h.float() ** 2).mean(dim=1, keepdim=True) + eps)
+
+
+@pytest.mark.parametrize("n,T,d,K,N2", [(2, 8, 4096, 512, 1536), (8, 8, 4096, 1376, 2752), (4, 33, 1024, 256, 512),
+                                        (3, 1, 256, 512, 256), (2, 64, 512, 1024, 384)])
+def test_fused_exchange_push_then_reduce(n, T, d, K, N2):
+    """All "ranks" are regions of one device.  First every rank's producer projection runs (it stores its tiles into its
+    slot of every region and releases its flag), then every rank's consumer projection (it finds all flags set, adds the
+    slots to h and projects the normalised h): no kernel ever waits for another.  Three exchanges: buffers 0, 1, 0."""
+    max_tokens = 64
+    regions, ptrs = make_regions(n, max_tokens, d)
+    states = [torch.zeros(80, dtype=torch.int32, device="cuda") for _ in range(n)]
+    eps = 1e-5
+    W2 = dev(cases.normal((N2, d), 930, 0, 0.05), torch.bfloat16)
+    W2p = jb.linear_pack(W2, N2)
+    h = dev(cases.normal((T, d), 931, 0), torch.bfloat16)
+    d_tiles = (d + 127) // 128
+    for call in range(3):
+        which, site = call % 2, call % 2
+        Xs = [dev(cases.normal((T, K), 932 + call, r), torch.bfloat16) for r in range(n)]
+        Ws = [dev(cases.normal((d, K), 940 + call, r, 0.05), torch.bfloat16) for r in range(n)]
+        packed = [jb.linear_pack(w, d) for w in Ws]
+        for r in range(n):
+            states[r][0] = call // 2          # the forward pass: epochs 1, 2, 3
+            jb.check(jb.lib().jsm_tp_linear_push(ptrs, r, n, which, max_tokens, states[r].data_ptr(), site, 2, Xs[r].data_ptr(),
+                                                 packed[r].data_ptr(), T, d, K, jb.stream_ptr()))
+        jb.check_device_errors()
+        total = torch.zeros(T, d, device="cuda")
+        for r in range(n):                    # rank order, each product rounded to bf16 as it was pushed
+            total = total + (Xs[r].float() @ Ws[r].float().t()).to(torch.bfloat16).float()
+        want_h = (h.float() + total.to(torch.bfloat16).float()).to(torch.bfloat16)
+        want_y = _rms_rows(want_h, eps) @ W2.float().t()
+        outs = []
+        for r in range(n):
+            hr = h.clone()
+            ssq = torch.zeros(d_tiles, T, device="cuda")
+            y = torch.empty(T, N2, device="cuda")
+            jb.check(jb.lib().jsm_tp_linear_reduce(regions[r].data_ptr(), r, n, which, max_tokens, states[r].data_ptr(), site, 2,
+                                                   hr.data_ptr(), ssq.data_ptr(), W2p.data_ptr(), 0, y.data_ptr(), jb.F32, T, N2, d,
+                                                   eps, jb.stream_ptr()))
+            outs.append((hr, ssq, y))
+        jb.check_device_errors()
+        for r, (hr, ssq, y) in enumerate(outs):
+            assert torch.equal(hr, outs[0][0]), f"rank {r}: h differs from rank 0"
+            assert torch.equal(y, outs[0][2]), f"rank {r}: projection differs from rank 0"
+            assert_close(host(hr), host(want_h), 1e-2, f"h of rank {r}, exchange {call}")
+            assert_close(host(ssq.sum(dim=0)), host((hr.float() ** 2).sum(dim=1)), 1e-5, f"row statistics of rank {r}")
+            assert_close(host(y), host(want_y), 2e-2, f"projection of the normalised h, rank {r}, exchange {call}")
+        h = outs[0][0]
+
+
+def test_fused_exchange_gives_up_when_a_peer_never_pushes():
+    """The consumer of an exchange whose peer never released its flag: the wait runs out after the (shortened) limit,
+    h stays as it was, the host reads JSM_TIMEOUT and the device still answers."""
+    n, T, d, N2, max_tokens = 2, 4, 512, 256, 64
+    regions, ptrs = make_regions(n, max_tokens, d)
+    state = torch.zeros(80, dtype=torch.int32, device="cuda")   # epoch 1 is expected; no flag was ever released
+    W2p = jb.linear_pack(dev(cases.normal((N2, d), 950, 0, 0.05), torch.bfloat16), N2)
+    h = dev(cases.normal((T, d), 951, 0), torch.bfloat16)
+    before = h.clone()
+    ssq = torch.zeros(4, T, device="cuda")
+    y = torch.empty(T, N2, device="cuda")
+    jb.check(jb.lib().jsm_tp_set_wait_limit_ms(20))
+    try:
+        jb.check(jb.lib().jsm_tp_linear_reduce(regions[0].data_ptr(), 0, n, 0, max_tokens, state.data_ptr(), 0, 1, h.data_ptr(),
+                                               ssq.data_ptr(), W2p.data_ptr(), 0, y.data_ptr(), jb.F32, T, N2, d, 1e-5, jb.stream_ptr()))
+        with pytest.raises(jb.JsmError) as e:
+            jb.check_device_errors()
+        assert e.value.status == jb.TIMEOUT
+        assert torch.equal(h, before)
+        jb.check_device_errors()
+        assert int(torch.ones(4, device="cuda").sum()) == 4
+    finally:
+        jb.check(jb.lib().jsm_tp_set_wait_limit_ms(1000))

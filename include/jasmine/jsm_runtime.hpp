@@ -13,6 +13,13 @@
 
 #include "jasmine_b200.h"
 
+// Defined by these headers and not by the reference's: code that wants the extensions below the reference's API
+// (cached generation, save / load) can test for it and still compile against either set of headers.
+#define JASMINE_B200 1
+
+#include <istream>
+#include <ostream>
+
 namespace jsm_rt {
 
 // The reference reports errors with exceptions only: std::invalid_argument for a dot-product shape
@@ -65,6 +72,37 @@ struct builder {
         prog.push_back(jsm_instr{code, 0, v});
     }
 };
+
+// Flat binary record of one tensor: "JSMT", rows, cols (int32), then rows * cols floats in row-major order.
+// The reference has no serialisation (mat_t.hpp:322-336 prints text only).
+template <typename mat>
+void save_tensor(std::ostream& os, const mat& m) {
+    const char magic[4] = {'J', 'S', 'M', 'T'};
+    const int32_t dims[2] = {(int32_t)m.row_num(), (int32_t)m.col_num()};
+    os.write(magic, 4);
+    os.write(reinterpret_cast<const char*>(dims), sizeof(dims));
+    std::vector<float> v((size_t)dims[0] * dims[1]);
+    for (int i = 0; i < dims[0]; ++i)
+        for (int j = 0; j < dims[1]; ++j) v[(size_t)i * dims[1] + j] = (float)m(i, j);
+    os.write(reinterpret_cast<const char*>(v.data()), (std::streamsize)(v.size() * sizeof(float)));
+    if (!os) throw std::runtime_error("save: write failed");
+}
+// resize: a tensor that the net creates lazily (the gain of a layer norm that never ran) takes the record's shape
+template <typename mat>
+void load_tensor(std::istream& is, mat& m, bool resize = false) {
+    char magic[4];
+    int32_t dims[2];
+    is.read(magic, 4);
+    is.read(reinterpret_cast<char*>(dims), sizeof(dims));
+    if (!is || std::memcmp(magic, "JSMT", 4) != 0) throw std::runtime_error("load: not a tensor record");
+    if (resize && (dims[0] != m.row_num() || dims[1] != m.col_num())) m = mat(dims[0], dims[1]);
+    if (dims[0] != m.row_num() || dims[1] != m.col_num()) throw std::runtime_error("load: tensor shape does not match the net");
+    std::vector<float> v((size_t)dims[0] * dims[1]);
+    is.read(reinterpret_cast<char*>(v.data()), (std::streamsize)(v.size() * sizeof(float)));
+    if (!is) throw std::runtime_error("load: truncated tensor");
+    for (int i = 0; i < dims[0]; ++i)
+        for (int j = 0; j < dims[1]; ++j) m(i, j) = v[(size_t)i * dims[1] + j];
+}
 
 }  // namespace jsm_rt
 

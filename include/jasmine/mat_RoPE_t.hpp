@@ -105,14 +105,26 @@ public:
     void set_param(int const& d_model) { m_d = d_model; m_table.reset(); m_table_pos = 0; }
 
     // x: [d_model, seq_len]; every pair of rows (2i, 2i+1) of column m is rotated by the block of (i, m)
-    mat_t<val_type> forward(input_type const& x) {
+    mat_t<val_type> forward(input_type const& x) { return forward(x, 0); }
+    // the same for columns that sit at positions first_position, first_position + 1, ... of a longer sequence (generation
+    // with cached keys and values feeds the new columns only); not in the reference, whose columns always start at 0
+    mat_t<val_type> forward(input_type const& x, int first_position) {
         const int seq_len = x.col_num(), d_model = x.row_num();
         if (d_model != m_d) throw std::runtime_error("Input dimension does not match RoPE dimension");
-        need_table(seq_len);
+        need_table(first_position + seq_len);
         mat_t<val_type> xt = x.view().t().clone();  // token-major: the pair of a token is adjacent in memory
         mat_t<val_type> yt(seq_len, d_model);
+        std::shared_ptr<jsm_rt::device_buffer> pos;
+        if (first_position != 0) {
+            std::vector<int32_t> h(seq_len);
+            for (int i = 0; i < seq_len; ++i) h[i] = first_position + i;
+            pos = std::make_shared<jsm_rt::device_buffer>(sizeof(int32_t) * (size_t)seq_len);
+            jsm_rt::check(jsm_upload(pos->p, h.data(), sizeof(int32_t) * (size_t)seq_len, jsm_rt::stream()));
+            jsm_rt::check(jsm_stream_sync(jsm_rt::stream()));  // h leaves scope
+        }
         jsm_rt::check(jsm_rope_apply(xt.jsm_device().data, yt.jsm_device_out().data, JSM_F32, static_cast<const float*>(m_table->p), d_model, 1,
-                                     nullptr, seq_len, jsm_rt::stream()));
+                                     pos ? static_cast<const int32_t*>(pos->p) : nullptr, seq_len, jsm_rt::stream()));
+        if (pos) jsm_rt::check(jsm_stream_sync(jsm_rt::stream()));  // the position buffer is released on return
         return yt.t().clone();
     }
     template <typename>

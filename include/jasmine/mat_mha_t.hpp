@@ -33,6 +33,13 @@ inline jsm_mat columns(const jsm_mat& x, int c0, int n) {
     t.cols = n;
     return t;
 }
+// rows [r0, r0+n) of a matrix window
+inline jsm_mat rows(const jsm_mat& x, int r0, int n) {
+    jsm_mat t = x;
+    t.data = static_cast<char*>(x.data) + (int64_t)r0 * x.row_stride * (int64_t)sizeof(float);
+    t.rows = n;
+    return t;
+}
 inline jsm_mat transposed(const jsm_mat& x) {
     jsm_mat t = x;
     t.rows = x.cols; t.cols = x.rows; t.row_stride = x.col_stride; t.col_stride = x.row_stride;
@@ -95,6 +102,8 @@ public:
     }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "mat_head_gen_t"; }
     void step() {}
+    void save(std::ostream& os) const { m_q_net.save(os); m_k_net.save(os); m_v_net.save(os); }
+    void load(std::istream& is) { m_q_net.load(is); m_k_net.load(is); m_v_net.load(is); }
 
 private:
     template <typename any_q, typename any_kv>
@@ -152,6 +161,44 @@ private:
     weight_net_t<mat_t<val_type>, updator_type> m_output_proj;
     int m_num_heads, m_d_model, m_d_head;
     bool m_mask;
+    // Keys and values of the positions seen so far, token-major [capacity, d_model], resident on the device.
+    // Self attention: grown by forward_cached.  Cross attention: computed once from the encoder output (set_memory).
+    mat_t<val_type> m_k_cache, m_v_cache;
+    int m_cached = 0;
+
+    void reserve_cache(int positions) {
+        if (positions <= m_k_cache.row_num() && m_k_cache.col_num() == m_d_model) return;
+        const int cap = std::max(positions, std::max(64, 2 * m_k_cache.row_num()));
+        mat_t<val_type> k(cap, m_d_model), v(cap, m_d_model);
+        if (m_cached > 0) {
+            k.view(0, 0, m_cached, m_d_model).assign(m_k_cache.view(0, 0, m_cached, m_d_model));
+            v.view(0, 0, m_cached, m_d_model).assign(m_v_cache.view(0, 0, m_cached, m_d_model));
+        }
+        m_k_cache = std::move(k);
+        m_v_cache = std::move(v);
+    }
+    // keys and values of the columns of x (token-major rows) into rows [at, at + columns) of the cache
+    void project_kv(const jsm_mat& X, int at) {
+        const jsm_mat K = jsm_attn::rows(m_k_cache.jsm_device_inout(), at, X.cols), V = jsm_attn::rows(m_v_cache.jsm_device_inout(), at, X.cols);
+        for (int h = 0; h < m_num_heads; ++h) {
+            jsm_attn::project(m_heads[h].k_net(), jsm_attn::token_major_rows(X, h * m_d_head, m_d_head), jsm_attn::columns(K, h * m_d_head, m_d_head));
+            jsm_attn::project(m_heads[h].v_net(), jsm_attn::token_major_rows(X, h * m_d_head, m_d_head), jsm_attn::columns(V, h * m_d_head, m_d_head));
+        }
+    }
+    // queries of the columns of x against the first n_keys cached positions, then the output projection
+    mat_t<val_type> attend_cached(const jsm_mat& Xq, int n_keys, bool mask) {
+        const int Sq = Xq.cols, d = m_d_model, dh = m_d_head;
+        mat_t<val_type> q(Sq, d), att(Sq, d);
+        const jsm_mat Q = q.jsm_device_out();
+        for (int h = 0; h < m_num_heads; ++h)
+            jsm_attn::project(m_heads[h].q_net(), jsm_attn::token_major_rows(Xq, h * dh, dh), jsm_attn::columns(Q, h * dh, dh));
+        jsm_rt::check(jsm_attn_prefill(Q.data, m_k_cache.jsm_device().data, m_v_cache.jsm_device().data, att.jsm_device_out().data, JSM_F32, 1, Sq,
+                                       n_keys, m_num_heads, m_num_heads, dh, mask ? 1 : 0, 1.0f / std::sqrt((float)dh), nullptr, 1, jsm_rt::stream()));
+        mat_t<val_type> out(d, Sq);
+        jsm_mat Wo = m_output_proj.jsm_weight().jsm_device(), Bo = m_output_proj.jsm_bias().jsm_device();
+        jsm_rt::check(jsm_dot_f32(Wo, jsm_attn::transposed(att.jsm_device()), &Bo, 0, nullptr, out.jsm_device_out(), jsm_rt::stream()));
+        return out;
+    }
 
 public:
     mat_mha_t(int num_heads = 1, int d_model = 1, bool mask = false, int seq_len = 1)
@@ -180,10 +227,50 @@ public:
         return attend(input, encoder_input, false);
     }
 
+    // ---- generation against cached keys and values --------------------------------------------------------------
+    // The reference generates by recomputing the whole prefix for every new position (transformer_test.hpp:227-241).
+    // forward_cached(x_new) returns what forward(prefix + x_new) returns in its LAST x_new.col_num() columns (the causal
+    // prefix property the reference demonstrates, transformer_test.hpp:246-282), but projects only the new columns and
+    // attends over the cached keys and values of the earlier ones.  Needs a masked (causal) attention layer.
+    void reset_cache() { m_cached = 0; }
+    int cached_positions() const { return m_cached; }
+    mat_t<val_type> forward_cached(const input_type& x_new) {
+        if (x_new.row_num() != m_d_model) throw std::runtime_error("Input row dimension must match d_model");
+        if (!m_mask) throw std::runtime_error("forward_cached needs a masked (causal) attention layer");
+        const jsm_mat X = x_new.jsm_device();
+        reserve_cache(m_cached + X.cols);
+        project_kv(X, m_cached);
+        m_cached += X.cols;
+        return attend_cached(X, m_cached, true);  // query i of the new block sees keys 0 .. m_cached - X.cols + i
+    }
+    // Cross attention against a fixed memory (the encoder output): its keys and values are projected ONCE here instead
+    // of at every decoding step (reference: :293-322 projects them in every forward).
+    void set_memory(const input_type& encoder_input) {
+        if (encoder_input.row_num() != m_d_model) throw std::runtime_error("Encoder input row dimension must match d_model");
+        m_cached = 0;
+        const jsm_mat X = encoder_input.jsm_device();
+        reserve_cache(X.cols);
+        project_kv(X, 0);
+        m_cached = X.cols;
+    }
+    mat_t<val_type> forward_memory(const input_type& input) {
+        if (input.row_num() != m_d_model) throw std::runtime_error("Input row dimension must match d_model");
+        if (m_cached == 0) throw std::runtime_error("Encoder output not set for cross attention");
+        return attend_cached(input.jsm_device(), m_cached, false);
+    }
+
     template <typename... upr_arg_types>
     void set_updator(upr_arg_types&&... args) {
         for (auto& h : m_heads) h.set_updator(args...);
         m_output_proj.set_updator(args...);
+    }
+    void save(std::ostream& os) const {
+        for (auto const& h : m_heads) h.save(os);
+        m_output_proj.save(os);
+    }
+    void load(std::istream& is) {
+        for (auto& h : m_heads) h.load(is);
+        m_output_proj.load(is);
     }
     // order: every head q(W,b) k(W,b) v(W,b), then the output projection (reference: :384-392)
     template <typename init_type>
@@ -240,6 +327,12 @@ public:
         if (m_encoder_output == nullptr) throw std::runtime_error("Encoder output not set for cross attention");
         return base_type::forward(input, *m_encoder_output);
     }
+    // the static cross cache: keys and values of the stored encoder output, projected once per encoder pass
+    void refresh_memory() {
+        if (m_encoder_output == nullptr) throw std::runtime_error("Encoder output not set for cross attention");
+        base_type::set_memory(*m_encoder_output);
+    }
+    mat_t<val_type> forward_cached(const input_type& input) { return base_type::forward_memory(input); }
     void step() {}
 };
 

@@ -65,6 +65,9 @@ public:
     // device windows for fused callers (attention packs the per-head projections itself)
     const mat_t<val_type>& jsm_weight() const { return m_weight; }
     const mat_t<val_type>& jsm_bias() const { return m_bias; }
+    // flat binary checkpoint (not in the reference, which cannot store a net): W then b
+    void save(std::ostream& os) const { jsm_rt::save_tensor(os, m_weight); jsm_rt::save_tensor(os, m_bias); }
+    void load(std::istream& is) { jsm_rt::load_tensor(is, m_weight); jsm_rt::load_tensor(is, m_bias); }
 };
 
 namespace jsm_net {
@@ -84,6 +87,8 @@ class sigmoid_net_t {
 public:
     using val_type = typename input_type::ele_type;
     sigmoid_net_t() = default;
+    void save(std::ostream&) const {}
+    void load(std::istream&) {}
     mat_t<val_type> forward(const input_type& input) { return jsm_net::unary<val_type>(input, JSM_OP_SIGMOID); }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "sigmoid_net_t"; }
     template <typename init_type>
@@ -97,6 +102,8 @@ class relu_net_t {
 public:
     using val_type = typename input_type::ele_type;
     relu_net_t() = default;
+    void save(std::ostream&) const {}
+    void load(std::istream&) {}
     mat_t<val_type> forward(const input_type& input) { return jsm_net::unary<val_type>(input, JSM_OP_RELU); }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "relu_net_t"; }
     template <typename init_type>
@@ -143,6 +150,18 @@ public:
         init_matrix<init_type>(m_beta);
     }
     void step() {}
+    // gain and bias exist from the first forward on: a flag says whether the record holds them
+    void save(std::ostream& os) const {
+        const int32_t present = m_gama.valid() ? 1 : 0;
+        os.write(reinterpret_cast<const char*>(&present), 4);
+        if (present) { jsm_rt::save_tensor(os, m_gama); jsm_rt::save_tensor(os, m_beta); }
+    }
+    void load(std::istream& is) {
+        int32_t present = 0;
+        is.read(reinterpret_cast<char*>(&present), 4);
+        if (!is) throw std::runtime_error("load: truncated layer norm record");
+        if (present) { jsm_rt::load_tensor(is, m_gama, true); jsm_rt::load_tensor(is, m_beta, true); }
+    }
 };
 
 template <typename input_type>
@@ -159,6 +178,8 @@ public:
     template <typename init_type>
     void init_weight() {}
     void step() {}
+    void save(std::ostream&) const {}
+    void load(std::istream&) {}
 };
 
 // f(x) + x (reference: mat_net_t.hpp:304-364)
@@ -186,6 +207,8 @@ public:
     template <size_t... nums>
     decltype(auto) get() const { return m_net.template get<nums...>(); }
     void step() { m_net.step(); }
+    void save(std::ostream& os) const { m_net.save(os); }
+    void load(std::istream& is) { m_net.load(is); }
 };
 
 // a tuple of nets applied left to right (reference: mat_net_t.hpp:366-488)
@@ -224,6 +247,13 @@ public:
     }
     void step() {
         std::apply([](auto&... nets) { ((nets.step()), ...); }, m_nets);
+    }
+    // the members' records in tuple order
+    void save(std::ostream& os) const {
+        std::apply([&os](auto const&... nets) { ((nets.save(os)), ...); }, m_nets);
+    }
+    void load(std::istream& is) {
+        std::apply([&is](auto&... nets) { ((nets.load(is)), ...); }, m_nets);
     }
     std::string net_type(int const& indent = 0) const {
         std::stringstream ss;

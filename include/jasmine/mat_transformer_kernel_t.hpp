@@ -60,6 +60,23 @@ public:
         for (auto& layer : m_layers) input = layer.forward(input);
         return input;
     }
+    // Generation with cached keys and values for a causal (decoder-only) stack: the output columns of the new input
+    // columns, equal to the last columns of forward(whole prefix) - which is how the reference generates
+    // (transformer_test.hpp:227-241) - at the cost of the new columns only.  Norms and feed-forward act per column.
+    void reset_cache() {
+        for (size_t i = 0; i < size(); ++i) get_mha(i).reset_cache();
+    }
+    mat_t<val_type> forward_cached(mat_t<val_type> x) {
+        for (size_t i = 0; i < size(); ++i) {
+            mat_t<val_type> a = get_mha(i).forward_cached(x);
+            x = get_mha_norm(i).forward((a + x).clone());
+            mat_t<val_type> f = get_ffn(i).forward(x);
+            x = get_ffn_norm(i).forward((((f > 0) * f) + x).clone());
+        }
+        return x;
+    }
+    void save(std::ostream& os) const { for (auto const& l : m_layers) l.save(os); }
+    void load(std::istream& is) { for (auto& l : m_layers) l.load(is); }
     auto& get_mha(int const& i) { return m_layers[i].template get<0, 0>().base_net(); }
     auto& get_mha_norm(int const& i) { return m_layers[i].template get<0, 1>(); }
     auto& get_ffn(int const& i) { return m_layers[i].template get<1, 0, 0>(); }
@@ -105,6 +122,7 @@ public:
 
 private:
     mat_t<val_type> m_encoder_output, m_encoder_delta;
+    bool m_memory_fresh = false;  // the cross-attention layers hold the keys and values of m_encoder_output
     encoder_t<val_type, updator_type>* m_encoder = nullptr;
     std::vector<decoder_layer_t<val_type, updator_type>> m_layers;
 
@@ -133,7 +151,35 @@ public:
         m_encoder = &encoder;
         for (size_t i = 0; i < size(); ++i) get_mhca(i).set_encoder_param(m_encoder_output, m_encoder_delta);
     }
-    void set_encoder_output(const mat_t<val_type>& encoder_output) { m_encoder_output = encoder_output; }
+    // a new encoder output: the self-attention caches start over and the cross-attention layers project their keys and
+    // values once, lazily at the first cached step
+    void set_encoder_output(const mat_t<val_type>& encoder_output) {
+        m_encoder_output = encoder_output;
+        m_memory_fresh = false;
+        reset_cache();
+    }
+    void reset_cache() {
+        for (size_t i = 0; i < size(); ++i) get_mha(i).reset_cache();
+    }
+    // the decoder outputs of the new input columns, equal to the last columns of forward(whole prefix) (the reference's
+    // predict loop, transformer_test.hpp:227-241, recomputes that prefix at every step)
+    mat_t<val_type> forward_cached(mat_t<val_type> x) {
+        if (!m_memory_fresh) {
+            for (size_t i = 0; i < size(); ++i) get_mhca(i).refresh_memory();
+            m_memory_fresh = true;
+        }
+        for (size_t i = 0; i < size(); ++i) {
+            mat_t<val_type> a = get_mha(i).forward_cached(x);
+            x = get_mha_norm(i).forward((a + x).clone());
+            mat_t<val_type> c = get_mhca(i).forward_cached(x);
+            x = get_mhca_norm(i).forward((c + x).clone());
+            mat_t<val_type> f = get_ffn(i).forward(x);
+            x = get_ffn_norm(i).forward((((f > 0) * f) + x).clone());
+        }
+        return x;
+    }
+    void save(std::ostream& os) const { for (auto const& l : m_layers) l.save(os); }
+    void load(std::istream& is) { for (auto& l : m_layers) l.load(is); }
     mat_t<val_type> get_encoder_output() const { return m_encoder_output; }
     size_t size() const { return m_layers.size(); }
 
@@ -197,6 +243,11 @@ public:
     void encoder_forward(const mat_t<val_type>& input) { m_decoder.set_encoder_output(m_encoder.forward(input)); }
     // after encoder_forward; may be called many times to generate a sequence (reference: :475-478)
     mat_t<val_type> forward(const mat_t<val_type>& input) { return m_decoder.forward(input); }
+    // the same for the new columns only, against cached self-attention keys / values and the static cross cache
+    mat_t<val_type> forward_cached(const mat_t<val_type>& new_columns) { return m_decoder.forward_cached(new_columns); }
+    void reset_cache() { m_decoder.reset_cache(); }
+    void save(std::ostream& os) const { m_encoder.save(os); m_decoder.save(os); }
+    void load(std::istream& is) { m_encoder.load(is); m_decoder.load(is); }
     template <typename... upr_param_types>
     void set_updator(upr_param_types&&... params) { m_encoder.set_updator(params...); m_decoder.set_updator(params...); }
     template <typename init_type>

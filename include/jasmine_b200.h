@@ -408,6 +408,26 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
  * a stream capture).  A tensor-parallel model that still uses the host all-reduce hook runs the step eagerly. */
 jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int batch, int32_t* h_next, float* h_logits,
                                       void* stream);
+/* ---- continuous batching over the paged cache (the step after decode_step; the reference's loop serves one sequence
+ *      at a time by full recompute, transformer_test.hpp:231-239) -------------------------------------------------
+ * jsm_llama_create_paged: like jsm_llama_create, but the KV pages form ONE pool of n_pages pages (64 positions each, all
+ * layers) that is handed out on demand, instead of max_batch fixed runs of pages; n_pages may be smaller than
+ * max_batch * ceil(max_context / 64) (over-subscription: admission then fails with JSM_OOM when the pool is empty).
+ * The active sequences occupy the batch rows 0 .. n_active-1.
+ * jsm_llama_seq_admit   takes the next free row, allocates pages for the prompt, prefills it (T <= 512 tokens) and
+ *                       returns the row and the first generated token (h_logits_last or NULL: F32 [vocab]).
+ * jsm_llama_step_active one greedy decode step for all active rows: h_ids[r] is appended to row r (a row that crosses a
+ *                       page boundary gets a new page first), h_next[r] / h_logits (or NULL, F32 [n_active, vocab]) out.
+ * jsm_llama_seq_retire  returns the row's pages to the pool; the LAST active row then takes the freed row (its block-table
+ *                       row moves, its pages stay): *moved_from is that row's old index, or -1 if nothing moved.
+ * Admission and retirement happen between steps; all three calls synchronise `stream` (a non-default stream).
+ * A model created this way serves only these calls; one created with jsm_llama_create only the calls above. */
+jsm_status jsm_llama_create_paged(const jsm_model_config* cfg, uint64_t seed, int n_pages, jsm_model** out);
+jsm_status jsm_llama_seq_admit(jsm_model* m, const int32_t* h_prompt, int T, int* row, int32_t* h_first_token,
+                               float* h_logits_last, void* stream);
+jsm_status jsm_llama_step_active(jsm_model* m, const int32_t* h_ids, int32_t* h_next, float* h_logits, void* stream);
+jsm_status jsm_llama_seq_retire(jsm_model* m, int row, int* moved_from, void* stream);
+jsm_status jsm_llama_pool_state(jsm_model* m, int* n_active, int* free_pages, int* total_pages);
 /* Host-side bookkeeping of context lengths (advance after a captured step is replayed). */
 jsm_status jsm_llama_set_context(jsm_model* m, int seq, int context_len);
 jsm_status jsm_llama_reset(jsm_model* m);

@@ -114,6 +114,11 @@ SYMBOLS = {
     "jsm_llama_prefill": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "jsm_llama_decode_step": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "jsm_llama_decode_step_host": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
+    "jsm_llama_create_paged": (_i, [C.POINTER(ModelConfig), _u64, _i, C.POINTER(_vp)]),
+    "jsm_llama_seq_admit": (_i, [_vp, _vp, _i, C.POINTER(_i), _vp, _vp, _vp]),
+    "jsm_llama_step_active": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "jsm_llama_seq_retire": (_i, [_vp, _i, C.POINTER(_i), _vp]),
+    "jsm_llama_pool_state": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "jsm_llama_set_context": (_i, [_vp, _i, _i]),
     "jsm_llama_reset": (_i, [_vp]),
     "jsm_llama_step_bytes": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),

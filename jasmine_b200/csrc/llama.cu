@@ -84,6 +84,15 @@ struct jsm_model {
     // host-buffer decode step (jsm_llama_decode_step_host): staging buffers and one instantiated graph per batch size
     int32_t *ids_dev = nullptr, *next_dev = nullptr;
     std::map<int, cudaGraphExec_t> step_graphs;
+    // continuous batching (jsm_llama_create_paged): pages are handed out on demand from one pool; the active sequences
+    // occupy the batch rows 0 .. n_active-1 and a retiring row is refilled with the last one (its block-table row moves,
+    // its pages stay where they are)
+    bool paged = false;
+    int n_pool_pages = 0, n_active = 0;
+    std::vector<int32_t> free_pages;
+    std::vector<std::vector<int32_t>> row_pages;
+    std::vector<int32_t> h_ctx;
+    int32_t* prompt_dev = nullptr;
 };
 
 namespace jsm {
@@ -531,7 +540,7 @@ using namespace jsm;
 
 extern "C" {
 
-jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_model** out) {
+static jsm_status llama_create_impl(const jsm_model_config* cfg, uint64_t seed, int pool_pages, jsm_model** out) {
     if (!cfg || !out) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_create: null argument");
     *out = nullptr;
     const jsm_model_config& c = *cfg;
@@ -569,7 +578,11 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
             return s__;             \
         }                           \
     } while (0)
-    const long long n_pages = (long long)c.max_batch * m->pages_per_seq;
+    // static layout: every sequence owns its own run of pages; paged: a pool of pool_pages pages shared by all rows
+    const long long table_entries = (long long)c.max_batch * m->pages_per_seq;
+    const long long n_pages = pool_pages > 0 ? pool_pages : table_entries;
+    m->paged = pool_pages > 0;
+    m->n_pool_pages = (int)n_pages;
     const size_t page_elems = (size_t)2 * m->Hkv_l * JSM_PAGE_SIZE * D;
     uint64_t wbytes = 0;
     const int qdim = m->Hq_l * D;  // K of the attention output projection
@@ -629,10 +642,16 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     m->weight_bytes = wbytes;
     JSM_TRY(dev_alloc(m, &m->rope, (size_t)c.max_context * (D / 2) * 4));
     JSM_TRY(jsm_rope_table(m->rope, 1, D, c.rope_theta, c.max_context, st));
-    JSM_TRY(dev_alloc(m, &m->block_table, (size_t)n_pages));
+    JSM_TRY(dev_alloc(m, &m->block_table, (size_t)table_entries));
     {
-        std::vector<int32_t> bt((size_t)n_pages);
-        for (long long i = 0; i < n_pages; ++i) bt[(size_t)i] = (int32_t)i;
+        std::vector<int32_t> bt((size_t)table_entries, 0);
+        if (!m->paged)
+            for (long long i = 0; i < table_entries; ++i) bt[(size_t)i] = (int32_t)i;
+        else {
+            for (int p = (int)n_pages - 1; p >= 0; --p) m->free_pages.push_back(p);  // page 0 is handed out first
+            m->row_pages.resize(c.max_batch);
+            m->h_ctx.assign(c.max_batch, 0);
+        }
         cudaError_t e = cudaMemcpy(m->block_table, bt.data(), bt.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
         if (e != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: block table upload: %s", cudaGetErrorString(e)); }
     }
@@ -677,6 +696,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
     JSM_TRY(dev_alloc(m, &m->ids_dev, (size_t)c.max_batch));
+    JSM_TRY(dev_alloc(m, &m->prompt_dev, (size_t)m->max_tokens));
     JSM_TRY(dev_alloc(m, &m->next_dev, (size_t)c.max_batch));
     tc_error_word();  // first use allocates the device's error word: do it here, not inside a captured step
     // the chunk length of the decode attention depends on the batch of the step: room for the largest need over 1..max_batch
@@ -688,6 +708,13 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
 #undef JSM_TRY
     *out = m;
     return JSM_OK;
+}
+
+jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_model** out) { return llama_create_impl(cfg, seed, 0, out); }
+
+jsm_status jsm_llama_create_paged(const jsm_model_config* cfg, uint64_t seed, int n_pages, jsm_model** out) {
+    if (n_pages <= 0) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_create_paged: %d pages", n_pages);
+    return llama_create_impl(cfg, seed, n_pages, out);
 }
 
 jsm_status jsm_llama_destroy(jsm_model* m) {
@@ -968,6 +995,101 @@ jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int ba
     JSM_CUDA_CHECK(cudaMemcpyAsync(h_next, m->next_dev, sizeof(int32_t) * batch, cudaMemcpyDeviceToHost, st));
     if (h_logits) JSM_CUDA_CHECK(cudaMemcpyAsync(h_logits, m->logits, sizeof(float) * (size_t)batch * m->c.vocab, cudaMemcpyDeviceToHost, st));
     JSM_CUDA_CHECK(cudaStreamSynchronize(st));
+    return JSM_OK;
+}
+
+// ---- continuous batching over the paged cache ----------------------------------------------------------------------
+// The reference's generation loop serves one sequence at a time and recomputes it from scratch (transformer_test.hpp:
+// 231-239).  Here sequences of different lengths share one decode step; they are admitted and retired between steps.
+namespace {
+// pages for `positions` cached positions of batch row `row`; uploads the part of the row's block table that changed
+jsm_status provision(jsm_model* m, int row, int positions, cudaStream_t st) {
+    std::vector<int32_t>& pages = m->row_pages[row];
+    const int have = (int)pages.size(), need = (positions + JSM_PAGE_SIZE - 1) / JSM_PAGE_SIZE;
+    if (need <= have) return JSM_OK;
+    if (need > m->pages_per_seq) JSM_FAIL(JSM_SHAPE, "context overflow: %d positions, the model was created for %d", positions, m->c.max_context);
+    if (need - have > (int)m->free_pages.size())
+        JSM_FAIL(JSM_OOM, "page pool exhausted: %d pages needed, %zu free of %d", need - have, m->free_pages.size(), m->n_pool_pages);
+    for (int i = have; i < need; ++i) {
+        pages.push_back(m->free_pages.back());
+        m->free_pages.pop_back();
+    }
+    JSM_CUDA_CHECK(cudaMemcpyAsync(m->block_table + (size_t)row * m->pages_per_seq + have, pages.data() + have, sizeof(int32_t) * (need - have),
+                                   cudaMemcpyHostToDevice, st));
+    JSM_CUDA_CHECK(cudaStreamSynchronize(st));  // the host vector may be reallocated by the next call
+    return JSM_OK;
+}
+}  // namespace
+
+jsm_status jsm_llama_seq_admit(jsm_model* m, const int32_t* h_prompt, int T, int* row_out, int32_t* h_first_token, float* h_logits_last,
+                               void* stream) {
+    if (!m || !h_prompt || !row_out) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_seq_admit: null argument");
+    if (!m->paged) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_seq_admit: the model was not created with jsm_llama_create_paged");
+    if (T <= 0 || T > m->max_tokens || T >= m->c.max_context) JSM_FAIL(JSM_SHAPE, "jsm_llama_seq_admit: %d prompt tokens (1..%d)", T, std::min(m->max_tokens, m->c.max_context - 1));
+    if (m->n_active >= m->c.max_batch) JSM_FAIL(JSM_OOM, "jsm_llama_seq_admit: all %d batch rows are in use", m->c.max_batch);
+    cudaStream_t st = as_stream(stream);
+    const int row = m->n_active;
+    jsm_status s = provision(m, row, T, st);
+    if (s != JSM_OK) return s;
+    JSM_CUDA_CHECK(cudaMemcpyAsync(m->prompt_dev, h_prompt, sizeof(int32_t) * T, cudaMemcpyHostToDevice, st));
+    float* lg = h_logits_last ? m->logits : nullptr;
+    s = jsm_llama_prefill(m, m->prompt_dev, row, T, m->next_dev, lg, st);
+    if (s != JSM_OK) return s;
+    if (h_first_token) JSM_CUDA_CHECK(cudaMemcpyAsync(h_first_token, m->next_dev + row, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    if (h_logits_last) JSM_CUDA_CHECK(cudaMemcpyAsync(h_logits_last, m->logits, sizeof(float) * m->c.vocab, cudaMemcpyDeviceToHost, st));
+    JSM_CUDA_CHECK(cudaStreamSynchronize(st));
+    m->h_ctx[row] = T;
+    m->n_active = row + 1;
+    *row_out = row;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_seq_retire(jsm_model* m, int row, int* moved_from, void* stream) {
+    if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_seq_retire: null model");
+    if (!m->paged) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_seq_retire: the model was not created with jsm_llama_create_paged");
+    if (row < 0 || row >= m->n_active) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_seq_retire: row %d of %d active", row, m->n_active);
+    cudaStream_t st = as_stream(stream);
+    for (int32_t p : m->row_pages[row]) m->free_pages.push_back(p);
+    m->row_pages[row].clear();
+    const int last = m->n_active - 1;
+    if (moved_from) *moved_from = -1;
+    if (row != last) {
+        // the last active row takes the freed place: its block-table row and context length move, its pages do not
+        m->row_pages[row] = std::move(m->row_pages[last]);
+        m->row_pages[last].clear();
+        m->h_ctx[row] = m->h_ctx[last];
+        JSM_CUDA_CHECK(cudaMemcpyAsync(m->block_table + (size_t)row * m->pages_per_seq, m->row_pages[row].data(),
+                                       sizeof(int32_t) * m->row_pages[row].size(), cudaMemcpyHostToDevice, st));
+        JSM_CUDA_CHECK(cudaMemcpyAsync(m->ctx + row, &m->h_ctx[row], sizeof(int32_t), cudaMemcpyHostToDevice, st));
+        JSM_CUDA_CHECK(cudaStreamSynchronize(st));
+        if (moved_from) *moved_from = last;
+    }
+    m->h_ctx[last] = 0;
+    m->n_active = last;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_step_active(jsm_model* m, const int32_t* h_ids, int32_t* h_next, float* h_logits, void* stream) {
+    if (!m || !h_ids || !h_next) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_step_active: null argument");
+    if (!m->paged) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_step_active: the model was not created with jsm_llama_create_paged");
+    if (m->n_active == 0) return JSM_OK;
+    cudaStream_t st = as_stream(stream);
+    for (int row = 0; row < m->n_active; ++row) {
+        if (m->h_ctx[row] >= m->c.max_context) JSM_FAIL(JSM_SHAPE, "context overflow: row %d already holds max_context = %d tokens", row, m->c.max_context);
+        jsm_status s = provision(m, row, m->h_ctx[row] + 1, st);
+        if (s != JSM_OK) return s;
+    }
+    jsm_status s = jsm_llama_decode_step_host(m, h_ids, m->n_active, h_next, h_logits, st);
+    if (s != JSM_OK) return s;
+    for (int row = 0; row < m->n_active; ++row) m->h_ctx[row] += 1;
+    return JSM_OK;
+}
+
+jsm_status jsm_llama_pool_state(jsm_model* m, int* n_active, int* free_pages, int* total_pages) {
+    if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_pool_state: null model");
+    if (n_active) *n_active = m->n_active;
+    if (free_pages) *free_pages = m->paged ? (int)m->free_pages.size() : 0;
+    if (total_pages) *total_pages = m->n_pool_pages;
     return JSM_OK;
 }
 

@@ -10,12 +10,39 @@ from . import ALLREDUCE_FN, BF16, F32, ModelConfig, check, lib, stream_ptr
 
 class Llama:
     def __init__(self, n_layers, d_model, n_heads, n_kv_heads, d_ffn, vocab, max_batch, max_context, head_dim=128,
-                 norm_eps=1e-5, rope_theta=10000.0, seed=4, tp_rank=0, tp_size=1):
+                 norm_eps=1e-5, rope_theta=10000.0, seed=4, tp_rank=0, tp_size=1, pool_pages=0):
+        """pool_pages > 0: continuous batching (jsm_llama_create_paged): admit / step_active / retire."""
         self.cfg = ModelConfig(n_layers, d_model, n_heads, n_kv_heads, head_dim, d_ffn, vocab, max_batch, max_context,
                                norm_eps, rope_theta, tp_rank, tp_size)
         self._h = C.c_void_p()
-        check(lib().jsm_llama_create(C.byref(self.cfg), seed, C.byref(self._h)))
+        if pool_pages > 0:
+            check(lib().jsm_llama_create_paged(C.byref(self.cfg), seed, pool_pages, C.byref(self._h)))
+        else:
+            check(lib().jsm_llama_create(C.byref(self.cfg), seed, C.byref(self._h)))
         self._cb = None
+
+    # ---- continuous batching (host tensors in, host values out) ----
+    def admit(self, h_prompt, h_logits_last=None):
+        """Prefills a prompt (int32 host tensor) into the next free batch row; returns (row, first generated token)."""
+        row, tok = C.c_int(), C.c_int32()
+        check(lib().jsm_llama_seq_admit(self._h, h_prompt.data_ptr(), h_prompt.numel(), C.byref(row), C.byref(tok),
+                                        h_logits_last.data_ptr() if h_logits_last is not None else None, stream_ptr()))
+        return row.value, tok.value
+
+    def step_active(self, h_ids, h_next, h_logits=None):
+        check(lib().jsm_llama_step_active(self._h, h_ids.data_ptr(), h_next.data_ptr(),
+                                          h_logits.data_ptr() if h_logits is not None else None, stream_ptr()))
+
+    def retire(self, row: int) -> int:
+        """Frees the row; returns the old index of the row that moved into its place, or -1."""
+        moved = C.c_int()
+        check(lib().jsm_llama_seq_retire(self._h, row, C.byref(moved), stream_ptr()))
+        return moved.value
+
+    def pool_state(self):
+        a, f, t = C.c_int(), C.c_int(), C.c_int()
+        check(lib().jsm_llama_pool_state(self._h, C.byref(a), C.byref(f), C.byref(t)))
+        return a.value, f.value, t.value
 
     def close(self):
         if self._h:

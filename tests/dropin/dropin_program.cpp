@@ -2,7 +2,10 @@
 //   g++ -std=c++20 -I<jasmine reference>               -> CPU, the reference's own headers (expected output)
 //   g++ -std=c++20 -Iinclude/jasmine -Iinclude -ljasmine_b200   -> this library, every operation on the GPU
 // and the two outputs are compared value by value (tests/test_gpu_dropin.py).
+#include <algorithm>
+#include <cmath>
 #include <cstdio>
+#include <sstream>
 #include <stdexcept>
 #include <vector>
 
@@ -163,5 +166,98 @@ int main() {
     tf.encoder_forward(ex);
     M dx = make(8, 3);
     dump("transformer", tf.forward(dx));
+
+    // ---- vsplit / vconcat (mat_mha_t.hpp:164-215) and their errors ----
+    {
+        M big = make(6, 4);
+        auto parts = vsplit(big, 3);
+        dump("vsplit_mid", parts[1].clone());
+        std::vector<M> pieces;
+        for (auto& p : parts) pieces.push_back(p.clone());
+        std::swap(pieces[0], pieces[2]);
+        dump("vconcat", vconcat(pieces));
+        int caught = 0;
+        try { vsplit(big, 4); } catch (const std::runtime_error&) { ++caught; }       // 6 rows do not split in 4
+        try { vsplit(big, 0); } catch (const std::runtime_error&) { ++caught; }
+        try { vconcat(std::vector<M>{}); } catch (const std::runtime_error&) { ++caught; }
+        try { vconcat(std::vector<M>{make(2, 3), make(2, 4)}); } catch (const std::runtime_error&) { ++caught; }
+        dump_scalar("split_concat_errors", caught);
+    }
+
+    // ---- generation: the reference's predict loop (transformer_test.hpp:227-241) feeds the growing decoder input through
+    // the whole stack at every step and takes the last output column as the next input column.  With JASMINE_B200 the same
+    // columns come from forward_cached: one new column per step against cached keys / values (self attention) and the
+    // keys / values of the encoder output projected once (cross attention). ----
+    {
+        const int d = 8, steps = 6;
+        transformer_base_t<M, sgd_t> gen(2, 2, 2, d);
+        gen.init_weight<seeded_t>();
+        M src = make(d, 4);
+        gen.encoder_forward(src);
+        M dec(d, steps + 1);
+        M first = make(d, 1);
+        dec.view(0, 0, d, 1).assign(first);
+        for (int len = 1; len <= steps; ++len) {
+#ifdef JASMINE_B200
+            M out_col = gen.forward_cached(dec.view(0, len - 1, d, 1).clone());
+            dec.view(0, len, d, 1).assign(out_col);
+#else
+            M out = gen.forward(dec.view(0, 0, d, len).clone());
+            dec.view(0, len, d, 1).assign(out.back_col());
+#endif
+        }
+        dump("predict", dec);
+        // a second sequence on the same object: the caches start over with the new encoder pass
+        M src2 = make(d, 3);
+        gen.encoder_forward(src2);
+        M dec2(d, 4);
+        dec2.view(0, 0, d, 1).assign(first);
+        for (int len = 1; len <= 3; ++len) {
+#ifdef JASMINE_B200
+            dec2.view(0, len, d, 1).assign(gen.forward_cached(dec2.view(0, len - 1, d, 1).clone()));
+#else
+            dec2.view(0, len, d, 1).assign(gen.forward(dec2.view(0, 0, d, len).clone()).back_col());
+#endif
+        }
+        dump("predict_again", dec2);
+
+        // decoder-only causal stack: a prompt of 3 columns at once, then column by column
+        encoder_t<F, sgd_t> lm(2, 2, d, 16);
+        for (int i = 0; i < 2; ++i) lm.get_mha(i).set_param(2, d, true, 16);
+        lm.init_weight<seeded_t>();
+        M seqm(d, 7);
+        seqm.view(0, 0, d, 3).assign(make(d, 3));
+#ifdef JASMINE_B200
+        M o3 = lm.forward_cached(seqm.view(0, 0, d, 3).clone());
+        seqm.view(0, 3, d, 1).assign(o3.back_col());
+        for (int len = 4; len < 7; ++len) seqm.view(0, len, d, 1).assign(lm.forward_cached(seqm.view(0, len - 1, d, 1).clone()));
+#else
+        for (int len = 3; len < 7; ++len) seqm.view(0, len, d, 1).assign(lm.forward(seqm.view(0, 0, d, len).clone()).back_col());
+#endif
+        dump("causal_stack_generate", seqm);
+
+        // checkpoint: a net that was initialised differently computes the saved net's outputs after loading its record
+#ifdef JASMINE_B200
+        std::stringstream file;
+        gen.save(file);
+        transformer_base_t<M, sgd_t> other(2, 2, 2, d);
+        other.init_weight<seeded_t>();        // other values: the generator has moved on
+        other.encoder_forward(src2);
+        M before = other.forward(dec2);
+        other.load(file);
+        other.encoder_forward(src2);
+        M after = other.forward(dec2);
+        M want = gen.forward(dec2);
+        double diff_before = 0, diff_after = 0;
+        for (int i = 0; i < d; ++i)
+            for (int j = 0; j < 4; ++j) {
+                diff_before = std::max(diff_before, (double)std::abs(before(i, j) - want(i, j)));
+                diff_after = std::max(diff_after, (double)std::abs(after(i, j) - want(i, j)));
+            }
+        dump_scalar("save_load", (diff_before > 1e-3 && diff_after == 0.0) ? 1 : 0);
+#else
+        dump_scalar("save_load", 1);
+#endif
+    }
     return 0;
 }

@@ -46,7 +46,8 @@ def test_program_output_equals_the_reference(tmp_path):
     assert list(got) == list(want)
     exact = {"add", "chain", "axpb", "bcast_col", "bcast_row", "scalar_left", "greater", "less", "relu_expr", "plus_assign", "convert",
              "elem_of_expr", "hmax", "max", "pow2", "sqrt", "view", "transpose", "back_col", "row", "view_expr", "assign", "dot", "dot_t",
-             "dot_chain", "dot_plus", "dot_error", "weight_net", "relu_net", "mlp", "mlp_fold", "residual", "mha_error"}
+             "dot_chain", "dot_plus", "dot_error", "weight_net", "relu_net", "mlp", "mlp_fold", "residual", "mha_error", "vsplit_mid", "vconcat",
+             "split_concat_errors", "save_load"}
     for name, w in want.items():
         g = got[name]
         assert g.shape == w.shape, name
@@ -56,5 +57,8 @@ def test_program_output_equals_the_reference(tmp_path):
             scale = max(float(np.max(np.abs(w))), 1e-30)
             err = float(np.max(np.abs(g - w))) / scale
             assert err <= 1e-5, f"{name}: relative error {err:.2e}"
+    # "predict", "predict_again" and "causal_stack_generate" come from forward_cached here (one new column per step against
+    # cached keys and values, cross-attention keys and values projected once per encoder pass) and from the reference's
+    # full-prefix recompute in the expected file (transformer_test.hpp:227-241): the <= 1e-5 bar above covers them.
     # the causal-prefix property of the reference's test_sequence_mha (transformer_test.hpp:246-282)
     assert np.max(np.abs(got["mha_prefix"] - got["mha_causal"][:, :4])) <= 1e-6

@@ -23,6 +23,7 @@ public:
 private:
     mat_t<val_type> m_weight, m_bias;
     updator_type<val_type> m_weight_updator, m_bias_updator;
+    mat_t<val_type> m_input;  // the last forward's input, for backward (reference: mat_net_t.hpp:23, 40)
 
 public:
     weight_net_t(int const& input_size = 1, int const& output_size = 1) : m_weight(output_size, input_size), m_bias(output_size, 1) {}
@@ -42,7 +43,23 @@ public:
         jsm_mat W = m_weight.jsm_device(), B = m_bias.jsm_device();
         mat_t<val_type> out(m_weight.row_num(), input.col_num());
         jsm_rt::check(jsm_dot_f32(W, X, &B, 0, nullptr, out.jsm_device_out(), jsm_rt::stream()));
+        if constexpr (std::is_same_v<any_input, mat_t<val_type>>) m_input = input;  // a device-to-device copy: kept for backward
+        else m_input = mat_t<val_type>();
         return out;
+    }
+
+    // Training step of the layer (reference: mat_net_t.hpp:65-75): dW = delta . X^T, db = row sums of delta, the
+    // gradient handed down is W^T . delta (with the weights BEFORE the update), then both updaters run.
+    template <typename other_type>
+    mat_t<val_type> backward(const other_type& delta) {
+        if (!m_input.valid()) throw std::runtime_error("backward without a preceding forward on a matrix input");
+        mat_t<val_type> d = delta;
+        mat_t<val_type> delta_weight = d.dot(m_input.t()).clone();
+        mat_t<val_type> delta_bias = hsum(d);
+        mat_t<val_type> ret = m_weight.t().dot(d).clone();
+        m_weight_updator.update(delta_weight, m_weight);
+        m_bias_updator.update(delta_bias, m_bias);
+        return ret;
     }
 
     template <typename init_type>
@@ -60,7 +77,7 @@ public:
         ss << print_indent(indent) << "weight_net_t:(in:" << m_weight.col_num() << ", out:" << m_weight.row_num() << ")";
         return ss.str();
     }
-    void step() {}
+    void step() { m_weight_updator.step(); m_bias_updator.step(); }
 
     // device windows for fused callers (attention packs the per-head projections itself)
     const mat_t<val_type>& jsm_weight() const { return m_weight; }
@@ -89,7 +106,16 @@ public:
     sigmoid_net_t() = default;
     void save(std::ostream&) const {}
     void load(std::istream&) {}
-    mat_t<val_type> forward(const input_type& input) { return jsm_net::unary<val_type>(input, JSM_OP_SIGMOID); }
+    mat_t<val_type> m_output;  // reference: mat_net_t.hpp:97
+    mat_t<val_type> forward(const input_type& input) {
+        m_output = jsm_net::unary<val_type>(input, JSM_OP_SIGMOID);
+        return m_output;
+    }
+    // delta * (1 - y) * y (reference: :108-116)
+    mat_t<val_type> backward(const mat_t<val_type>& delta) {
+        if (delta.row_num() != m_output.row_num() || delta.col_num() != m_output.col_num()) throw std::runtime_error("delta size does not match input size");
+        return (delta * (1 - m_output) * m_output).clone();
+    }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "sigmoid_net_t"; }
     template <typename init_type>
     void init_weight() {}
@@ -104,7 +130,17 @@ public:
     relu_net_t() = default;
     void save(std::ostream&) const {}
     void load(std::istream&) {}
-    mat_t<val_type> forward(const input_type& input) { return jsm_net::unary<val_type>(input, JSM_OP_RELU); }
+    mat_t<val_type> m_input;  // reference: mat_net_t.hpp:142
+    mat_t<val_type> forward(const input_type& input) {
+        m_input = input;
+        return jsm_net::unary<val_type>(input, JSM_OP_RELU);
+    }
+    // delta * (x > 0) (reference: :155-165)
+    template <typename other_type>
+    mat_t<val_type> backward(const other_type& delta) {
+        if (delta.row_num() != m_input.row_num() || delta.col_num() != m_input.col_num()) throw std::runtime_error("delta size does not match input size");
+        return (delta * (m_input > 0)).clone();
+    }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "relu_net_t"; }
     template <typename init_type>
     void init_weight() {}
@@ -195,6 +231,13 @@ public:
         mat_t<val_type> y = m_net.forward(input);
         return (y + input).clone();
     }
+    // reference: mat_net_t.hpp:330-334
+    template <typename other_type>
+    mat_t<val_type> backward(const other_type& delta) {
+        mat_t<val_type> d = delta;
+        mat_t<val_type> inner = m_net.backward(d);
+        return (inner + d).clone();
+    }
     std::string net_type(int const& indent = 0) const {
         std::stringstream ss;
         ss << print_indent(indent) << "residual_net_t:\n" << m_net.net_type(indent + 2);
@@ -222,6 +265,11 @@ public:
     template <typename input_type>
     auto forward(const input_type& input) {
         return std::apply([&input](auto&... nets) { return net_forward(input, nets...); }, m_nets);
+    }
+    // the members' backward steps from the last net to the first (reference: mat_net_t.hpp:381-385)
+    template <typename input_type>
+    auto backward(const input_type& delta) {
+        return std::apply([&delta](auto&... nets) { return net_backward(delta, nets...); }, m_nets);
     }
     constexpr size_t size() { return sizeof...(net_types); }
 

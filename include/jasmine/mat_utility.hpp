@@ -25,6 +25,17 @@ auto net_forward(In const& input, Nets&&... nets) {
     return (input >> ... >> nets);
 }
 
+// net << delta  ==  net.backward(delta); a chain folds right to left (complex_net_t::backward; reference: mat_utility.hpp:28-39)
+template <typename Net, typename In>
+requires is_backwardable<Net, In>
+auto operator<<(Net& net, In const& input) {
+    return net.backward(input);
+}
+template <typename In, typename... Nets>
+auto net_backward(In const& input, Nets&&... nets) {
+    return (nets << ... << input);
+}
+
 inline std::string print_indent(int n) { return std::string(n > 0 ? (size_t)n : 0, ' '); }
 
 #endif

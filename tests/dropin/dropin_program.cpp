@@ -18,6 +18,8 @@
 #include "mat_transformer_kernel_t.hpp"
 #include "mat_RoPE_t.hpp"
 #include "mat_transformer_t.hpp"
+#include "mat_loss_t.hpp"
+#include "mat_updator_t.hpp"
 
 using F = float;
 using M = mat_t<F>;
@@ -258,6 +260,57 @@ int main() {
 #else
         dump_scalar("save_load", 1);
 #endif
+    }
+
+    // ---- training of the basic nets: forward, mse gradient, backward through the chain, updater (mat_net_t.hpp:65-75,
+    // 108-116, 155-165, 330-334, 381-385; mat_updator_t.hpp; mat_loss_t.hpp) ----
+    {
+        g_state = 777u;  // the checkpoint block above draws a different number of values under the two sets of headers
+        M tx = make(6, 5), ty = make(4, 5);
+        {
+            using net_t = complex_net_builder_t<F>::push_back_updatable<weight_net_t, sgd_t>::push_back_staticnet<relu_net_t>::
+                push_back_updatable<weight_net_t, sgd_t>::type;
+            net_t net;
+            net.reinit(std::vector<int>{6, 7, 4});
+            net.init_weight<seeded_t>();
+            net.set_updator(0.05f);
+            mse_loss_t<M> loss;
+            M losses(1, 6);
+            for (int it = 0; it < 6; ++it) {
+                loss.forward(net.forward(tx));
+                losses(0, it) = loss.loss(ty);
+                net.backward(loss.backward(ty));
+                net.step();
+            }
+            dump("train_sgd_loss", losses);
+            dump("train_sgd_out", net.forward(tx));
+        }
+        {
+            residual_net_t<complex_net_t<weight_net_t<M, nadam_t>, relu_net_t<M>>> net;
+            net.base_net().reinit(std::vector<int>{6, 6});
+            net.init_weight<seeded_t>();
+            mse_loss_t<M> loss;
+            M target = make(6, 5);
+            for (int it = 0; it < 4; ++it) {
+                loss.forward(net.forward(tx));
+                net.backward(loss.backward(target));
+            }
+            dump("train_nadam_residual_out", net.forward(tx));
+        }
+        {
+            weight_net_t<M, adam_t> net(6, 4);
+            net.init_weight<seeded_t>();
+            mse_loss_t<M> loss;
+            M down;
+            for (int it = 0; it < 4; ++it) {
+                loss.forward(net.forward(tx));
+                down = net.backward(loss.backward(ty));
+            }
+            dump("train_adam_out", net.forward(tx));
+            dump("train_adam_grad_in", down);
+        }
+        // (sigmoid_net_t::backward is left out: the reference's version, mat_net_t.hpp:108-116, keeps an expression that
+        // refers to a temporary of the previous statement and reads freed memory when optimised.)
     }
     return 0;
 }

@@ -45,6 +45,25 @@ inline jsm_mat transposed(const jsm_mat& x) {
     t.rows = x.cols; t.cols = x.rows; t.row_stride = x.col_stride; t.col_stride = x.row_stride;
     return t;
 }
+// softmax(mask(Q K^T * scale)) V over token-major fp32 q [Sq, H*dh], k and v (the first Sk rows of their buffers), all
+// contiguous rows of H*dh floats.  fp32 kernel with the reference's arithmetic (mat_mha_t.hpp:53-71), or - when the
+// caller opted in (jsm_rt::attention_bf16) and the heads are 128 wide - the tensor-core flash kernel on bf16 copies.
+inline void attention(const float* q, const float* k, const float* v, float* out, int Sq, int Sk, int H, int dh, bool mask) {
+    const float scale = 1.0f / std::sqrt((float)dh);
+    if (!(jsm_rt::attention_bf16() && dh == 128)) {
+        jsm_rt::check(jsm_attn_prefill(q, k, v, out, JSM_F32, 1, Sq, Sk, H, H, dh, mask ? 1 : 0, scale, nullptr, 1, jsm_rt::stream()));
+        return;
+    }
+    const size_t nq = (size_t)Sq * H * dh, nk = (size_t)Sk * H * dh;
+    jsm_rt::device_buffer qb(nq * 2), kb(nk * 2), vb(nk * 2), ob(nq * 2);
+    jsm_rt::check(jsm_convert(qb.p, JSM_BF16, q, JSM_F32, nq, jsm_rt::stream()));
+    jsm_rt::check(jsm_convert(kb.p, JSM_BF16, k, JSM_F32, nk, jsm_rt::stream()));
+    jsm_rt::check(jsm_convert(vb.p, JSM_BF16, v, JSM_F32, nk, jsm_rt::stream()));
+    jsm_rt::check(jsm_attn_prefill(qb.p, kb.p, vb.p, ob.p, JSM_BF16, 1, Sq, Sk, H, H, dh, mask ? 1 : 0, scale, nullptr, 2, jsm_rt::stream()));
+    jsm_rt::check(jsm_convert(out, JSM_F32, ob.p, JSM_BF16, nq, jsm_rt::stream()));
+    jsm_rt::check(jsm_stream_sync(jsm_rt::stream()));  // the temporaries are released on return
+}
+
 // Y[tokens, out] = X_tm . W^T + b^T for a weight_net_t: the same k-ascending sums as W . X + b
 template <typename net>
 void project(const net& w, const jsm_mat& x_tm, const jsm_mat& out) {
@@ -192,8 +211,9 @@ private:
         const jsm_mat Q = q.jsm_device_out();
         for (int h = 0; h < m_num_heads; ++h)
             jsm_attn::project(m_heads[h].q_net(), jsm_attn::token_major_rows(Xq, h * dh, dh), jsm_attn::columns(Q, h * dh, dh));
-        jsm_rt::check(jsm_attn_prefill(Q.data, m_k_cache.jsm_device().data, m_v_cache.jsm_device().data, att.jsm_device_out().data, JSM_F32, 1, Sq,
-                                       n_keys, m_num_heads, m_num_heads, dh, mask ? 1 : 0, 1.0f / std::sqrt((float)dh), nullptr, 1, jsm_rt::stream()));
+        jsm_attn::attention(static_cast<const float*>(Q.data), static_cast<const float*>(m_k_cache.jsm_device().data),
+                            static_cast<const float*>(m_v_cache.jsm_device().data), static_cast<float*>(att.jsm_device_out().data), Sq, n_keys,
+                            m_num_heads, dh, mask);
         mat_t<val_type> out(d, Sq);
         jsm_mat Wo = m_output_proj.jsm_weight().jsm_device(), Bo = m_output_proj.jsm_bias().jsm_device();
         jsm_rt::check(jsm_dot_f32(Wo, jsm_attn::transposed(att.jsm_device()), &Bo, 0, nullptr, out.jsm_device_out(), jsm_rt::stream()));
@@ -296,8 +316,8 @@ private:
             jsm_attn::project(m_heads[h].k_net(), jsm_attn::token_major_rows(Xkv, h * dh, dh), jsm_attn::columns(K, h * dh, dh));
             jsm_attn::project(m_heads[h].v_net(), jsm_attn::token_major_rows(Xkv, h * dh, dh), jsm_attn::columns(V, h * dh, dh));
         }
-        jsm_rt::check(jsm_attn_prefill(Q.data, K.data, V.data, att.jsm_device_out().data, JSM_F32, 1, Sq, Sk, m_num_heads, m_num_heads, dh,
-                                       mask ? 1 : 0, 1.0f / std::sqrt((float)dh), nullptr, 1, jsm_rt::stream()));
+        jsm_attn::attention(static_cast<const float*>(Q.data), static_cast<const float*>(K.data), static_cast<const float*>(V.data),
+                            static_cast<float*>(att.jsm_device_out().data), Sq, Sk, m_num_heads, dh, mask);
         // out[d, S] = Wo . concat + bo, the concatenated heads being att^T
         mat_t<val_type> out(d, Sq);
         jsm_mat Wo = m_output_proj.jsm_weight().jsm_device(), Bo = m_output_proj.jsm_bias().jsm_device();

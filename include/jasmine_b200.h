@@ -342,8 +342,10 @@ jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions);
  * (*d_pass) * n_sites + site + 1 and must grow from call to call, identically on every rank (d_pass: I32 in device
  * memory, written before the launch); h (bf16 [T, d]) += sum over ranks of their buffer; xn (or NULL) = RMSNorm(h)
  * without gain.
- * A peer that does not arrive within the wait limit (jsm_tp_set_wait_limit_ms, default about 1 s) leaves h untouched
- * and raises JSM_TIMEOUT at the next jsm_check_device_errors. */
+ * A peer that does not arrive within the wait limit (jsm_tp_set_wait_limit_ms, default about 1 s) raises JSM_TIMEOUT at
+ * the next jsm_check_device_errors; the CTAs (one per token) time their waits separately, so the tokens whose CTA gave up
+ * keep their old h while a token whose CTA still saw the flag is updated: after JSM_TIMEOUT the step's result is invalid
+ * as a whole.  The self-resetting counters of the projections stay consistent (no kernel leaves one half-counted). */
 size_t jsm_tp_region_bytes(int max_tokens, int d);
 jsm_status jsm_tp_set_wait_limit_ms(int ms);
 jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,

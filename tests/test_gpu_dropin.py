@@ -62,3 +62,24 @@ def test_program_output_equals_the_reference(tmp_path):
     # full-prefix recompute in the expected file (transformer_test.hpp:227-241): the <= 1e-5 bar above covers them.
     # the causal-prefix property of the reference's test_sequence_mha (transformer_test.hpp:246-282)
     assert np.max(np.abs(got["mha_prefix"] - got["mha_causal"][:, :4])) <= 1e-6
+
+
+def _build_ours(src, exe):
+    cmd = ["g++", "-std=c++20", "-O2", f"-I{ROOT / 'include' / 'jasmine'}", f"-I{ROOT / 'include'}", str(src), "-o", str(exe),
+           f"-L{ROOT / 'jasmine_b200'}", "-ljasmine_b200", f"-Wl,-rpath,{ROOT / 'jasmine_b200'}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-4000:]
+    return exe
+
+
+@pytest.mark.gpu
+def test_encoder_decoder_attention_on_the_tensor_cores(tmp_path):
+    """tests/dropin/tensor_core_attention.cpp: an encoder-decoder transformer of the header API with 128-wide heads, once on
+    the fp32 kernels and once with jsm_rt::attention_bf16() (self, cross and cached attention through the tcgen05 flash
+    kernel, Tq != Tk, Tq = 1): the outputs agree to the bf16 bar."""
+    exe = _build_ours(ROOT / "tests" / "dropin" / "tensor_core_attention.cpp", tmp_path / "tca")
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    vals = dict(line.split() for line in res.stdout.strip().splitlines())
+    assert float(vals["full_pass"]) <= 2e-2, vals
+    assert float(vals["cached_generation"]) <= 2e-2, vals

@@ -328,9 +328,9 @@ def run_timeline(args):
         ptrs[0] = p.value
         for r in range(1, tp):
             ptrs[r] = fakes[r - 1].data_ptr()
-        flags = torch.full((32,), 1 << 30, dtype=torch.int32)   # the flag words of both exchange protocols: peers "arrived"
+        flags = torch.full((48,), 1 << 30, dtype=torch.int32)   # the flag words of all exchange protocols: peers "arrived"
         flags[16] = 0                                            # ... but this rank's own push flag is set by its own kernels
-        jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 128, jb.stream_ptr()))
+        jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 192, jb.stream_ptr()))
         torch.cuda.synchronize()
         jb.check(jb.lib().jsm_llama_tp_connect(m._h, ptrs))
     nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
@@ -399,7 +399,14 @@ def tp_parity_check(world, rank, local, dist):
             m.decode_step(ids, nxt, lg)
             out.append(lg.clone())
             toks.append(nxt.clone())
+        # one more step that asks for tokens only: a tensor-parallel group then shares the lm_head by vocabulary and the
+        # ranks exchange (best logit, index) pairs; its tokens must be the arg-max of the same step's full logits
+        ids = toks[-1].clone()
+        tok_only = torch.zeros_like(nxt)
+        m.decode_step(ids, tok_only)
         jb.check_device_errors()
+        torch.cuda.synchronize()
+        out.append(tok_only.clone())
         torch.cuda.synchronize()
         if connect:
             dist.barrier()
@@ -410,6 +417,7 @@ def tp_parity_check(world, rank, local, dist):
     if rank != 0:
         return None
     out_1, tok_1 = run(0, 1, False)
+    tok_only_n, tok_only_1 = out_n.pop(), out_1.pop()
     worst, clear_equal, n_clear = 0.0, True, 0
     prefix_same = True
     for i, (a, b) in enumerate(zip(out_n, out_1)):
@@ -423,7 +431,10 @@ def tp_parity_check(world, rank, local, dist):
         if bool((tok_n[i][clear] != tok_1[i][clear]).any()):
             clear_equal = False
         prefix_same = bool((tok_n[i] == tok_1[i]).all())
+    # the tokens-only step (vocabulary-sharded lm_head + arg-max exchange) against the single rank's tokens of the same step
+    sharded_equal = bool((tok_only_n == tok_only_1).all()) if prefix_same else None
     return {"max_rel_logit_diff": worst, "top1_equal_where_margin_clear": clear_equal, "rows_with_clear_margin": n_clear,
+            "sharded_lm_head_tokens_equal": sharded_equal,
             "layers": L, "batch": B, "prompt_len": T, "decode_steps": steps, "tolerance": 2e-2,
             "what": f"logits of a {L}-layer full-width model (d 4096, 32x128 heads, ffn 11008, vocab 32000): the live tp{world} "
                     "group over peer memory against a single rank on rank 0's GPU; prefill + decode steps"}
@@ -764,7 +775,8 @@ def main():
         except Exception as e:
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {type(e).__name__}: {e}"}
-    bad_parity = parity is not None and (parity["max_rel_logit_diff"] > parity["tolerance"] or not parity["top1_equal_where_margin_clear"])
+    bad_parity = parity is not None and (parity["max_rel_logit_diff"] > parity["tolerance"] or not parity["top1_equal_where_margin_clear"]
+                                         or parity["sharded_lm_head_tokens_equal"] is False)
     if bad_parity:
         line["invalid"] = "tensor-parallel parity check failed"
     print(json.dumps(line), flush=True)

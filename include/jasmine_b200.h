@@ -326,7 +326,7 @@ jsm_status jsm_llama_create(const jsm_model_config* cfg, uint64_t seed, jsm_mode
 jsm_status jsm_llama_destroy(jsm_model* m);
 jsm_status jsm_llama_set_allreduce(jsm_model* m, jsm_allreduce_fn fn, void* user);
 /* Tensor-parallel exchange over peer memory (no counterpart in the reference, which has no parallelism).
- * Every rank owns a region [flags | buffer A | buffer B | two push buffers of 8 slots] in its own memory
+ * Every rank owns a region [flags | buffer A | buffer B | two push buffers of 8 slots | arg-max slots] in its own memory
  * (jsm_llama_tp_region); the host makes the
  * peers' regions addressable (jsm_ipc_export / jsm_ipc_import between processes of one node) and hands them to
  * jsm_llama_tp_connect ([tp_size] device pointers, the entry of the own rank is ignored).  From then on the model sums
@@ -374,6 +374,14 @@ jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int size, int wh
 jsm_status jsm_tp_linear_reduce(void* d_region, int rank, int size, int which_buffer, int max_tokens, int32_t* d_state,
                                 int site, int n_sites, void* d_h, float* d_ssq, const void* d_packed, int epilogue,
                                 void* d_Y, int out_dtype, int T, int N, int d, float eps, void* stream);
+/* Arg-max over a vocabulary that is split across the ranks (a tensor-parallel group that is asked for tokens only lets
+ * every rank stream just its share of the lm_head): d_best_val / d_best_idx hold this rank's best logit per token and its
+ * index in the full vocabulary; one CTA stores the pairs into its slot of every region, releases the epoch
+ * (*d_pass) * n_sites + site + 1, waits (bounded) for the peers and writes the index of the largest value over the ranks
+ * (lowest index on a tie) to d_out[T].  The slots lie behind the push buffers of a region (d = d_model of the region). */
+jsm_status jsm_tp_argmax_exchange(void* const* d_regions, int rank, int size, int max_tokens, int d, const int32_t* d_pass,
+                                  int site, int n_sites, const float* d_best_val, const int32_t* d_best_idx, int32_t* d_out,
+                                  int T, void* stream);
 /* CUDA IPC plumbing for regions that live in another process of the same node (64-byte handles). */
 jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64);
 jsm_status jsm_ipc_import(const unsigned char* handle64, void** d_ptr);

@@ -103,6 +103,7 @@ SYMBOLS = {
     "jsm_tp_allreduce_add_norm": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _f, _i, _i, _vp]),
     "jsm_tp_linear_push": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "jsm_tp_linear_reduce": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp]),
+    "jsm_tp_argmax_exchange": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp]),
     "jsm_ipc_export": (_i, [_vp, C.c_char_p]),
     "jsm_ipc_import": (_i, [C.c_char_p, C.POINTER(_vp)]),
     "jsm_ipc_close": (_i, [_vp]),

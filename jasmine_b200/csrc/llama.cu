@@ -30,6 +30,8 @@ jsm_status attn_decode_append_checked(const void* d_q, int64_t q_row_stride, con
                                       int32_t* d_counters, void* d_out, void* stream);
 int* tc_error_word();
 constexpr int TC_CONTEXT_OVERFLOW = 32;  // error word code: a decode step met a sequence that already holds max_context tokens
+jsm_status tp_argmax_exchange_launch(void* const* regions, int rank, int size, int max_tokens, int d, const int* pass, int site, int n_sites,
+                                     const float* best_val, const int* best_idx, int32_t* out, int T, cudaStream_t st);
 jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size, size_t buf_offset, const int* pass, int site,
                                         int n_sites, void* h, void* xn, float eps, int T, int d, cudaStream_t st);
 
@@ -77,6 +79,8 @@ struct jsm_model {
     void* tp_regions[8] = {nullptr};
     int32_t* tp_state = nullptr;
     bool tp_connected = false;
+    float* best_val = nullptr;   // vocabulary-sharded lm_head: this rank's best logit per token
+    int32_t* best_idx = nullptr;
     bool last_push = false;  // the last forward call exchanged by push (its final exchange is consumed by the logits projection)
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
@@ -310,6 +314,36 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
     }
 }
 
+// best (value, index + col0) of every row: the local half of the arg-max over a vocabulary that is split across ranks
+__global__ void __launch_bounds__(256) argmax_rows_pair_kernel(const float* __restrict__ x, float* __restrict__ best_val, int* __restrict__ best_idx,
+                                                               int n, int col0) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    chain_trigger();
+    chain_wait();
+    const float* row = x + (long long)blockIdx.x * n;
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float v = row[i];
+        if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, m, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+        if (ov > m || (ov == m && oi < mi)) { m = ov; mi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = m; si[threadIdx.x >> 5] = mi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > m || (sv[w] == m && si[w] < mi)) { m = sv[w]; mi = si[w]; }
+        best_val[blockIdx.x] = m;
+        best_idx[blockIdx.x] = mi == 0x7fffffff ? 0x7fffffff : mi + col0;
+    }
+}
+
 template <typename T>
 static jsm_status dev_alloc(jsm_model* m, T** p, size_t n) {
     void* q = nullptr;
@@ -383,7 +417,7 @@ static jsm_status run_linear(jsm_model* m, const __nv_bfloat16* X, long long x_s
 static TpFuse exchange_base(jsm_model* m, int site) {
     TpFuse f;
     f.n_ranks = m->c.tp_size; f.rank = m->c.tp_rank;
-    f.pass = m->tp_state; f.site = site; f.n_sites = 2 * m->c.n_layers;
+    f.pass = m->tp_state; f.site = site; f.n_sites = 2 * m->c.n_layers + 1;  // two per layer and the arg-max exchange
     f.state = m->tp_state + 4;
     f.wait_limit = tp_wait_limit_cycles();
     return f;
@@ -428,7 +462,7 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
         const size_t off = tp_buffer_offset(which, m->max_tokens, d);
         jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->tp_region + off, false, T, st);
         if (s != JSM_OK) return s;
-        return tp_allreduce_add_norm_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, off, m->tp_state, site, 2 * m->c.n_layers, m->h,
+        return tp_allreduce_add_norm_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, off, m->tp_state, site, 2 * m->c.n_layers + 1, m->h,
                                             normalise ? m->xn : nullptr, m->c.norm_eps, T, d, st);
     }
     jsm_status s = run_linear(m, X, K, Wp, N, K, LIN_NONE, nullptr, m->red, false, T, st);
@@ -525,6 +559,25 @@ static jsm_status logits_and_argmax(jsm_model* m, int first, int rows, int T, in
     const __nv_bfloat16* x = ((tp && !push) ? m->xn : m->h) + (long long)first * d;
     TpFuse f;
     if (push) f = consume_exchange(m, 1, 2 * (m->c.n_layers - 1) + 1, m->ssq_b, first);
+    // Tokens only (no logits asked for) on a connected tensor-parallel group: every rank streams only its share of the
+    // lm_head - a run of whole 128-row tiles of the same packed matrix - takes the best logit of its slice, and the ranks
+    // exchange (value, index) pairs: 8 bytes per token and rank instead of (N-1)/N of the matrix on every rank.
+    if (tp && m->tp_connected && d_next && !d_logits && rows <= m->c.max_batch) {
+        int nt, kbt;
+        pk_dims(m->c.vocab, d, 0, &nt, &kbt);
+        const int t0 = (int)((long long)m->c.tp_rank * nt / m->c.tp_size), t1 = (int)((long long)(m->c.tp_rank + 1) * nt / m->c.tp_size);
+        const int col0 = t0 * 128, n_local = std::min(t1 * 128, m->c.vocab) - col0;
+        if (n_local > 0) {
+            jsm_status s = run_linear(m, x, d, m->lm_head + (size_t)t0 * kbt * (128 * 64 * 2), n_local, d, LIN_NONE, nullptr, m->logits, true, rows, st,
+                                      rs, T, push ? &f : nullptr);
+            if (s != JSM_OK) return s;
+            JSM_CUDA_CHECK(launch_chained(argmax_rows_pair_kernel, dim3(rows), dim3(256), 0, st, (const float*)m->logits, m->best_val, m->best_idx,
+                                          n_local, col0));
+            JSM_LAUNCH_CHECK();
+            return tp_argmax_exchange_launch(m->tp_regions, m->c.tp_rank, m->c.tp_size, m->max_tokens, d, m->tp_state, 2 * m->c.n_layers,
+                                             2 * m->c.n_layers + 1, m->best_val, m->best_idx, d_next, rows, st);
+        }
+    }
     jsm_status s = run_linear(m, x, d, m->lm_head, m->c.vocab, d, LIN_NONE, nullptr, lg, true, rows, st, rs, T, push ? &f : nullptr);
     if (s != JSM_OK) return s;
     if (d_next) {
@@ -695,6 +748,8 @@ static jsm_status llama_create_impl(const jsm_model_config* cfg, uint64_t seed, 
     JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
+    JSM_TRY(dev_alloc(m, &m->best_val, (size_t)c.max_batch));
+    JSM_TRY(dev_alloc(m, &m->best_idx, (size_t)c.max_batch));
     JSM_TRY(dev_alloc(m, &m->ids_dev, (size_t)c.max_batch));
     JSM_TRY(dev_alloc(m, &m->prompt_dev, (size_t)m->max_tokens));
     JSM_TRY(dev_alloc(m, &m->next_dev, (size_t)c.max_batch));
@@ -972,15 +1027,17 @@ jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int ba
     if (!st) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step_host: needs a stream of its own (the legacy default stream cannot be captured)");
     JSM_CUDA_CHECK(cudaMemcpyAsync(m->ids_dev, h_ids, sizeof(int32_t) * batch, cudaMemcpyHostToDevice, st));
     const bool host_allreduce = m->c.tp_size > 1 && !m->tp_connected;  // the hook belongs to the host: run such a step eagerly
+    float* lg = h_logits ? m->logits : nullptr;  // tokens only: a tensor-parallel group then shares the lm_head by vocabulary
     if (host_allreduce) {
-        jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, m->logits, st);
+        jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, lg, st);
         if (s != JSM_OK) return s;
     } else {
-        auto it = m->step_graphs.find(batch);
+        const int key = 2 * batch + (lg ? 1 : 0);  // one graph per batch size and output form
+        auto it = m->step_graphs.find(key);
         if (it == m->step_graphs.end()) {
             cudaGraph_t graph = nullptr;
             JSM_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
-            jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, m->logits, st);
+            jsm_status s = jsm_llama_decode_step(m, m->ids_dev, batch, m->next_dev, lg, st);
             cudaError_t e = cudaStreamEndCapture(st, &graph);
             if (s != JSM_OK) { if (graph) cudaGraphDestroy(graph); return s; }
             if (e != cudaSuccess) { cudaGetLastError(); JSM_FAIL(JSM_CUDA, "jsm_llama_decode_step_host: stream capture failed: %s", cudaGetErrorString(e)); }
@@ -988,7 +1045,7 @@ jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int ba
             e = cudaGraphInstantiate(&exec, graph, 0);
             cudaGraphDestroy(graph);
             if (e != cudaSuccess) { cudaGetLastError(); JSM_FAIL(JSM_CUDA, "jsm_llama_decode_step_host: graph instantiation failed: %s", cudaGetErrorString(e)); }
-            it = m->step_graphs.emplace(batch, exec).first;
+            it = m->step_graphs.emplace(key, exec).first;
         }
         JSM_CUDA_CHECK(cudaGraphLaunch(it->second, st));
     }
@@ -1110,7 +1167,13 @@ jsm_status jsm_llama_step_bytes(jsm_model* m, uint64_t* weight_bytes, uint64_t* 
     if (!m) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_step_bytes: null model");
     // every projection including lm_head is streamed once per step; the embedding table is gathered (one row per token)
     // and is not part of the count
-    if (weight_bytes) *weight_bytes = m->weight_bytes;
+    // (a connected tensor-parallel rank that is asked for tokens only streams its 1/N share of lm_head)
+    uint64_t w = m->weight_bytes;
+    if (m->c.tp_size > 1 && m->tp_connected) {
+        const uint64_t lm = 2ull * (uint64_t)m->c.vocab * m->c.d_model;
+        w = w - lm + lm / m->c.tp_size;
+    }
+    if (weight_bytes) *weight_bytes = w;
     if (kv_bytes_per_token) *kv_bytes_per_token = (uint64_t)m->c.n_layers * 2ull * m->Hkv_l * m->c.head_dim * 2ull;
     return JSM_OK;
 }

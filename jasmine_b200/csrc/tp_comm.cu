@@ -173,13 +173,19 @@ __global__ void __launch_bounds__(256) tp_allreduce_add_norm_kernel(TpArgs a) {
 
 constexpr int TP_PUSH_FLAG_WORD = 16;  // first push flag inside the flag block (one word per source rank)
 size_t tp_slot_bytes(int d) { return (size_t)TP_PUSH_MAX_T * d * sizeof(__nv_bfloat16); }
-size_t tp_region_bytes(int max_tokens, int d) {
-    return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + 2 * (size_t)TP_MAX_RANKS * tp_slot_bytes(d);
-}
+size_t tp_argmax_offset(int max_tokens, int d);
+size_t tp_region_bytes(int max_tokens, int d) { return tp_argmax_offset(max_tokens, d) + (size_t)TP_MAX_RANKS * max_tokens * 8; }
 size_t tp_buffer_offset(int which, int max_tokens, int d) { return TP_FLAG_BYTES + (size_t)(which & 1) * max_tokens * d * sizeof(__nv_bfloat16); }
 // slot 0 of push buffer `which`; rank r's slot follows at r * tp_slot_bytes(d)
 size_t tp_push_offset(int which, int max_tokens, int d) {
     return TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + (size_t)(which & 1) * TP_MAX_RANKS * tp_slot_bytes(d);
+}
+// The arg-max exchange of a vocabulary-sharded lm_head: every rank's (best logit, its index) per token, 8 slots of
+// max_tokens pairs behind the push buffers; flag words TP_ARGMAX_FLAG_WORD.. (one per source rank)
+constexpr int TP_ARGMAX_FLAG_WORD = 32;
+size_t tp_argmax_offset(int max_tokens, int d) {
+    const size_t off = TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + 2 * (size_t)TP_MAX_RANKS * tp_slot_bytes(d);
+    return (off + 255) & ~(size_t)255;
 }
 int tp_push_flag_word() { return TP_PUSH_FLAG_WORD; }
 long long tp_wait_limit_cycles() { return g_tp_wait_limit_cycles; }
@@ -199,6 +205,88 @@ jsm_status tp_allreduce_add_norm_launch(void* const* regions, int rank, int size
     a.h = reinterpret_cast<__nv_bfloat16*>(h); a.xn = reinterpret_cast<__nv_bfloat16*>(xn);
     a.eps = eps; a.d = d; a.err = tc_error_word(); a.wait_limit = g_tp_wait_limit_cycles;
     JSM_CUDA_CHECK(launch_chained(tp_allreduce_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, a));
+    JSM_LAUNCH_CHECK();
+    return JSM_OK;
+}
+
+// ---- arg-max over a vocabulary that is split across the ranks --------------------------------------------------------
+// Every rank has the best logit of its vocabulary slice per token (value, global index).  One CTA per rank: stores its
+// pairs into its slot of every rank's region (plain peer stores), one system-scope fence, the epoch into every peer's flag
+// word; waits (bounded) for the peers; takes, per token, the largest value over the ranks in rank order (the lowest index
+// wins a tie, as in the one-GPU arg-max).  8 bytes per token and rank cross NVLink instead of every rank streaming the
+// whole lm_head.
+struct TpArgmaxArgs {
+    uint8_t* regions[TP_MAX_RANKS];
+    int rank, size;
+    size_t slot_offset;     // of slot 0 inside a region; slot r follows at r * max_tokens * 8
+    int max_tokens;
+    const int* pass;
+    int site, n_sites;
+    const float* best_val;  // local [T]
+    const int* best_idx;    // local [T], global vocabulary indices
+    int32_t* out;           // [T]
+    int T;
+    int* err;
+    long long wait_limit;
+};
+__global__ void __launch_bounds__(256) tp_argmax_exchange_kernel(TpArgmaxArgs a) {
+    __shared__ int ok_s;
+    chain_trigger();
+    chain_wait();
+    const int E = *reinterpret_cast<const volatile int*>(a.pass) * a.n_sites + a.site + 1;
+    if (threadIdx.x == 0) ok_s = 1;
+    for (int i = threadIdx.x; i < a.size * a.T; i += blockDim.x) {
+        const int r = i / a.T, t = i % a.T;
+        uint2 pair = make_uint2(__float_as_uint(a.best_val[t]), (uint32_t)a.best_idx[t]);
+        *reinterpret_cast<uint2*>(a.regions[r] + a.slot_offset + ((size_t)a.rank * a.max_tokens + t) * 8) = pair;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        for (int r = 0; r < a.size; ++r)
+            if (r != a.rank)
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(reinterpret_cast<int*>(a.regions[r]) + TP_ARGMAX_FLAG_WORD + a.rank), "r"(E) : "memory");
+    }
+    if (threadIdx.x < a.size && threadIdx.x != a.rank) {
+        const int* flag = reinterpret_cast<const int*>(a.regions[a.rank]) + TP_ARGMAX_FLAG_WORD + threadIdx.x;
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys(flag) - E) < 0) {
+            __nanosleep(64);
+            if (clock64() - t0 > a.wait_limit) {
+                ok_s = 0;
+                if (a.err) atomicCAS(a.err, 0, TP_TIMEOUT_CODE);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!ok_s) return;  // the tokens stay as they were; the error word says why
+    for (int t = threadIdx.x; t < a.T; t += blockDim.x) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int r = 0; r < a.size; ++r) {
+            const uint2 pair = __ldcg(reinterpret_cast<const uint2*>(a.regions[a.rank] + a.slot_offset + ((size_t)r * a.max_tokens + t) * 8));
+            const float v = __uint_as_float(pair.x);
+            const int idx = (int)pair.y;
+            if (v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
+        }
+        a.out[t] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+jsm_status tp_argmax_exchange_launch(void* const* regions, int rank, int size, int max_tokens, int d, const int* pass, int site, int n_sites,
+                                     const float* best_val, const int* best_idx, int32_t* out, int T, cudaStream_t st) {
+    if (T <= 0) return JSM_OK;
+    if (!regions || !pass || !best_val || !best_idx || !out) JSM_FAIL(JSM_INVALID_ARG, "tp_argmax: null pointer");
+    if (size < 1 || size > TP_MAX_RANKS || rank < 0 || rank >= size || T > max_tokens) JSM_FAIL(JSM_INVALID_ARG, "tp_argmax: rank %d of %d, %d tokens", rank, size, T);
+    TpArgmaxArgs a;
+    for (int r = 0; r < TP_MAX_RANKS; ++r) a.regions[r] = r < size ? reinterpret_cast<uint8_t*>(regions[r]) : nullptr;
+    for (int r = 0; r < size; ++r)
+        if (!a.regions[r]) JSM_FAIL(JSM_INVALID_ARG, "tp_argmax: region of rank %d is not connected", r);
+    a.rank = rank; a.size = size; a.slot_offset = tp_argmax_offset(max_tokens, d); a.max_tokens = max_tokens;
+    a.pass = pass; a.site = site; a.n_sites = n_sites; a.best_val = best_val; a.best_idx = best_idx; a.out = out; a.T = T;
+    a.err = tc_error_word(); a.wait_limit = g_tp_wait_limit_cycles;
+    JSM_CUDA_CHECK(launch_chained(tp_argmax_exchange_kernel, dim3(1), dim3(256), 0, st, a));
     JSM_LAUNCH_CHECK();
     return JSM_OK;
 }
@@ -224,6 +312,11 @@ extern "C" jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank
     if (T > max_tokens) JSM_FAIL(JSM_SHAPE, "jsm_tp_allreduce_add_norm: %d tokens, the region holds %d", T, max_tokens);
     return tp_allreduce_add_norm_launch(d_regions, rank, size, tp_buffer_offset(which_buffer, max_tokens, d), d_pass, site, n_sites, d_h,
                                         d_xn, eps, T, d, as_stream(stream));
+}
+
+extern "C" jsm_status jsm_tp_argmax_exchange(void* const* d_regions, int rank, int size, int max_tokens, int d, const int32_t* d_pass, int site,
+                                             int n_sites, const float* d_best_val, const int32_t* d_best_idx, int32_t* d_out, int T, void* stream) {
+    return tp_argmax_exchange_launch(d_regions, rank, size, max_tokens, d, d_pass, site, n_sites, d_best_val, d_best_idx, d_out, T, as_stream(stream));
 }
 
 extern "C" jsm_status jsm_ipc_export(const void* d_ptr, unsigned char* handle64) {

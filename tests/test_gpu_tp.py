@@ -163,3 +163,45 @@ def test_fused_exchange_gives_up_when_a_peer_never_pushes():
         assert int(torch.ones(4, device="cuda").sum()) == 4
     finally:
         jb.check(jb.lib().jsm_tp_set_wait_limit_ms(1000))
+
+
+def test_argmax_exchange_over_vocabulary_shards():
+    """The arg-max of a vocabulary-sharded lm_head: every rank contributes (best logit, global index) per token.  The
+    peers' pairs are written into this rank's region by the host and their flags are set before the launch, so the one
+    kernel of rank 1 never waits: it must publish its own pairs into every region and pick, per token, the largest value
+    over the ranks (lowest index on a tie)."""
+    n, T, d, max_tokens, rank = 4, 7, 512, 16, 1
+    regions, ptrs = make_regions(n, max_tokens, d)
+    nbytes = jb.lib().jsm_tp_region_bytes(max_tokens, d)
+    slot0 = nbytes - 8 * max_tokens * 8                      # the arg-max slots are the last part of a region
+    vals = cases.normal((n, T), 960, 0).astype(np.float32)
+    idx = np.stack([cases.ints(T, 4, 961 + r, r * 1000, (r + 1) * 1000) for r in range(n)]).astype(np.int32)
+    vals[2, 3] = vals[0, 3] = 9.0                            # a tie between ranks 0 and 2: the lower index (rank 0's) wins
+    vals[3, 5] = 8.0
+    for r in range(n):
+        if r == rank:
+            continue
+        pairs = np.zeros((max_tokens, 2), np.uint32)
+        pairs[:T, 0] = vals[r].view(np.uint32)
+        pairs[:T, 1] = idx[r].view(np.uint32)
+        off = slot0 + r * max_tokens * 8
+        regions[rank][off:off + max_tokens * 8] = torch.from_numpy(pairs.view(np.uint8).reshape(-1)).cuda()
+    regions[rank][128:128 + 32].view(torch.int32).fill_(1 << 30)   # flag words 32..39: every peer has "arrived"
+    state = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((T,), -1, dtype=torch.int32, device="cuda")
+    bv, bi = dev(vals[rank]), torch.from_numpy(idx[rank]).cuda()
+    jb.check(jb.lib().jsm_tp_argmax_exchange(ptrs, rank, n, max_tokens, d, state.data_ptr(), 0, 1, bv.data_ptr(), bi.data_ptr(),
+                                             out.data_ptr(), T, jb.stream_ptr()))
+    jb.check_device_errors()
+    want = []
+    for t in range(T):
+        best = max(range(n), key=lambda r: (vals[r, t], -idx[r, t]))
+        want.append(int(idx[best, t]))
+    assert out.cpu().tolist() == want
+    # rank 1's own pairs reached its slot in every region, and its flag word in every peer's region holds epoch 1
+    for r in range(n):
+        off = slot0 + rank * max_tokens * 8
+        got = regions[r][off:off + T * 8].cpu().numpy().view(np.uint32).reshape(T, 2)
+        assert np.array_equal(got[:, 0], vals[rank].view(np.uint32)) and np.array_equal(got[:, 1], idx[rank].view(np.uint32))
+        if r != rank:
+            assert int(regions[r][128:128 + 32].view(torch.int32)[rank]) == 1

@@ -278,8 +278,7 @@ def run_kernel_workload(args, collect=False):
             jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2, out=o)
 
         def with_rope(_):
-            jb.rope_apply(q, table, D, H, positions=pos, out=qr)
-            jb.rope_apply(k, table, D, H, positions=pos, out=kr)
+            jb.rope_apply_qk(q, k, table, D, H, H, positions=pos, q_out=qr, k_out=kr)
             jb.attn_prefill(qr, kr, v, batch, H, H, D, causal=True, impl=2, out=o)
         with_rope(0)
         jb.check_device_errors()  # a kernel that gave up on a wait must not be timed

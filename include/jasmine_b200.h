@@ -218,6 +218,11 @@ jsm_status jsm_rope_table(float* d_table, int mode, int d, float theta, int max_
 jsm_status jsm_rope_apply(const void* d_x, void* d_out, jsm_dtype dtype, const float* d_table, int d, int n_heads,
                           const int32_t* d_positions, int T, void* stream);
 
+/* Queries and keys of one prefill rotated by ONE launch (both share the positions): q [T, Hq*d], k [T, Hkv*d]; the same
+ * arithmetic as two jsm_rope_apply calls (bit-identical results). */
+jsm_status jsm_rope_apply_qk(const void* d_q, void* d_q_out, int Hq, const void* d_k, void* d_k_out, int Hkv, jsm_dtype dtype,
+                             const float* d_table, int d, const int32_t* d_positions, int T, void* stream);
+
 /* ---- attention (mat_head_gen_t::forward, mat_mha_t.hpp:45-74) -----------
  * q:[T_q, Hq*D], k,v:[T_k, Hkv*D] token-major, per sequence b of `batch`
  * equally long sequences; out:[T_q, Hq*D].  scores = q.k / sqrt(D) (scale passed

@@ -84,6 +84,7 @@ SYMBOLS = {
     "jsm_linear_bf16_packed": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "jsm_rope_table": (_i, [_vp, _i, _i, _f, _i, _vp]),
     "jsm_rope_apply": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp]),
+    "jsm_rope_apply_qk": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
     "jsm_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
     "jsm_kv_append": (_i, [_vp, _vp, _i, _vp, _vp, _i64, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "jsm_attn_decode_scratch_bytes": (_sz, [_i, _i, _i, _i]),
@@ -268,6 +269,16 @@ def rope_apply(x, table, d, n_heads, positions=None, out=None):
     check(lib().jsm_rope_apply(x.data_ptr(), out.data_ptr(), dtype_of(x), table.data_ptr(), d, n_heads,
                                positions.data_ptr() if positions is not None else None, x.shape[0], stream_ptr()))
     return out
+
+
+def rope_apply_qk(q, k, table, d, Hq, Hkv, positions=None, q_out=None, k_out=None):
+    """Queries and keys rotated by one launch (jsm_rope_apply_qk)."""
+    torch = _torch()
+    q_out = torch.empty_like(q) if q_out is None else q_out
+    k_out = torch.empty_like(k) if k_out is None else k_out
+    check(lib().jsm_rope_apply_qk(q.data_ptr(), q_out.data_ptr(), Hq, k.data_ptr(), k_out.data_ptr(), Hkv, dtype_of(q), table.data_ptr(), d,
+                                  positions.data_ptr() if positions is not None else None, q.shape[0], stream_ptr()))
+    return q_out, k_out
 
 
 def attn_prefill(q, k, v, batch, Hq, Hkv, D, causal=True, scale=None, rope=None, impl=0, out=None):

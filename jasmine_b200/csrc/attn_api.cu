@@ -35,20 +35,31 @@ extern "C" jsm_status jsm_attn_prefill(const void* d_q, const void* d_k, const v
         if (!d_rope_table) return flash_prefill_launch(d_q, d_k, d_v, d_out, batch, T_q, T_k, Hq, Hkv, causal, scale, nullptr, st);
         // the tensor-core kernel takes rotated q and k: rotate into stream-ordered temporaries first
         // (sequences start at position 0; queries sit at the end of the keys)
-        void *qr = nullptr, *kr = nullptr;
-        int32_t* pos = nullptr;
+        // (stream-ordered allocations: no device synchronisation, legal inside a stream capture; released on every path)
+        struct Temps {
+            cudaStream_t st;
+            void *qr = nullptr, *kr = nullptr;
+            int32_t* pos = nullptr;
+            ~Temps() {
+                if (qr) cudaFreeAsync(qr, st);
+                if (kr) cudaFreeAsync(kr, st);
+                if (pos) cudaFreeAsync(pos, st);
+            }
+        } tmp{st};
         const size_t qn = (size_t)batch * T_q * Hq * D, kn = (size_t)batch * T_k * Hkv * D;
-        JSM_CUDA_CHECK(cudaMallocAsync(&qr, qn * 2, st));
-        JSM_CUDA_CHECK(cudaMallocAsync(&kr, kn * 2, st));
-        JSM_CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&pos), sizeof(int32_t) * (size_t)batch * (T_q + T_k), st));
+        JSM_CUDA_CHECK(cudaMallocAsync(&tmp.qr, qn * 2, st));
+        JSM_CUDA_CHECK(cudaMallocAsync(&tmp.kr, kn * 2, st));
+        JSM_CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&tmp.pos), sizeof(int32_t) * (size_t)batch * (T_q + T_k), st));
+        int32_t* pos = tmp.pos;
         jsm_status s = fill_positions(pos, batch, T_q, T_k - T_q, st);
         if (s == JSM_OK) s = fill_positions(pos + (size_t)batch * T_q, batch, T_k, 0, st);
-        if (s == JSM_OK) s = jsm_rope_apply(d_q, qr, JSM_BF16, d_rope_table, D, Hq, pos, batch * T_q, st);
-        if (s == JSM_OK) s = jsm_rope_apply(d_k, kr, JSM_BF16, d_rope_table, D, Hkv, pos + (size_t)batch * T_q, batch * T_k, st);
-        if (s == JSM_OK) s = flash_prefill_launch(qr, kr, d_v, d_out, batch, T_q, T_k, Hq, Hkv, causal, scale, nullptr, st);
-        cudaFreeAsync(qr, st);
-        cudaFreeAsync(kr, st);
-        cudaFreeAsync(pos, st);
+        if (s == JSM_OK && T_q == T_k) {
+            s = jsm_rope_apply_qk(d_q, tmp.qr, Hq, d_k, tmp.kr, Hkv, JSM_BF16, d_rope_table, D, pos, batch * T_q, st);  // one launch
+        } else {
+            if (s == JSM_OK) s = jsm_rope_apply(d_q, tmp.qr, JSM_BF16, d_rope_table, D, Hq, pos, batch * T_q, st);
+            if (s == JSM_OK) s = jsm_rope_apply(d_k, tmp.kr, JSM_BF16, d_rope_table, D, Hkv, pos + (size_t)batch * T_q, batch * T_k, st);
+        }
+        if (s == JSM_OK) s = flash_prefill_launch(tmp.qr, tmp.kr, d_v, d_out, batch, T_q, T_k, Hq, Hkv, causal, scale, nullptr, st);
         return s;
     }
     return attn_simt_launch(d_q, d_k, d_v, d_out, dtype, batch, T_q, T_k, Hq, Hkv, D, causal, scale, d_rope_table, st);

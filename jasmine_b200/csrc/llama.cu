@@ -192,11 +192,10 @@ __global__ void advance_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int
         seq_ids[b] = b;
         ctx[b] = c + 1;
     }
-    if (b == 0 && pass) {
-        *pass = *pass + 1;
-        __threadfence();
-    }
-    chain_trigger();  // after the pass number is in memory (see iota_kernel)
+    if (b == 0 && pass) *pass = *pass + 1;
+    __threadfence();
+    chain_trigger();  // after the pass number and the context lengths are in memory (see iota_kernel): later kernels of the
+                      // chain read both before they wait for their predecessors
 }
 
 __device__ __forceinline__ float block_sum_256(float v, float* smem) {

@@ -112,9 +112,82 @@ __global__ void __launch_bounds__(256) rope_apply_bf16_heads_kernel(const __nv_b
     }
 }
 
+// Queries and keys of a prefill in ONE launch (two tensors, the same positions): a thread issues the loads of all its
+// heads of both tensors before the first rotation (four 16-byte loads in flight per thread at 32 + 32 heads instead of
+// two), and the table entries of the next token are requested before the current token is rotated.
+__global__ void __launch_bounds__(256) rope_apply_bf16_qk_kernel(const __nv_bfloat16* __restrict__ xq, __nv_bfloat16* __restrict__ oq, int Hq,
+                                                                 const __nv_bfloat16* __restrict__ xk, __nv_bfloat16* __restrict__ ok, int Hk,
+                                                                 const float4* __restrict__ table, const int32_t* __restrict__ positions,
+                                                                 int T_tokens) {
+    constexpr int D = 128, MAXU = 8;  // up to 64 + 64 heads
+    const int qd = threadIdx.x & 15, hl = threadIdx.x >> 4;
+    const int nq = (Hq - hl + 15) / 16, nk = (Hk - hl + 15) / 16;  // heads of this lane in q and in k
+    int t = blockIdx.x;
+    if (t >= T_tokens) return;
+    float4 c[4];
+    {
+        const int m = positions ? positions[t] : t;
+        const float4* e = table + (long long)m * (D / 2) + qd * 4;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) c[p] = e[p];
+    }
+    while (t < T_tokens) {
+        const int t_next = t + gridDim.x;
+        uint4 w[MAXU];
+#pragma unroll
+        for (int u = 0; u < MAXU; ++u) {
+            if (u < nq) w[u] = __ldcs(reinterpret_cast<const uint4*>(xq + ((long long)t * Hq + hl + 16 * u) * D + 8 * qd));
+            else if (u - nq < nk) w[u] = __ldcs(reinterpret_cast<const uint4*>(xk + ((long long)t * Hk + hl + 16 * (u - nq)) * D + 8 * qd));
+        }
+        float4 cn[4];
+        if (t_next < T_tokens) {
+            const int m = positions ? positions[t_next] : t_next;
+            const float4* e = table + (long long)m * (D / 2) + qd * 4;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) cn[p] = e[p];
+        }
+#pragma unroll
+        for (int u = 0; u < MAXU; ++u) {
+            if (u >= nq + nk) break;
+            const uint32_t in[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const float x0 = bf16lo(in[p]), x1 = bf16hi(in[p]);
+                o[p] = pack_bf16x2(__fadd_rn(__fmul_rn(c[p].x, x0), __fmul_rn(-c[p].w, x1)),
+                                   __fadd_rn(__fmul_rn(c[p].y, x0), __fmul_rn(c[p].z, x1)));
+            }
+            __nv_bfloat16* dst = u < nq ? oq + ((long long)t * Hq + hl + 16 * u) * D + 8 * qd : ok + ((long long)t * Hk + hl + 16 * (u - nq)) * D + 8 * qd;
+            __stcs(reinterpret_cast<uint4*>(dst), make_uint4(o[0], o[1], o[2], o[3]));
+        }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) c[p] = cn[p];
+        t = t_next;
+    }
+}
+
 }  // namespace jsm
 
 using namespace jsm;
+
+extern "C" jsm_status jsm_rope_apply_qk(const void* d_q, void* d_q_out, int Hq, const void* d_k, void* d_k_out, int Hkv, jsm_dtype dtype,
+                                        const float* d_table, int d, const int32_t* d_positions, int T, void* stream) {
+    if (T == 0) return JSM_OK;
+    if (!d_q || !d_q_out || !d_k || !d_k_out || !d_table) JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_apply_qk: null pointer");
+    const bool aligned = !((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_q_out) | reinterpret_cast<uintptr_t>(d_k) |
+                            reinterpret_cast<uintptr_t>(d_k_out)) & 15);
+    if (dtype == JSM_BF16 && d == 128 && aligned && Hq > 0 && Hkv > 0 && (Hq + 15) / 16 + (Hkv + 15) / 16 <= 8 && T >= 64) {
+        const unsigned grid = (unsigned)(T < sm_count() * 8 ? T : sm_count() * 8);
+        rope_apply_bf16_qk_kernel<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(d_q), reinterpret_cast<__nv_bfloat16*>(d_q_out), Hq,
+                                                                       reinterpret_cast<const __nv_bfloat16*>(d_k), reinterpret_cast<__nv_bfloat16*>(d_k_out), Hkv,
+                                                                       reinterpret_cast<const float4*>(d_table), d_positions, T);
+        JSM_LAUNCH_CHECK();
+        return JSM_OK;
+    }
+    jsm_status s = jsm_rope_apply(d_q, d_q_out, dtype, d_table, d, Hq, d_positions, T, stream);
+    if (s != JSM_OK) return s;
+    return jsm_rope_apply(d_k, d_k_out, dtype, d_table, d, Hkv, d_positions, T, stream);
+}
 
 extern "C" jsm_status jsm_rope_table(float* d_table, int mode, int d, float theta, int max_pos, void* stream) {
     if (!d_table) JSM_FAIL(JSM_INVALID_ARG, "jsm_rope_table: null table");

@@ -42,6 +42,21 @@ def test_rope_standard_mode_matches_oracle():
     assert np.array_equal(host(yb), torch.from_numpy(want_b).to(torch.bfloat16).float().numpy())
 
 
+@pytest.mark.parametrize("T,Hq,Hkv", [(200, 32, 32), (96, 12, 4), (130, 5, 64)])
+def test_rope_of_queries_and_keys_in_one_launch(T, Hq, Hkv):
+    """jsm_rope_apply_qk rotates q and k of a prefill with one launch: bit-identical to two jsm_rope_apply calls."""
+    D = 128
+    q = dev(cases.normal((T, Hq * D), 625, 0), torch.bfloat16)
+    k = dev(cases.normal((T, Hkv * D), 625, 1), torch.bfloat16)
+    pos = torch.from_numpy((np.arange(T, dtype=np.int32) * 7) % 256).cuda()
+    table = jb.rope_table(1, D, 10000.0, 256)
+    qr, kr = jb.rope_apply_qk(q, k, table, D, Hq, Hkv, positions=pos)
+    assert torch.equal(qr, jb.rope_apply(q, table, D, Hq, positions=pos))
+    assert torch.equal(kr, jb.rope_apply(k, table, D, Hkv, positions=pos))
+    qr2, kr2 = jb.rope_apply_qk(q, k, table, D, Hq, Hkv)           # positions 0..T-1
+    assert torch.equal(qr2, jb.rope_apply(q, table, D, Hq)) and torch.equal(kr2, jb.rope_apply(k, table, D, Hkv))
+
+
 def mha_device(w, x, H, causal):
     """mat_mha_t::forward (mat_mha_t.hpp:265-291) from C-ABI calls: block-diagonal per-head projections
     (each head sees its own slice, :199-215), attention, concatenation, output projection."""

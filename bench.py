@@ -417,13 +417,14 @@ def tp_parity_check(world, rank, local, dist):
         return None
     out_1, tok_1 = run(0, 1, False)
     tok_only_n, tok_only_1 = out_n.pop(), out_1.pop()
-    worst, clear_equal, n_clear = 0.0, True, 0
+    worst, worst_rms, clear_equal, n_clear = 0.0, 0.0, True, 0
     prefix_same = True
     for i, (a, b) in enumerate(zip(out_n, out_1)):
         if not prefix_same:
             break  # the two runs decode different prefixes from here on: nothing to compare
         scale = float(b.abs().max())
         worst = max(worst, float((a - b).abs().max()) / scale)
+        worst_rms = max(worst_rms, float((a - b).pow(2).mean().sqrt()) / scale)
         top2 = torch.topk(b, 2, dim=1).values
         clear = (top2[:, 0] - top2[:, 1]) > 2 * 2e-2 * scale
         n_clear += int(clear.sum())
@@ -432,9 +433,15 @@ def tp_parity_check(world, rank, local, dist):
         prefix_same = bool((tok_n[i] == tok_1[i]).all())
     # the tokens-only step (vocabulary-sharded lm_head + arg-max exchange) against the single rank's tokens of the same step
     sharded_equal = bool((tok_only_n == tok_only_1).all()) if prefix_same else None
-    return {"max_rel_logit_diff": worst, "top1_equal_where_margin_clear": clear_equal, "rows_with_clear_margin": n_clear,
+    # Both runs are bf16 evaluations of the same function with different summation orders (rank-local products are rounded
+    # to bf16 before they are summed); each is held to 2e-2 of the fp32 oracle by the parity tests, so two of them may
+    # differ by up to twice that.  The run fails above 4e-2 or on a token mismatch at a clear margin; `within_2e-2` says
+    # whether the mutual difference also stays inside the single bar (it does in every run seen: 0.014 - 0.019 at 2, 4 and
+    # 8 ranks, which is the rounding noise of the bf16 residual stream, independent of the rank count).
+    return {"max_rel_logit_diff": worst, "rms_rel_logit_diff": worst_rms, "within_2e-2": worst <= 2e-2,
+            "top1_equal_where_margin_clear": clear_equal, "rows_with_clear_margin": n_clear,
             "sharded_lm_head_tokens_equal": sharded_equal,
-            "layers": L, "batch": B, "prompt_len": T, "decode_steps": steps, "tolerance": 2e-2,
+            "layers": L, "batch": B, "prompt_len": T, "decode_steps": steps, "tolerance": 4e-2,
             "what": f"logits of a {L}-layer full-width model (d 4096, 32x128 heads, ffn 11008, vocab 32000): the live tp{world} "
                     "group over peer memory against a single rank on rank 0's GPU; prefill + decode steps"}
 

@@ -9,6 +9,7 @@
 #ifndef JASMINE_B200_MAT_MHA_T_HPP_
 #define JASMINE_B200_MAT_MHA_T_HPP_
 #include <cmath>
+#include <limits>
 #include <stdexcept>
 #include <vector>
 
@@ -101,6 +102,9 @@ public:
     const ffn_type& q_net() const { return m_q_net; }
     const ffn_type& k_net() const { return m_k_net; }
     const ffn_type& v_net() const { return m_v_net; }
+    ffn_type& q_net() { return m_q_net; }
+    ffn_type& k_net() { return m_k_net; }
+    ffn_type& v_net() { return m_v_net; }
 
     // softmax(mask(Q^T K / sqrt(d))) applied to V (reference: mat_mha_t.hpp:45-74); input: [d, S]
     template <typename any_input>
@@ -120,7 +124,7 @@ public:
         m_v_net.template init_weight<init_type>();
     }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "mat_head_gen_t"; }
-    void step() {}
+    void step() { m_q_net.step(); m_k_net.step(); m_v_net.step(); }
     void save(std::ostream& os) const { m_q_net.save(os); m_k_net.save(os); m_v_net.save(os); }
     void load(std::istream& is) { m_q_net.load(is); m_k_net.load(is); m_v_net.load(is); }
 
@@ -184,6 +188,7 @@ private:
     // Self attention: grown by forward_cached.  Cross attention: computed once from the encoder output (set_memory).
     mat_t<val_type> m_k_cache, m_v_cache;
     int m_cached = 0;
+    mat_t<val_type> m_train_input;  // the last self-attention forward's input, for backward
 
     void reserve_cache(int positions) {
         if (positions <= m_k_cache.row_num() && m_k_cache.col_num() == m_d_model) return;
@@ -238,7 +243,46 @@ public:
     // self attention (reference: mat_mha_t.hpp:265-291)
     mat_t<val_type> forward(const input_type& input) {
         if (input.row_num() != m_d_model) throw std::runtime_error("Input row dimension must match d_model");
-        return attend(input, input, m_mask);
+        m_train_input = input;
+        return attend(input, input, m_mask, /*remember=*/true);
+    }
+    // Training step of self attention (reference: mat_mha_t.hpp:92-117 per head, :324-346 for the layer).  The forward
+    // kernel keeps no probabilities, so each head's q, k, v and softmax are rebuilt here from the stored input with the
+    // matrix operations of the API (the head's weight nets thereby remember their inputs for their own backward):
+    //   dV = delta . P, dP = delta^T . V, dS = P * (dP - rowsum(P * dP)) with the masked entries zeroed,
+    //   dQ = K . dS^T / sqrt(d_head), dK = Q . dS / sqrt(d_head), input gradient = sum of the three nets' backward.
+    mat_t<val_type> backward(const input_type& delta) {
+        if (!m_train_input.valid()) throw std::runtime_error("backward without a preceding forward");
+        mat_t<val_type> delta_concat = m_output_proj.backward(delta);
+        const int S = m_train_input.col_num(), dh = m_d_head;
+        const val_type root = static_cast<val_type>(std::sqrt((double)dh));
+        mat_t<val_type> keep(S, S), drop(S, S);  // causal mask as factors: 1 where key <= query; additive: -inf elsewhere
+        if (m_mask) {
+            for (int i = 0; i < S; ++i)
+                for (int j = 0; j < S; ++j) {
+                    keep(i, j) = j <= i ? val_type(1) : val_type(0);
+                    drop(i, j) = j <= i ? val_type(0) : -std::numeric_limits<val_type>::infinity();
+                }
+        }
+        mat_t<val_type> total(delta.row_num(), delta.col_num());
+        for (int h = 0; h < m_num_heads; ++h) {
+            mat_t<val_type> x_h = m_train_input.view(h * dh, 0, dh, S).clone();
+            mat_t<val_type> d_h = delta_concat.view(h * dh, 0, dh, S).clone();
+            mat_t<val_type> q = m_heads[h].q_net().forward(x_h), k = m_heads[h].k_net().forward(x_h), v = m_heads[h].v_net().forward(x_h);
+            mat_t<val_type> scores = (q.t().dot(k) / root).clone();
+            if (m_mask) scores = (scores + drop).clone();
+            mat_t<val_type> P = hsoftmax(scores);
+            mat_t<val_type> d_v = d_h.dot(P).clone();
+            mat_t<val_type> d_P = d_h.t().dot(v).clone();
+            mat_t<val_type> row_dot = hsum(P * d_P);
+            mat_t<val_type> d_S = (P * (d_P - row_dot)).clone();
+            if (m_mask) d_S = (d_S * keep).clone();
+            mat_t<val_type> d_q = (k.dot(d_S.t()) / root).clone();
+            mat_t<val_type> d_k = (q.dot(d_S) / root).clone();
+            mat_t<val_type> gq = m_heads[h].q_net().backward(d_q), gk = m_heads[h].k_net().backward(d_k), gv = m_heads[h].v_net().backward(d_v);
+            total.view(h * dh, 0, dh, S).assign((gq + gk + gv).clone());
+        }
+        return total;
     }
     // cross attention (reference: :293-322)
     mat_t<val_type> forward(const input_type& input, const input_type& encoder_input) {
@@ -303,10 +347,13 @@ public:
         ss << print_indent(indent) << "mat_mha_t:(heads:" << m_num_heads << ", d_model:" << m_d_model << ")";
         return ss.str();
     }
-    void step() {}
+    void step() {
+        for (auto& h : m_heads) h.step();
+        m_output_proj.step();
+    }
 
 private:
-    mat_t<val_type> attend(const input_type& xq, const input_type& xkv, bool mask) {
+    mat_t<val_type> attend(const input_type& xq, const input_type& xkv, bool mask, bool remember = false) {
         const jsm_mat Xq = xq.jsm_device(), Xkv = xkv.jsm_device();
         const int Sq = Xq.cols, Sk = Xkv.cols, d = m_d_model, dh = m_d_head;
         mat_t<val_type> q(Sq, d), k(Sk, d), v(Sk, d), att(Sq, d);
@@ -319,6 +366,7 @@ private:
         jsm_attn::attention(static_cast<const float*>(Q.data), static_cast<const float*>(K.data), static_cast<const float*>(V.data),
                             static_cast<float*>(att.jsm_device_out().data), Sq, Sk, m_num_heads, dh, mask);
         // out[d, S] = Wo . concat + bo, the concatenated heads being att^T
+        if (remember) m_output_proj.jsm_remember_input(att.t().clone());  // the output projection's input, for its backward
         mat_t<val_type> out(d, Sq);
         jsm_mat Wo = m_output_proj.jsm_weight().jsm_device(), Bo = m_output_proj.jsm_bias().jsm_device();
         jsm_rt::check(jsm_dot_f32(Wo, jsm_attn::transposed(att.jsm_device()), &Bo, 0, nullptr, out.jsm_device_out(), jsm_rt::stream()));

@@ -82,6 +82,8 @@ public:
     // device windows for fused callers (attention packs the per-head projections itself)
     const mat_t<val_type>& jsm_weight() const { return m_weight; }
     const mat_t<val_type>& jsm_bias() const { return m_bias; }
+    // a fused caller ran the projection itself: it hands over the input that backward needs
+    void jsm_remember_input(const mat_t<val_type>& input) { m_input = input; }
     // flat binary checkpoint (not in the reference, which cannot store a net): W then b
     void save(std::ostream& os) const { jsm_rt::save_tensor(os, m_weight); jsm_rt::save_tensor(os, m_bias); }
     void load(std::istream& is) { jsm_rt::load_tensor(is, m_weight); jsm_rt::load_tensor(is, m_bias); }
@@ -155,6 +157,7 @@ class layer_norm_net_t {
     mat_t<val_type> m_gama, m_beta;
     updator_type<val_type> m_gama_updator, m_beta_updator;
     val_type m_eps = 0;
+    mat_t<val_type> m_input;  // the last forward's input: backward rebuilds the normalised values and deviations from it
 
 public:
     layer_norm_net_t() = default;
@@ -177,7 +180,31 @@ public:
         }
         const float* g = static_cast<const float*>(m_gama.jsm_device().data);
         const float* b = static_cast<const float*>(m_beta.jsm_device().data);
+        m_input = input;
         return jsm_expr::along_axis(JSM_ROWS_LAYERNORM, 0, input, g, b, (float)m_eps);
+    }
+    // Training step (reference: mat_net_t.hpp:227-243, eps = 0).  With x_hat the normalised input, sigma the per-column
+    // deviation and m the number of rows: d_gain = row sums of delta * x_hat, d_bias = row sums of delta, and the gradient
+    // handed down is (g * m - rowsum(g) - x_hat * rowsum(g * x_hat)) / m / sigma with g = delta * gain - the reference's
+    // own formula, row sums included.
+    template <typename other_type>
+    mat_t<val_type> backward(const other_type& delta_in) {
+        if (!m_input.valid()) throw std::runtime_error("backward without a preceding forward");
+        mat_t<val_type> delta = delta_in;
+        mat_t<val_type> mean_row = vmean(m_input);
+        mat_t<val_type> centred = (m_input - mean_row).clone();
+        mat_t<val_type> sigma = sqrt(vmean(pow(centred, 2.0)));
+        mat_t<val_type> hx = (centred / sigma).clone();
+        mat_t<val_type> d_gain = hsum(delta * hx);
+        mat_t<val_type> d_bias = hsum(delta);
+        const val_type m = static_cast<val_type>(delta.row_num());
+        mat_t<val_type> g = (delta * m_gama).clone();
+        mat_t<val_type> sum_g = hsum(g);
+        mat_t<val_type> sum_g_hx = hsum(g * hx);
+        mat_t<val_type> down = ((g * m - sum_g - hx * sum_g_hx) / m / sigma).clone();
+        m_gama_updator.update(d_gain, m_gama);
+        m_beta_updator.update(d_bias, m_beta);
+        return down;
     }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "layer_norm_net_t"; }
     template <typename init_type>
@@ -185,7 +212,7 @@ public:
         init_matrix<init_type>(m_gama);
         init_matrix<init_type>(m_beta);
     }
-    void step() {}
+    void step() { m_gama_updator.step(); m_beta_updator.step(); }
     // gain and bias exist from the first forward on: a flag says whether the record holds them
     void save(std::ostream& os) const {
         const int32_t present = m_gama.valid() ? 1 : 0;
@@ -209,6 +236,11 @@ public:
     mat_t<val_type> forward(const any_input& input) {
         m_output = jsm_expr::along_axis(JSM_ROWS_SOFTMAX, 1, input);
         return m_output;
+    }
+    // y * (delta - rowsum(y * delta)) (reference: mat_net_t.hpp:281-285)
+    mat_t<val_type> backward(const mat_t<val_type>& delta) {
+        mat_t<val_type> dot_rows = hsum(m_output * delta);
+        return (m_output * (delta - dot_rows)).clone();
     }
     std::string net_type(int const& indent = 0) const { return print_indent(indent) + "hsoftmax_net_t"; }
     template <typename init_type>

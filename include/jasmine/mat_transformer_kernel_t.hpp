@@ -60,6 +60,11 @@ public:
         for (auto& layer : m_layers) input = layer.forward(input);
         return input;
     }
+    // Training step of the stack: the layers' backward steps in reverse order (reference: :112-119)
+    mat_t<val_type> backward(mat_t<val_type> delta) {
+        for (int i = (int)m_layers.size() - 1; i >= 0; --i) delta = m_layers[i].backward(delta);
+        return delta;
+    }
     // Generation with cached keys and values for a causal (decoder-only) stack: the output columns of the new input
     // columns, equal to the last columns of forward(whole prefix) - which is how the reference generates
     // (transformer_test.hpp:227-241) - at the cost of the new columns only.  Norms and feed-forward act per column.
@@ -112,7 +117,11 @@ public:
             get_ffn_norm(i).set_updator(args...);
         }
     }
-    void step() {}
+    void step() {
+        for (size_t i = 0; i < size(); ++i) {
+            get_mha(i).step(); get_mha_norm(i).step(); get_ffn(i).step(); get_ffn_norm(i).step();
+        }
+    }
 };
 
 template <typename val_type_, template <typename> class updator_type>

@@ -2,7 +2,6 @@
 // update(grad, mat) changes `mat` in place; the arithmetic is the reference's formula written with the same matrix
 // expressions, which here run as fused element-wise kernels on the device copy of the weights (float throughout: the
 // reference promotes the beta2 / epsilon terms to double, the results agree to float rounding).
-// The gradient-averaging wrapper cache_updator_t (reference: :172-218) is not provided.
 #ifndef JASMINE_B200_MAT_UPDATOR_T_HPP_
 #define JASMINE_B200_MAT_UPDATOR_T_HPP_
 #include "mat_express_t.hpp"
@@ -93,6 +92,36 @@ public:
         mat = (mat - step / (sqrt(v_hat) + s.eps)).clone();
     }
     void step() {}
+};
+
+// Averages the gradients of several backward passes and applies them with the wrapped updater at step()
+// (reference: mat_updator_t.hpp:172-218): a running mean, cache = cache * (1 - 1/(n+1)) + grad / (n+1).
+template <typename val_type, template <typename> class updator_type>
+class cache_updator_t {
+    updator_type<val_type> m_updator;
+    mat_t<val_type> m_cache;
+    mat_t<val_type>* m_mat = nullptr;
+    val_type m_count = 0;
+
+public:
+    cache_updator_t(val_type learning_rate = val_type(0.001)) : m_updator(learning_rate) {}
+    void update(const mat_t<val_type>& grad, mat_t<val_type>& mat) {
+        if (m_mat == nullptr) {
+            m_cache = mat_t<val_type>(grad.row_num(), grad.col_num());
+            m_mat = &mat;
+        }
+        m_cache = (m_cache * (val_type(1.0) - val_type(1.0) / val_type(m_count + 1)) + grad / val_type(m_count + 1)).clone();
+        m_count += 1;
+    }
+    void step() {
+        if (m_mat == nullptr) return;
+        m_updator.update(m_cache, *m_mat);
+        m_cache = val_type(0);
+        m_count = 0;
+    }
+    void set_lr(val_type lr) { m_updator.set_lr(lr); }
+    template <typename... upr_arg_types>
+    void set(val_type learning_rate, upr_arg_types&&... args) { m_updator.set(learning_rate, std::forward<upr_arg_types>(args)...); }
 };
 
 #endif

@@ -30,6 +30,8 @@ static F next_value() {
     g_state = g_state * 1664525u + 1013904223u;
     return (F)((g_state >> 8) & 0xFFFF) / 32768.0f - 1.0f;
 }
+template <typename T>
+using averaged_sgd_t = cache_updator_t<T, sgd_t>;
 // every weight of a net, in the API's fixed order, through the init_t customisation point
 struct seeded_t;
 template <>
@@ -308,6 +310,86 @@ int main() {
             }
             dump("train_adam_out", net.forward(tx));
             dump("train_adam_grad_in", down);
+        }
+        {
+            // a layer norm inside the chain: its gain and bias train too (mat_net_t.hpp:227-243)
+            using net_t = complex_net_builder_t<F>::push_back_updatable<weight_net_t, sgd_t>::push_back_updatable<layer_norm_net_t, sgd_t>::
+                push_back_updatable<weight_net_t, sgd_t>::type;
+            net_t net;
+            net.reinit(std::vector<int>{6, 7, 4});
+            net.init_weight<seeded_t>();
+            net.set_updator(0.02f);
+            mse_loss_t<M> loss;
+            M down;
+            for (int it = 0; it < 4; ++it) {
+                loss.forward(net.forward(tx));
+                down = net.backward(loss.backward(ty));
+            }
+            dump("train_layer_norm_out", net.forward(tx));
+            dump("train_layer_norm_grad_in", down);
+        }
+        {
+            hsoftmax_net_t<M> hs;
+            M sx = make(5, 6);
+            hs.forward(sx);
+            dump("hsoftmax_backward", hs.backward(make(5, 6)));
+        }
+        {
+            // gradients of two backward passes averaged, applied at step() (mat_updator_t.hpp:172-218)
+            weight_net_t<M, averaged_sgd_t> net(6, 4);
+            net.init_weight<seeded_t>();
+            net.set_updator(0.1f);
+            mse_loss_t<M> loss;
+            M tx2 = make(6, 5);
+            for (int round = 0; round < 2; ++round) {
+                loss.forward(net.forward(tx));
+                net.backward(loss.backward(ty));
+                loss.forward(net.forward(tx2));
+                net.backward(loss.backward(ty));
+                net.step();
+            }
+            dump("train_averaged_out", net.forward(tx));
+        }
+        {
+            cosine_annealing_decay sched(40, 8, 1e-3, 1e-5, 0.25, 2.0, 0.5);
+            M lrs(1, 40);
+            int n = 0;
+            do {
+                lrs(0, n++) = (F)(sched.get_lr() * 1000.0);
+            } while (sched.step() && n < 40);
+            dump("cosine_schedule", lrs);
+            dump_scalar("cosine_cycles", sched.get_total_cycle() * 100 + sched.get_current_cycle());
+        }
+        {
+            // self attention and a causal two-layer stack: backward through softmax, the per-head projections, the layer
+            // norms and the residual connections (mat_mha_t.hpp:92-117, 324-346; mat_transformer_kernel_t.hpp:112-119).
+            // One head: the reference's backward of every further head goes through a transposed view with a row offset,
+            // whose element access adds the row offset to the column and the column offset to the row
+            // (mat_view_t.hpp:29-39), so it reads another head's gradient rows.
+            M ax = make(8, 5), target = make(8, 5);
+            mse_loss_t<M> loss;
+            M down;
+            mat_mha_t<M, sgd_t> att(1, 8, true, 5);
+            att.init_weight<seeded_t>();
+            att.set_updator(0.05f);
+            for (int it = 0; it < 3; ++it) {
+                loss.forward(att.forward(ax));
+                down = att.backward(loss.backward(target));
+                att.step();
+            }
+            dump("train_mha_out", att.forward(ax));
+            dump("train_mha_grad_in", down);
+            encoder_t<F, sgd_t> stack(2, 1, 8, 5);
+            for (int i = 0; i < 2; ++i) stack.get_mha(i).set_param(1, 8, true, 5);
+            stack.init_weight<seeded_t>();
+            stack.set_updator(0.02f);
+            for (int it = 0; it < 3; ++it) {
+                loss.forward(stack.forward(ax));
+                down = stack.backward(loss.backward(target));
+                stack.step();
+            }
+            dump("train_stack_out", stack.forward(ax));
+            dump("train_stack_grad_in", down);
         }
         // (sigmoid_net_t::backward is left out: the reference's version, mat_net_t.hpp:108-116, keeps an expression that
         // refers to a temporary of the previous statement and reads freed memory when optimised.)

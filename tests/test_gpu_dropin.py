@@ -47,7 +47,7 @@ def test_program_output_equals_the_reference(tmp_path):
     exact = {"add", "chain", "axpb", "bcast_col", "bcast_row", "scalar_left", "greater", "less", "relu_expr", "plus_assign", "convert",
              "elem_of_expr", "hmax", "max", "pow2", "sqrt", "view", "transpose", "back_col", "row", "view_expr", "assign", "dot", "dot_t",
              "dot_chain", "dot_plus", "dot_error", "weight_net", "relu_net", "mlp", "mlp_fold", "residual", "mha_error", "vsplit_mid", "vconcat",
-             "split_concat_errors", "save_load"}
+             "split_concat_errors", "save_load", "cosine_schedule", "cosine_cycles"}
     for name, w in want.items():
         g = got[name]
         assert g.shape == w.shape, name

@@ -83,30 +83,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
     int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     constexpr int D = 128;
     chain_trigger();
+    chain_wait();
     const int chunk = blockIdx.x, hk = blockIdx.y, seq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c_begin = chunk * chunk_len;
-    // What does not come from the predecessor kernel (the qkv projection) is requested BEFORE the wait for it: the context
-    // length (written at the start of the step by a kernel that lets its dependents start only after its writes), the
-    // page of the chunk's first keys (read before the length is known: the entry exists whatever it holds, it is used only
-    // if the chunk has keys) and the rotation entries of the query's position.  Their round trips overlap the tail of
-    // the projection; after the wait only the queries themselves are one round trip away from the first K/V rows.
+    // The loads that do not depend on one another go out together: the context length, the page of the chunk's first
+    // keys (read before the length is known: the entry exists whatever it holds, it is used only if the chunk has keys)
+    // and the raw query heads.  One memory round trip instead of three on the way to the first K/V rows.
     const int32_t* bt = block_table + (long long)seq * max_pages;
     const int ks = lane >> 4;          // which of the two keys of a warp load
     const int dsub = (lane & 15) * 8;  // this lane's 8 dims
     const int first_base = c_begin + warp * (2 * DEC_UNROLL);
     const int page_first = first_base / JSM_PAGE_SIZE < max_pages ? bt[first_base / JSM_PAGE_SIZE] : 0;
-    const int ctx = context_lens[seq];
-    if (c_begin >= ctx) return;
-    float4 rot[4];
-    if (rope) {
-#pragma unroll
-        for (int p = 0; p < 4; ++p) rot[p] = rope[(long long)(ctx - 1) * (D / 2) + dsub / 2 + p];
-    }
-    chain_wait();
     uint4 q_raw[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) q_raw[g] = *reinterpret_cast<const uint4*>(q + seq * q_stride + (long long)(hk * G + g) * D + dsub);
+    const int ctx = context_lens[seq];
+    if (c_begin >= ctx) return;
     const int c_end = min(ctx, c_begin + chunk_len);
     if (FUSED && k_new && ctx - 1 >= c_begin) {  // ctx - 1 < c_end always: this CTA owns the newest position
         const int pos = ctx - 1;
@@ -163,7 +156,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(
         if (rope) {
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-                const float4 e = rot[p];
+                const float4 e = rope[(long long)(ctx - 1) * (D / 2) + dsub / 2 + p];
                 const float x0 = qf[g][2 * p], x1 = qf[g][2 * p + 1];
                 // rounded to bf16 like a stored, rotated q would be
                 const uint32_t pk = pack_bf16x2(__fadd_rn(__fmul_rn(e.x, x0), __fmul_rn(-e.w, x1)),

@@ -166,8 +166,11 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
 // else one.  Producer and MMA issuer walk the same sequence.
 __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok && left >= 2) ? 2 : 1; }
 
-// CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it
-template <int BN, bool CL>
+// CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it.
+// TP: the instantiation contains the fused tensor-parallel exchange (push / reduce).  Code that a launch never runs still
+// costs it: the larger image made the one-GPU decode step 2 % slower (tails run once per launch and fetch their
+// instructions cold), so launches without an exchange run an image without it.
+template <int BN, bool CL, bool TP>
 __global__ void __launch_bounds__(PK_THREADS, 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -264,7 +267,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     } else if (warp == 6) {
         // ---- X producer: the token blocks of every stage, once the predecessor kernel has written them --------------
         if (lane == 0) {
-            if (P.tp_mode == 2) {
+            if ((TP && P.tp_mode == 2)) {
                 // X is the residual stream that the first CTAs of this launch are completing (h += the ranks' slots).  Its
                 // readiness is announced through an epoch word, not by the end of the predecessor kernel; then the generic
                 // writes of the reducing CTAs are ordered before the copy engine's reads.  Nothing else the X producer
@@ -353,7 +356,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         int seg = 0, cl_syncs = 0;
         // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
         // predecessor now (the MMA warp is busy with the weight stream meanwhile) and prepare what does not need the accumulator.
-        if (P.tp_mode == 2) {
+        if ((TP && P.tp_mode == 2)) {
             // ---- tensor-parallel exchange, consumer side.  Every rank (this one included) has pushed its block of the
             // previous projection's output into its slot of this rank's buffer and released the exchange's epoch to this
             // rank's flag word for it.  The first CTAs of the launch (one per 128-column tile of h, while all CTAs stream
@@ -770,7 +773,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             } else {
                                 uint2 o;
                                 o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-                                if (P.tp_mode == 1) {
+                                if ((TP && P.tp_mode == 1)) {
                                     // this rank's block of every rank's exchange buffer (plain stores; peers over NVLink)
                                     if (valid) {
                                         const size_t off = ((size_t)t * P.N + n) * 2;
@@ -789,7 +792,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         }
                     }
                 }
-                if (do_fold && P.tp_mode == 1) {
+                if (do_fold && (TP && P.tp_mode == 1)) {
                     // The barrier orders every thread's slot stores before thread 0, which releases them (device scope) through
                     // the launch's counter.  The CTA that completes the launch has thereby acquired every other CTA's stores;
                     // ONE system-scope fence then orders all of them before the epoch it stores (relaxed) into every rank's
@@ -959,7 +962,7 @@ size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
 static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
-template <int BN, bool CL>
+template <int BN, bool CL, bool TP>
 static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
@@ -977,9 +980,9 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaFuncAttributes fa;
-        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL>));
+        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL, TP>));
         // 227 KB per CTA in all: what the kernel's static arrays leave is open to the stage ring
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
@@ -1007,7 +1010,7 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL>, mx, mx2, P));
+    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL, TP>, mx, mx2, P));
     g_launches.fetch_add(1);
     return JSM_OK;
 }
@@ -1096,16 +1099,23 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     // (from 32 tokens on every launch runs the cluster-capable image, with cluster size 1 where no cluster forms: one
     // kernel image per token block keeps the once-per-launch tail code warm in the instruction cache)
     const bool with_cl = cluster > 1 || a.T >= 32;
+    const bool with_tp = P.tp_mode != 0;  // (at most 64 tokens: checked above)
 #define PK_GO(BN_)                                                                                  \
-    return with_cl ? launch_packed<BN_, true>(mx, mx2, P, grid, cluster, a.chained, st)            \
-                   : launch_packed<BN_, false>(mx, mx2, P, grid, cluster, a.chained, st)
+    return with_cl ? launch_packed<BN_, true, false>(mx, mx2, P, grid, cluster, a.chained, st)     \
+                   : launch_packed<BN_, false, false>(mx, mx2, P, grid, cluster, a.chained, st)
+#define PK_GO_TP(BN_)                                                                                        \
+    if (with_tp)                                                                                             \
+        return with_cl ? launch_packed<BN_, true, true>(mx, mx2, P, grid, cluster, a.chained, st)           \
+                       : launch_packed<BN_, false, true>(mx, mx2, P, grid, cluster, a.chained, st);        \
+    PK_GO(BN_)
     switch (bn) {
-        case 16: PK_GO(16);
-        case 32: PK_GO(32);
-        case 64: PK_GO(64);
+        case 16: PK_GO_TP(16);
+        case 32: PK_GO_TP(32);
+        case 64: PK_GO_TP(64);
         case 128: PK_GO(128);
         default: PK_GO(256);
     }
+#undef PK_GO_TP
 #undef PK_GO
 }
 

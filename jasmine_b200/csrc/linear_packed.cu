@@ -37,7 +37,7 @@ constexpr int PK_TILE_BYTES = 128 * 64 * 2;  // one packed unit: 128 rows x 64 k
 constexpr int PK_THREADS = 224;
 constexpr int PK_MAX_STAGES = 12;
 
-__device__ __forceinline__ float pk_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
+__device__ __noinline__ float pk_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
 __device__ __forceinline__ float pk_silu(float x) { return x / (1.0f + __expf(-x)); }
 
 // 1-D bulk copy global -> shared (this CTA), completion counted in bytes on `bar`; both addresses 16-byte aligned
@@ -188,9 +188,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_flag;
     __shared__ int is_last_smem[2];
-    __shared__ float pair_smem[64 * 17];  // paired epilogue: up values of 16 token columns, padded rows
-    __shared__ float row_scale[256];      // 1 / rms of every token when the RMSNorm is fused into this projection
-    __shared__ float ssq_part[4 * 256];   // per-warp sums of squares of a whole tile's outputs
+    // ROWS: whole tiles that do not end the CTA's range take the row-per-thread epilogue straight from the accumulator (the
+    // stage ring is busy).  The few-token image has a staging tile of its own instead and sends every whole tile through
+    // the vectorised epilogue: one epilogue, a third less code to fetch in the tail that runs once per launch.
+    constexpr bool ROWS = BN >= 32;
+    __shared__ float pair_smem[ROWS ? 64 * 17 : 1];   // paired epilogue: up values of 16 token columns, padded rows
+    __shared__ float row_scale[256];                  // 1 / rms of every token when the RMSNorm is fused into this projection
+    __shared__ float ssq_part[ROWS ? 4 * 256 : 1];    // per-warp sums of squares of a whole tile's outputs
+    __shared__ __align__(16) float stage_small[ROWS ? 4 : 16 * 128];  // few-token image: a whole tile's accumulator
     __shared__ int tp_ok_smem;            // reduce: every peer's flag arrived in time
 
     chain_trigger();
@@ -512,8 +517,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             // A whole tile that is this CTA's last segment goes through shared memory (the stage ring is free: every MMA
             // of the CTA has completed) and the vectorised epilogue below, whose stores are 8 or 16 bytes per thread and
             // contiguous per token; earlier segments overlap the main loop and keep the row-per-thread epilogue.
-            const bool local = whole && (u + len == u_end) && P.local_epi;
+            const bool local = whole && (!ROWS || ((u + len == u_end) && P.local_epi));
+            bool rows_done = false;
+            if constexpr (ROWS) {
             if (whole && !local) {
+                rows_done = true;
                 // ---- the tile is complete in this CTA: epilogue straight from the accumulator
                 if (!P.paired) {
                     const int n = tile * 128 + row;
@@ -589,12 +597,15 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            } else {
+            }
+            }
+            if (!rows_done) {
                 // ---- shared tile: store the raw partial in this CTA's slot, the last contributor folds
                 // aligned split: the contributors are the CTAs of this cluster and the partial goes to this CTA's own shared
                 // memory (the stage ring is free: every MMA of the CTA has completed); otherwise to its workspace slot
                 const bool cl = CL && P.cluster_s > 1 && !local;
-                float* part_smem = reinterpret_cast<float*>(tiles);
+                float* part_smem = (!ROWS && local) ? stage_small : reinterpret_cast<float*>(tiles);
+                if (!ROWS && local) asm volatile("bar.sync 1, 128;" ::: "memory");  // the previous tile's fold has read the staging tile
                 const bool to_smem = cl || local || solo;
                 if (BN >= 32 && to_smem) {
                     // 32 columns per round trip to tensor memory
@@ -750,16 +761,20 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         float sc4[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) sc4[i] = (scaled && tb + TS * i < t_hi) ? row_scale[tb + TS * i] : 1.0f;
-#pragma unroll
+                        // one copy of the epilogue's code for the four tokens: the loop stays rolled and the tokens' registers
+                        // move up by one after each (a dozen moves; the code is fetched once per launch, cold)
+#pragma unroll 1
                         for (int i = 0; i < 4; ++i) {
                             const int t = tb + TS * i;
                             if (t >= t_hi) break;
-                            const float sc = sc4[i];
-                            float v[4] = {g[i].x * sc + bias4.x, g[i].y * sc + bias4.y, g[i].z * sc + bias4.z, g[i].w * sc + bias4.w};
-                            const float uu[4] = {up[i].x * sc, up[i].y * sc, up[i].z * sc, up[i].w * sc};
+                            const float sc = sc4[0];
+                            float v[4] = {g[0].x * sc + bias4.x, g[0].y * sc + bias4.y, g[0].z * sc + bias4.z, g[0].w * sc + bias4.w};
+                            const float uu[4] = {up[0].x * sc, up[0].y * sc, up[0].z * sc, up[0].w * sc};
                             if (P.epilogue == LIN_RESIDUAL) {
-                                v[0] += bf16lo(rr[i].x); v[1] += bf16hi(rr[i].x); v[2] += bf16lo(rr[i].y); v[3] += bf16hi(rr[i].y);
+                                v[0] += bf16lo(rr[0].x); v[1] += bf16hi(rr[0].x); v[2] += bf16lo(rr[0].y); v[3] += bf16hi(rr[0].y);
                             }
+#pragma unroll
+                            for (int q = 0; q < 3; ++q) { g[q] = g[q + 1]; up[q] = up[q + 1]; rr[q] = rr[q + 1]; sc4[q] = sc4[q + 1]; }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 if (P.paired) v[j] = pk_silu(v[j]) * uu[j];

@@ -135,16 +135,13 @@ __device__ __forceinline__ unsigned long long global_ns() {
     } while (0)
 
 // unit range of CTA c: [c*U/G, (c+1)*U/G)
-// (32-bit division where the products fit: a 64-bit division is a routine of about a hundred instructions)
-__host__ __device__ inline long long pk_begin(long long c, long long U, long long G) {
-    if ((U + 1) * G < (1ll << 31)) return (long long)((unsigned)(c * U) / (unsigned)G);
-    return c * U / G;
-}
+__host__ __device__ inline long long pk_begin(long long c, long long U, long long G) { return c * U / G; }
 // CTA that owns unit u: the largest c with c*U/G <= u
-__host__ __device__ inline int pk_owner(long long u, long long U, long long G) {
-    if ((U + 1) * G < (1ll << 31)) return (int)(((unsigned)((u + 1) * G) + (unsigned)U - 1u) / (unsigned)U) - 1;
-    return (int)(((u + 1) * G + U - 1) / U - 1);
-}
+__host__ __device__ inline int pk_owner(long long u, long long U, long long G) { return (int)(((u + 1) * G + U - 1) / U - 1); }
+// The kernel's own copies in 32-bit arithmetic (a 64-bit division is a routine of about a hundred instructions, and the
+// kernel's code is fetched cold by every launch).  The host checks (U + 1) * (G + 1) < 2^31 before it launches.
+__device__ __forceinline__ int pk_begin32(unsigned c, unsigned U, unsigned G) { return (int)(c * U / G); }
+__device__ __forceinline__ int pk_owner32(unsigned u, unsigned U, unsigned G) { return (int)(((u + 1u) * G + U - 1u) / U) - 1; }
 
 // ---- thread-block cluster helpers: the CTAs that share a tile exchange their partials through distributed shared memory
 __device__ __forceinline__ void cluster_sync_all() {
@@ -202,8 +199,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = P.stages;
-    const long long U = (long long)P.n_tiles * P.kbt, G = gridDim.x;
-    const long long u_begin = pk_begin(blockIdx.x, U, G), u_end = pk_begin(blockIdx.x + 1, U, G);
+    const unsigned U = (unsigned)(P.n_tiles * P.kbt), G = gridDim.x;
+    const int u_begin = pk_begin32(blockIdx.x, U, G), u_end = pk_begin32(blockIdx.x + 1, U, G);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -235,7 +232,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             // weights first: the ring is filled with W before the predecessor kernel has finished (constant weights);
             // the X blocks of the same stages follow once it has
             // loop state kept incrementally (k-block within the tile, stage, phase): no division per request
-            int rem = (int)(u_end - u_begin), kb = (int)(u_begin % P.kbt);
+            int rem = u_end - u_begin, kb = u_begin % P.kbt;
             int i = 0, s = 0;
             uint32_t ph = 0;
             const uint8_t* src = wsrc;
@@ -250,12 +247,10 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 ++i;
                 if (++s == stages) { s = 0; ph ^= 1; }
             };
-            if (P.w_early)
-                while (rem > 0 && i < stages) issue();
-            PK_TRACE(1);  // first ring of W requested
-            while (rem > 0) {
+            while (rem > 0) {  // the first ring goes out at once: before the predecessor kernel has finished
                 if (i >= stages && !mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, P.err, TC_TIMEOUT_EMPTY)) break;
                 issue();
+                if (i == stages) PK_TRACE(1);  // first ring of W requested
             }
             const int issued = i;
             if (abort_flag) {  // let the copies in flight land before the CTA exits (bounded)
@@ -282,7 +277,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 pk_fence_proxy_async();
             } else chain_wait();
             PK_TRACE(2);  // predecessor complete (fused exchange: h complete)
-            int rem = (int)(u_end - u_begin), kb = (int)(u_begin % P.kbt);
+            int rem = u_end - u_begin, kb = u_begin % P.kbt;
             int i = 0, s = 0;
             uint32_t ph = 0;
             while (rem > 0) {
@@ -311,7 +306,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             bool ok = true;
             int it = 0, seg = 0, s = 0;
             uint32_t ph = 0;
-            int rem = (int)(u_end - u_begin), kb0 = (int)(u_begin % P.kbt);
+            int rem = u_end - u_begin, kb0 = u_begin % P.kbt;
             while (rem > 0 && ok) {
                 const int len = min(P.kbt - kb0, rem);
                 const int buf = seg & 1;
@@ -457,9 +452,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         // weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile sums of squares that
         // the kernel which wrote x left behind (added in tile order).
         if (P.ssq_in) {
+#pragma unroll 1
             for (int t = etid; t < P.T; t += 128) {
                 float q = 0.0f;
                 int j = 0;
+#pragma unroll 1
                 for (; j + 8 <= P.ssq_in_tiles; j += 8) {  // eight loads in flight, added in tile order
                     float v8[8];
 #pragma unroll
@@ -467,16 +464,17 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
 #pragma unroll
                     for (int k = 0; k < 8; ++k) q += v8[k];
                 }
+#pragma unroll 1
                 for (; j < P.ssq_in_tiles; ++j) q += __ldcg(P.ssq_in + (size_t)j * P.ssq_stride + t);
                 row_scale[t] = 1.0f / sqrtf(q * P.inv_d + P.eps);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }  // cluster barriers this thread has taken part in (two per CTA, whatever happens)
-        long long u = u_begin;
+        int u = u_begin;
         while (u < u_end && ok) {
-            const int tile = (int)(u / P.kbt);
-            const int kb0 = (int)(u % P.kbt);
-            const int len = (int)min((long long)(P.kbt - kb0), u_end - u);
+            const int tile = u / P.kbt;
+            const int kb0 = u - tile * P.kbt;
+            const int len = min(P.kbt - kb0, u_end - u);
             const int buf = seg & 1;
             // A shared tile that ends this CTA's range: if every other contributor has already arrived at the tile counter
             // (the usual case: they hold the tile's later k-blocks as their FIRST segment), this CTA is the one that folds,
@@ -486,9 +484,9 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             // shares the tile (two 64-bit divisions) and this thread's place in the vectorised epilogue.  The tail after
             // the last MMA runs once per launch on four warps, so every instruction moved out of it shortens the launch.
             const bool whole = (len == P.kbt);
-            const long long uf = (long long)tile * P.kbt;
-            const int c_first = whole ? (int)blockIdx.x : pk_owner(uf, U, G);
-            const int c_last = whole ? (int)blockIdx.x : pk_owner(uf + P.kbt - 1, U, G);
+            const int uf = tile * P.kbt;
+            const int c_first = whole ? (int)blockIdx.x : pk_owner32((unsigned)uf, U, G);
+            const int c_last = whole ? (int)blockIdx.x : pk_owner32((unsigned)(uf + P.kbt - 1), U, G);
             const int n_contrib = c_last - c_first + 1;
             const int slot = (int)blockIdx.x - c_first;
             const int gshift = P.paired ? 4 : 5;  // 16 or 32 groups of 4 features per tile
@@ -652,8 +650,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                     // reading all partials in slot order; the second barrier keeps the shared memory alive until all have read.
                     cluster_sync_all();
                     ++cl_syncs;
-                    t_lo = (int)((long long)slot * P.T / n_contrib);
-                    t_hi = (int)((long long)(slot + 1) * P.T / n_contrib);
+                    t_lo = slot * P.T / n_contrib;
+                    t_hi = (slot + 1) * P.T / n_contrib;
                     do_fold = true;
                 } else {
                     // release / acquire through the tile counter: the barrier orders every thread's partial stores before the
@@ -670,17 +668,18 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                     do_fold = is_last_smem[seg & 1] != 0;
                 }
                 if (do_fold) {
-                    // A thread owns 4 consecutive output features of every TS-th token; the partials of four tokens are in
-                    // flight at once and the slots are added in slot order.  Plain tiles: a warp shares its tokens (32 groups
+                    // A thread owns 4 consecutive output features of every TS-th token; the partials of NT tokens (four; two in the
+                    // few-token image, which keeps its code short) are in flight at once and the slots are added in slot order.  Plain tiles: a warp shares its tokens (32 groups
                     // of 4 features), so the per-token sum of squares is one warp reduction.
                     const int n = n_f;
                     const bool valid = valid_f;
                     const uint32_t part_addr = smem_u32(part_smem);
-                    for (int tb = t_lo + tsub; tb < t_hi; tb += 4 * TS) {  // warp-uniform trip count for plain tiles
-                        float4 g[4], up[4];
-                        uint2 rr[4];
+                    constexpr int NT = BN >= 32 ? 4 : 2;
+                    for (int tb = t_lo + tsub; tb < t_hi; tb += NT * TS) {  // warp-uniform trip count for plain tiles
+                        float4 g[NT], up[NT];
+                        uint2 rr[NT];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
+                        for (int i = 0; i < NT; ++i) {
                             g[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                             up[i] = g[i];
                             rr[i] = make_uint2(0u, 0u);
@@ -689,7 +688,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         }
                         if (valid && local) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
+                            for (int i = 0; i < NT; ++i) {
                                 const int t = tb + TS * i;
                                 if (t < t_hi) {
                                     g[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4);
@@ -703,7 +702,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             for (int z = 0; z < n_contrib; ++z) {
                                 const uint32_t zbase = dsmem_addr(part_addr, (uint32_t)z);
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
+                                for (int i = 0; i < NT; ++i) {
                                     const int t = tb + TS * i;
                                     if (t < t_hi) {
                                         const uint32_t ra = zbase + (uint32_t)(t * 128 + f4) * 4u;
@@ -718,12 +717,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             }
                         }
                         if (valid && !cl && !local) {
-                            // workspace partials (L2 round trips): slots in batches of four, two (few-token launches) or four tokens at a time; all loads of a
-                            // batch are issued before the first add, so a batch costs one round trip; the adds run in slot order
-                            constexpr int TOKB = BN >= 32 ? 4 : 2;  // more tokens in flight where the fold is long
-#pragma unroll
-                            for (int ip = 0; ip < 4; ip += TOKB) {
-                                if (tb + TS * ip >= t_hi) break;
+                            // workspace partials (L2 round trips): slots in batches of four for all NT tokens; all loads of a batch
+                            // are issued before the first add, so a batch costs one round trip; the adds run in slot order
+                            constexpr int TOKB = NT, ip = 0;
+                            {
+#pragma unroll 1
                                 for (int zb = 0; zb < n_contrib; zb += 4) {
                                     float4 a[4][TOKB], c[4][TOKB];
 #pragma unroll
@@ -758,28 +756,39 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 }
                             }
                         }
-                        float sc4[4];
+                        float sc4[NT];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) sc4[i] = (scaled && tb + TS * i < t_hi) ? row_scale[tb + TS * i] : 1.0f;
+                        for (int i = 0; i < NT; ++i) sc4[i] = (scaled && tb + TS * i < t_hi) ? row_scale[tb + TS * i] : 1.0f;
                         // one copy of the epilogue's code for the four tokens: the loop stays rolled and the tokens' registers
                         // move up by one after each (a dozen moves; the code is fetched once per launch, cold)
 #pragma unroll 1
-                        for (int i = 0; i < 4; ++i) {
+                        for (int i = 0; i < NT; ++i) {
                             const int t = tb + TS * i;
                             if (t >= t_hi) break;
                             const float sc = sc4[0];
                             float v[4] = {g[0].x * sc + bias4.x, g[0].y * sc + bias4.y, g[0].z * sc + bias4.z, g[0].w * sc + bias4.w};
-                            const float uu[4] = {up[0].x * sc, up[0].y * sc, up[0].z * sc, up[0].w * sc};
+                            float uu[4] = {up[0].x * sc, up[0].y * sc, up[0].z * sc, up[0].w * sc};
                             if (P.epilogue == LIN_RESIDUAL) {
                                 v[0] += bf16lo(rr[0].x); v[1] += bf16hi(rr[0].x); v[2] += bf16lo(rr[0].y); v[3] += bf16hi(rr[0].y);
                             }
 #pragma unroll
-                            for (int q = 0; q < 3; ++q) { g[q] = g[q + 1]; up[q] = up[q + 1]; rr[q] = rr[q + 1]; sc4[q] = sc4[q + 1]; }
+                            for (int q = 0; q < NT - 1; ++q) { g[q] = g[q + 1]; up[q] = up[q + 1]; rr[q] = rr[q + 1]; sc4[q] = sc4[q + 1]; }
+                            if (P.paired) {
+#pragma unroll 1
+                                for (int j = 0; j < 4; ++j) {  // one copy of the division: the values take turns in v[0]
+                                    const float y = pk_silu(v[0]) * uu[0];
+                                    v[0] = v[1]; v[1] = v[2]; v[2] = v[3]; v[3] = y;
+                                    uu[0] = uu[1]; uu[1] = uu[2]; uu[2] = uu[3];
+                                }
+                            } else if (P.epilogue == LIN_RELU) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (P.paired) v[j] = pk_silu(v[j]) * uu[j];
-                                else if (P.epilogue == LIN_RELU) v[j] = fmaxf(v[j], 0.0f);
-                                else if (P.epilogue == LIN_GELU) v[j] = pk_gelu(v[j]);
+                                for (int j = 0; j < 4; ++j) v[j] = fmaxf(v[j], 0.0f);
+                            } else if (P.epilogue == LIN_GELU) {
+#pragma unroll 1
+                                for (int j = 0; j < 4; ++j) {  // one call site: the values take turns in v[0]
+                                    const float y = pk_gelu(v[0]);
+                                    v[0] = v[1]; v[1] = v[2]; v[2] = v[3]; v[3] = y;
+                                }
                             }
                             float sq = 0.0f;
                             if (P.out_f32) {
@@ -1051,6 +1060,8 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     const int grid = linear_packed_grid(a.N, a.K, paired, a.T);
     P.max_slots = linear_packed_slots(a.N, a.K, paired, a.T);
     const long long U = (long long)P.n_tiles * P.kbt;
+    if ((U + 1) * ((long long)grid + 1) >= (1ll << 31))  // the kernel partitions the units in 32-bit arithmetic
+        JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: %lld units of work on %d CTAs exceed one launch (a packed matrix of tens of gigabytes)", U, grid);
     const bool shared_tiles = (U % grid) != 0 || ((U / grid) % P.kbt) != 0;
     if (shared_tiles) {
         if (!a.ws || !a.counters)

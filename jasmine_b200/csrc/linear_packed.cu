@@ -186,13 +186,13 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     __shared__ int abort_flag;
     __shared__ int is_last_smem[2];
     // ROWS: whole tiles that do not end the CTA's range take the row-per-thread epilogue straight from the accumulator (the
-    // stage ring is busy).  The few-token image has a staging tile of its own instead and sends every whole tile through
-    // the vectorised epilogue: one epilogue, a third less code to fetch in the tail that runs once per launch.
-    constexpr bool ROWS = BN >= 32;
+    // stage ring is busy).  The images of up to 64 tokens have a staging tile of their own instead and send every whole
+    // tile through the vectorised epilogue: one epilogue, a third less code to fetch in the tail that runs once per launch.
+    constexpr bool ROWS = BN >= 128;
     __shared__ float pair_smem[ROWS ? 64 * 17 : 1];   // paired epilogue: up values of 16 token columns, padded rows
     __shared__ float row_scale[256];                  // 1 / rms of every token when the RMSNorm is fused into this projection
     __shared__ float ssq_part[ROWS ? 4 * 256 : 1];    // per-warp sums of squares of a whole tile's outputs
-    __shared__ __align__(16) float stage_small[ROWS ? 4 : 16 * 128];  // few-token image: a whole tile's accumulator
+    __shared__ __align__(16) float stage_small[ROWS ? 4 : BN * 128];  // up to 64 tokens: a whole tile's accumulator
     __shared__ int tp_ok_smem;            // reduce: every peer's flag arrived in time
 
     chain_trigger();

@@ -38,7 +38,7 @@ constexpr int PK_THREADS = 224;
 constexpr int PK_MAX_STAGES = 12;
 
 __device__ __noinline__ float pk_gelu(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); }
-__device__ __forceinline__ float pk_silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float pk_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }  // 2 ulp division: short code
 
 // 1-D bulk copy global -> shared (this CTA), completion counted in bytes on `bar`; both addresses 16-byte aligned
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 }
 #pragma unroll 1
                 for (; j < P.ssq_in_tiles; ++j) q += __ldcg(P.ssq_in + (size_t)j * P.ssq_stride + t);
-                row_scale[t] = 1.0f / sqrtf(q * P.inv_d + P.eps);
+                row_scale[t] = rsqrtf(q * P.inv_d + P.eps);  // 2 ulp; the exact 1 / sqrt costs 1.7 KB of code in every launch
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }  // cluster barriers this thread has taken part in (two per CTA, whatever happens)

@@ -680,22 +680,28 @@ def main():
         packed_sets.append(jb.linear_pack(w, ffn_l, paired=True))
         del w
 
-    def stream_once(i):
-        jb.check(jb.lib().jsm_linear_bf16_packed(x.data_ptr(), packed_sets[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16,
-                                                 B, ffn_l, d, jb.stream_ptr()))
-    for i in range(4):
-        stream_once(i)
-    torch.cuda.synchronize()
-    n_launch = 96
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for i in range(n_launch):
-        stream_once(i % 4)
-    r1.record()
-    torch.cuda.synchronize()
-    k_ms = r0.elapsed_time(r1) / n_launch
+    def stream_once(i, fn):
+        jb.check(fn(x.data_ptr(), packed_sets[i].data_ptr(), None, 3, None, y.data_ptr(), jb.BF16, B, ffn_l, d, jb.stream_ptr()))
+
+    def time_launches(fn, n_launch=96):
+        for i in range(4):
+            stream_once(i, fn)
+        torch.cuda.synchronize()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for i in range(n_launch):
+            stream_once(i % 4, fn)
+        r1.record()
+        torch.cuda.synchronize()
+        return r0.elapsed_time(r1) / n_launch
+
+    # launched the way the decode step launches it (jsm_linear_bf16_packed_chained: every launch a link of a kernel chain,
+    # resident and requesting its first weights while its predecessor finishes), and as plain stream-ordered launches
+    k_ms = time_launches(jb.lib().jsm_linear_bf16_packed_chained)
+    k_ms_plain = time_launches(jb.lib().jsm_linear_bf16_packed)
     alg_bytes = 2 * ffn_l * d * 2 + B * d * 2 + B * ffn_l * 2
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+    achieved_plain = alg_bytes / (k_ms_plain * 1e-3) / 1e9
     # the same kernel inside the step (chained launches: its ring is full of weights when its predecessor ends): device
     # time stamps of one eager step, predecessor end -> last CTA done, mean over the gate/up launches of the layers
     in_step = None
@@ -734,7 +740,12 @@ def main():
                      "traffic_note": "measured under ncu for one launch of this kernel at 8 tokens on one GPU; null for any other shape",
                      "kernel": "linear_packed_kernel: gate/up projection weight stream (jsm_linear_bf16_packed, silu*up epilogue)",
                      "peak_source": f"{peak_kind} HBM copy bandwidth", "ms_per_launch": k_ms, "bytes_per_launch": alg_bytes,
-                     "timed": "isolated launches of the kernel (CUDA events, 96 launches over 4 rotating weight sets)",
+                     "timed": "this kernel alone, CUDA events around 96 back-to-back launches over 4 rotating weight sets, launched as "
+                              "the decode step launches it (jsm_linear_bf16_packed_chained: programmatic dependent launch, a launch "
+                              "sets up and requests its first weights during its predecessor's tail); elapsed / launches",
+                     "plain_launches": {"ms_per_launch": k_ms_plain, "achieved": achieved_plain, "frac": achieved_plain / peak,
+                                        "how": "the same 96 launches through jsm_linear_bf16_packed (plain stream order: each "
+                                               "launch starts after its predecessor has ended)"},
                      "in_step": in_step},
         "step_roofline": dict(step_roofline(B, ms / K, head["ctx_mid"]),
                               note="all streamed weights (every projection and lm_head) + cached K/V of the step over the measured step time"),

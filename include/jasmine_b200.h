@@ -197,6 +197,14 @@ jsm_status jsm_linear_pack(const void* d_W, int N, int K, int paired, void* d_pa
 jsm_status jsm_linear_unpack(const void* d_packed, int N, int K, int paired, void* d_W, void* stream);
 jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_packed, const float* d_bias, int epilogue,
                                   const void* d_R, void* d_Y, int out_dtype, int T, int N, int K, void* stream);
+/* The same call launched as a link of a kernel chain (programmatic dependent launch), which is how the decoder runner
+ * launches its projections: the kernel may become resident and fetch its first weights while the kernel before it in
+ * the stream is still finishing, and waits for that kernel only before it touches X, R, Y or the workspace.  The caller
+ * promises that no work earlier in the stream that may still be running writes d_packed (weights that are packed once
+ * and then only read: inference).  Same results, bit for bit; back-to-back projections overlap their set-up and first
+ * weight requests with the predecessor's tail.  JSM_PDL=0 makes it the plain call. */
+jsm_status jsm_linear_bf16_packed_chained(const void* d_X, const void* d_packed, const float* d_bias, int epilogue,
+                                          const void* d_R, void* d_Y, int out_dtype, int T, int N, int K, void* stream);
 
 /* Timeline of the packed projections (profiling aid, off by default; the reference has no tracing).  Between
  * jsm_trace_begin and jsm_trace_end every launch of the packed projection kernel (up to max_launches, eager launches

@@ -82,6 +82,7 @@ SYMBOLS = {
     "jsm_linear_packed_reserve": (_i, [_i, _i, _i]),
     "jsm_linear_unpack": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "jsm_linear_bf16_packed": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "jsm_linear_bf16_packed_chained": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "jsm_rope_table": (_i, [_vp, _i, _i, _f, _i, _vp]),
     "jsm_rope_apply": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _i, _vp]),
     "jsm_rope_apply_qk": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
@@ -247,12 +248,12 @@ def linear_unpack(packed, N: int, K: int, paired: bool = False):
     return W
 
 
-def linear_bf16_packed(X, packed, out, bias=None, epilogue=0, residual=None):
+def linear_bf16_packed(X, packed, out, bias=None, epilogue=0, residual=None, chained=False):
     T, K = X.shape
     N = out.shape[1]
-    check(lib().jsm_linear_bf16_packed(X.data_ptr(), packed.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                       epilogue, residual.data_ptr() if residual is not None else None, out.data_ptr(),
-                                       dtype_of(out), T, N, K, stream_ptr()))
+    fn = lib().jsm_linear_bf16_packed_chained if chained else lib().jsm_linear_bf16_packed
+    check(fn(X.data_ptr(), packed.data_ptr(), bias.data_ptr() if bias is not None else None, epilogue,
+             residual.data_ptr() if residual is not None else None, out.data_ptr(), dtype_of(out), T, N, K, stream_ptr()))
     return out
 
 

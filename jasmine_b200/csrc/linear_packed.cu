@@ -1242,8 +1242,8 @@ extern "C" jsm_status jsm_linear_unpack(const void* d_packed, int N, int K, int 
     return linear_pack_launch(d_W, N, K, paired ? 1 : 0, const_cast<void*>(d_packed), true, as_stream(stream));
 }
 
-extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_packed, const float* d_bias, int epilogue, const void* d_R,
-                                             void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
+static jsm_status linear_bf16_packed_entry(const void* d_X, const void* d_packed, const float* d_bias, int epilogue, const void* d_R,
+                                           void* d_Y, int out_dtype, int T, int N, int K, void* stream, bool chained) {
     if (out_dtype != JSM_BF16 && out_dtype != JSM_F32) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16_packed: out dtype %d", out_dtype);
     if (T <= 0 || N <= 0) return JSM_OK;
     int dev = -1;
@@ -1253,7 +1253,7 @@ extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_pack
     const int paired = epilogue == LIN_SILU_MUL ? 1 : 0;
     PackedArgs a;
     a.X = d_X; a.Wp = d_packed; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.out_f32 = out_dtype == JSM_F32;
-    a.N = N; a.K = K; a.x_row_stride = 0; a.chained = false;
+    a.N = N; a.K = K; a.x_row_stride = 0; a.chained = chained;
     {
         // the workspace of this device, sized at set-up time (jsm_linear_pack / jsm_linear_packed_reserve); the launch
         // checks its capacity and fails rather than allocate
@@ -1273,6 +1273,16 @@ extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_pack
         if (s != JSM_OK) return s;
     }
     return JSM_OK;
+}
+
+extern "C" jsm_status jsm_linear_bf16_packed(const void* d_X, const void* d_packed, const float* d_bias, int epilogue, const void* d_R,
+                                             void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
+    return linear_bf16_packed_entry(d_X, d_packed, d_bias, epilogue, d_R, d_Y, out_dtype, T, N, K, stream, false);
+}
+
+extern "C" jsm_status jsm_linear_bf16_packed_chained(const void* d_X, const void* d_packed, const float* d_bias, int epilogue,
+                                                     const void* d_R, void* d_Y, int out_dtype, int T, int N, int K, void* stream) {
+    return linear_bf16_packed_entry(d_X, d_packed, d_bias, epilogue, d_R, d_Y, out_dtype, T, N, K, stream, true);
 }
 
 // ---- the fused exchange on its own (what the decoder runner composes; also how the protocol is tested on one GPU) ----

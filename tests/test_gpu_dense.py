@@ -143,6 +143,32 @@ def test_linear_packed_against_the_oracle(T, N, K):
     assert_close(host(Y), want, 2e-3, f"packed vs oracle T={T} N={N} K={K}")
 
 
+def test_linear_packed_chained_launches_give_the_same_bits():
+    """jsm_linear_bf16_packed_chained (each launch a link of a kernel chain: resident and fetching weights while its
+    predecessor finishes) against the plain call: a chain of projections that feed one another, results bit-equal."""
+    T, d, ffn = 8, 1024, 2816
+    X, Wgu = make_xw(T, 2 * ffn, d, 190)
+    _, Wd = make_xw(T, d, ffn, 191)
+    jb.fill(Wgu, 190, 1, 0, 0.0, 0.01)           # small weights: the update is quadratic in h and must stay bounded
+    jb.fill(Wd, 191, 1, 0, 0.0, 0.01)
+    Pgu, Pd = jb.linear_pack(Wgu, ffn, paired=True), jb.linear_pack(Wd, d)
+
+    def run(chained):
+        h = X.clone()
+        act = torch.empty(T, ffn, device="cuda", dtype=torch.bfloat16)
+        for _ in range(6):                       # h += down(silu(gate(h)) * up(h)), six times back to back
+            jb.linear_bf16_packed(h, Pgu, act, epilogue=3, chained=chained)
+            jb.linear_bf16_packed(act, Pd, h, epilogue=4, residual=h, chained=chained)
+        jb.check_device_errors()
+        return h
+
+    with torch.cuda.stream(torch.cuda.Stream()):
+        plain, chained = run(False), run(True)
+        torch.cuda.current_stream().synchronize()
+    assert torch.isfinite(plain.float()).all()
+    assert torch.equal(plain, chained)
+
+
 def test_linear_packed_needs_a_reserved_workspace():
     """The compute call never allocates: a packed image that did not come from jsm_linear_pack on this device (loaded
     from a file, say) needs jsm_linear_packed_reserve once, at set-up time; without it the call is refused."""

@@ -65,7 +65,6 @@ struct PkParams {
     int* counters;        // [n_tiles], zero between launches
     int max_slots;
     int* err;
-    int w_early;          // weights may be fetched before the predecessor kernel has finished
     int pf_units;         // units beyond the ring that are prefetched into L2 up front
     int stages;
     int cluster_s;        // > 1: aligned split, the cluster_s CTAs of a tile form a cluster and fold through shared memory
@@ -167,7 +166,7 @@ __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok
 // TP: the instantiation contains the fused tensor-parallel exchange (push / reduce).  Code that a launch never runs still
 // costs it: the larger image made the one-GPU decode step 2 % slower (tails run once per launch and fetch their
 // instructions cold), so launches without an exchange run an image without it.
-template <int BN, bool CL, bool TP>
+template <int BN, bool CL, bool TP, int PRM>
 __global__ void __launch_bounds__(PK_THREADS, 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -195,6 +194,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     __shared__ __align__(16) float stage_small[ROWS ? 4 : BN * 128];  // up to 64 tokens: a whole tile's accumulator
     __shared__ int tp_ok_smem;            // reduce: every peer's flag arrived in time
 
+    // PRM: 1 / 0 = an image for gate/up pairs only / for plain tiles only (what the other kind needs is not in it), -1 = both
+    const bool paired = PRM < 0 ? P.paired != 0 : PRM == 1;
     chain_trigger();
     if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -351,7 +352,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // packed row of the tile = TMEM lane
         const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
-        const bool want_ssq = P.ssq_out != nullptr;  // plain tiles only (checked on the host)
+        const bool want_ssq = !paired && P.ssq_out != nullptr;  // plain tiles only (checked on the host)
         bool ok = true;
         int seg = 0, cl_syncs = 0;
         // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
@@ -481,7 +482,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             // and its own partial need not travel through the workspace - it stays in shared memory.  The counter is read
             // while the accumulator is still being produced.
             // Everything about the segment that does not need the accumulator is worked out before the wait for it: who
-            // shares the tile (two 64-bit divisions) and this thread's place in the vectorised epilogue.  The tail after
+            // shares the tile (two divisions) and this thread's place in the vectorised epilogue.  The tail after
             // the last MMA runs once per launch on four warps, so every instruction moved out of it shortens the launch.
             const bool whole = (len == P.kbt);
             const int uf = tile * P.kbt;
@@ -489,11 +490,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             const int c_last = whole ? (int)blockIdx.x : pk_owner32((unsigned)(uf + P.kbt - 1), U, G);
             const int n_contrib = c_last - c_first + 1;
             const int slot = (int)blockIdx.x - c_first;
-            const int gshift = P.paired ? 4 : 5;  // 16 or 32 groups of 4 features per tile
+            const int gshift = paired ? 4 : 5;  // 16 or 32 groups of 4 features per tile
             const int f4 = (etid & ((1 << gshift) - 1)) * 4, tsub = etid >> gshift, TS = 128 >> gshift;
-            const int n_f = (P.paired ? tile * 64 : tile * 128) + f4;
+            const int n_f = (paired ? tile * 64 : tile * 128) + f4;
             const bool valid_f = n_f < P.N;
-            const float4 bias4 = (P.bias && !P.paired && valid_f) ? *reinterpret_cast<const float4*>(P.bias + n_f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 bias4 = (P.bias && !paired && valid_f) ? *reinterpret_cast<const float4*>(P.bias + n_f) : make_float4(0.f, 0.f, 0.f, 0.f);
             const size_t slot_stride = (size_t)P.T * 128;
             const float* tbase = P.ws + (size_t)tile * P.max_slots * slot_stride;
             float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * slot_stride;
@@ -521,7 +522,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             if (whole && !local) {
                 rows_done = true;
                 // ---- the tile is complete in this CTA: epilogue straight from the accumulator
-                if (!P.paired) {
+                if (!paired) {
                     const int n = tile * 128 + row;
                     const bool valid = n < P.N;
                     const float bias = (P.bias && valid) ? P.bias[n] : 0.0f;
@@ -540,7 +541,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 v += bias;
                                 if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
                                 else if (P.epilogue == LIN_GELU) v = pk_gelu(v);
-                                else if (P.epilogue == LIN_RESIDUAL && valid) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
+                                else if ((!paired && P.epilogue == LIN_RESIDUAL) && valid) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
                                 float stored = v;
                                 if (!P.out_f32) {
                                     const __nv_bfloat16 hb = __float2bfloat16_rn(v);
@@ -684,7 +685,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             up[i] = g[i];
                             rr[i] = make_uint2(0u, 0u);
                             const int t = tb + TS * i;
-                            if (P.epilogue == LIN_RESIDUAL && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                            if ((!paired && P.epilogue == LIN_RESIDUAL) && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
                         }
                         if (valid && local) {
 #pragma unroll
@@ -692,12 +693,12 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 const int t = tb + TS * i;
                                 if (t < t_hi) {
                                     g[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4);
-                                    if (P.paired) up[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
+                                    if (paired) up[i] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
                                 }
                             }
                         }
                         if (valid && cl) {
-                            // shared-memory partials of the cluster: short latency, four tokens in flight, adds in slot order
+                            // shared-memory partials of the cluster: short latency, NT tokens in flight, adds in slot order
 #pragma unroll 4
                             for (int z = 0; z < n_contrib; ++z) {
                                 const uint32_t zbase = dsmem_addr(part_addr, (uint32_t)z);
@@ -708,7 +709,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                         const uint32_t ra = zbase + (uint32_t)(t * 128 + f4) * 4u;
                                         const float4 av = ld_dsmem_f4(ra);
                                         g[i].x += av.x; g[i].y += av.y; g[i].z += av.z; g[i].w += av.w;
-                                        if (P.paired) {
+                                        if (paired) {
                                             const float4 cv = ld_dsmem_f4(ra + 256u);
                                             up[i].x += cv.x; up[i].y += cv.y; up[i].z += cv.z; up[i].w += cv.w;
                                         }
@@ -735,11 +736,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                             if (t < t_hi && z < n_contrib) {
                                                 if (solo && z == slot) {
                                                     a[zz][ii] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4);
-                                                    if (P.paired) c[zz][ii] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
+                                                    if (paired) c[zz][ii] = *reinterpret_cast<const float4*>(part_smem + t * 128 + f4 + 64);
                                                 } else {
                                                     const float* w = tbase + z * slot_stride + (size_t)t * 128 + f4;
                                                     a[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w));
-                                                    if (P.paired) c[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w + 64));
+                                                    if (paired) c[zz][ii] = __ldcg(reinterpret_cast<const float4*>(w + 64));
                                                 }
                                             }
                                         }
@@ -759,7 +760,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         float sc4[NT];
 #pragma unroll
                         for (int i = 0; i < NT; ++i) sc4[i] = (scaled && tb + TS * i < t_hi) ? row_scale[tb + TS * i] : 1.0f;
-                        // one copy of the epilogue's code for the four tokens: the loop stays rolled and the tokens' registers
+                        // one copy of the epilogue's code for the NT tokens: the loop stays rolled and the tokens' registers
                         // move up by one after each (a dozen moves; the code is fetched once per launch, cold)
 #pragma unroll 1
                         for (int i = 0; i < NT; ++i) {
@@ -768,12 +769,12 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             const float sc = sc4[0];
                             float v[4] = {g[0].x * sc + bias4.x, g[0].y * sc + bias4.y, g[0].z * sc + bias4.z, g[0].w * sc + bias4.w};
                             float uu[4] = {up[0].x * sc, up[0].y * sc, up[0].z * sc, up[0].w * sc};
-                            if (P.epilogue == LIN_RESIDUAL) {
+                            if ((!paired && P.epilogue == LIN_RESIDUAL)) {
                                 v[0] += bf16lo(rr[0].x); v[1] += bf16hi(rr[0].x); v[2] += bf16lo(rr[0].y); v[3] += bf16hi(rr[0].y);
                             }
 #pragma unroll
                             for (int q = 0; q < NT - 1; ++q) { g[q] = g[q + 1]; up[q] = up[q + 1]; rr[q] = rr[q + 1]; sc4[q] = sc4[q + 1]; }
-                            if (P.paired) {
+                            if (paired) {
 #pragma unroll 1
                                 for (int j = 0; j < 4; ++j) {  // one copy of the division: the values take turns in v[0]
                                     const float y = pk_silu(v[0]) * uu[0];
@@ -986,7 +987,7 @@ size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
 static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
-template <int BN, bool CL, bool TP>
+template <int BN, bool CL, bool TP, int PRM = -1>
 static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
@@ -1004,13 +1005,12 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaFuncAttributes fa;
-        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL, TP>));
+        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL, TP, PRM>));
         // 227 KB per CTA in all: what the kernel's static arrays leave is open to the stage ring
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL, TP, PRM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
-    P.w_early = chained ? 1 : 0;
     P.pf_units = 0;
     P.cluster_s = cluster > 1 ? cluster : 0;
     cudaLaunchConfig_t cfg = {};
@@ -1034,7 +1034,7 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL, TP>, mx, mx2, P));
+    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL, TP, PRM>, mx, mx2, P));
     g_launches.fetch_add(1);
     return JSM_OK;
 }
@@ -1134,6 +1134,10 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         return with_cl ? launch_packed<BN_, true, true>(mx, mx2, P, grid, cluster, a.chained, st)           \
                        : launch_packed<BN_, false, true>(mx, mx2, P, grid, cluster, a.chained, st);        \
     PK_GO(BN_)
+    // the few-token launches without an exchange (the decode step of one GPU): an image per kind of tile
+    if (bn == 16 && !with_cl && !with_tp)
+        return paired ? launch_packed<16, false, false, 1>(mx, mx2, P, grid, cluster, a.chained, st)
+                      : launch_packed<16, false, false, 0>(mx, mx2, P, grid, cluster, a.chained, st);
     switch (bn) {
         case 16: PK_GO_TP(16);
         case 32: PK_GO_TP(32);

@@ -194,8 +194,17 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     __shared__ __align__(16) float stage_small[ROWS ? 4 : BN * 128];  // up to 64 tokens: a whole tile's accumulator
     __shared__ int tp_ok_smem;            // reduce: every peer's flag arrived in time
 
-    // PRM: 1 / 0 = an image for gate/up pairs only / for plain tiles only (what the other kind needs is not in it), -1 = both
-    const bool paired = PRM < 0 ? P.paired != 0 : PRM == 1;
+    // PRM: what the image can do.  -1: everything; 0 / 1: plain tiles only / gate-up pairs only (what the other kind needs is
+    // not in it); 2, 3, 4: exactly one projection of a LLaMA-style decoder step each - 2: plain tiles, fused RMSNorm row
+    // scale, no bias, no activation, bf16 out (qkv); 3: plain tiles, residual added, per-tile sums of squares written, bf16
+    // out (wo, down); 4: gate-up pairs with the row scale, bf16 out.  The host picks the image from the arguments; a launch
+    // pays for the size of its image, so the common launches get the smallest ones.
+    constexpr bool FIX = PRM >= 2;
+    const bool paired = PRM < 0 ? P.paired != 0 : (PRM == 1 || PRM == 4);
+    const bool has_ssq_in = FIX ? PRM != 3 : P.ssq_in != nullptr;
+    const bool f32o = FIX ? false : P.out_f32 != 0;
+    const float* const biasp = FIX ? nullptr : P.bias;
+    const int epi = FIX ? (PRM == 3 ? LIN_RESIDUAL : PRM == 4 ? LIN_SILU_MUL : LIN_NONE) : P.epilogue;
     chain_trigger();
     if (threadIdx.x == 0) PK_TRACE(0);  // CTA resident
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -352,7 +361,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         const int quad = warp & 3;
         const int row = quad * 32 + lane;  // packed row of the tile = TMEM lane
         const int etid = threadIdx.x - 64; // 0..127 within the epilogue warps
-        const bool want_ssq = !paired && P.ssq_out != nullptr;  // plain tiles only (checked on the host)
+        const bool want_ssq = FIX ? PRM == 3 : (!paired && P.ssq_out != nullptr);  // plain tiles only (checked on the host)
         bool ok = true;
         int seg = 0, cl_syncs = 0;
         // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
@@ -452,7 +461,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         // Row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into the packed
         // weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile sums of squares that
         // the kernel which wrote x left behind (added in tile order).
-        if (P.ssq_in) {
+        if (has_ssq_in) {
 #pragma unroll 1
             for (int t = etid; t < P.T; t += 128) {
                 float q = 0.0f;
@@ -494,7 +503,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             const int f4 = (etid & ((1 << gshift) - 1)) * 4, tsub = etid >> gshift, TS = 128 >> gshift;
             const int n_f = (paired ? tile * 64 : tile * 128) + f4;
             const bool valid_f = n_f < P.N;
-            const float4 bias4 = (P.bias && !paired && valid_f) ? *reinterpret_cast<const float4*>(P.bias + n_f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 bias4 = (biasp && !paired && valid_f) ? *reinterpret_cast<const float4*>(biasp + n_f) : make_float4(0.f, 0.f, 0.f, 0.f);
             const size_t slot_stride = (size_t)P.T * 128;
             const float* tbase = P.ws + (size_t)tile * P.max_slots * slot_stride;
             float* wbase = P.ws + ((size_t)tile * P.max_slots + slot) * slot_stride;
@@ -511,7 +520,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             }
             if (!mbar_wait(&acc_full[buf], (seg >> 1) & 1, &abort_flag, P.err, TC_TIMEOUT_ACC)) { ok = false; break; }
             tc_fence_after();
-            const bool scaled = P.ssq_in != nullptr;
+            const bool scaled = has_ssq_in;
             const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
             // A whole tile that is this CTA's last segment goes through shared memory (the stage ring is free: every MMA
             // of the CTA has completed) and the vectorised epilogue below, whose stores are 8 or 16 bytes per thread and
@@ -525,7 +534,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 if (!paired) {
                     const int n = tile * 128 + row;
                     const bool valid = n < P.N;
-                    const float bias = (P.bias && valid) ? P.bias[n] : 0.0f;
+                    const float bias = (biasp && valid) ? biasp[n] : 0.0f;
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 16) {
                         if (c0 >= P.T) break;
@@ -539,11 +548,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 float v = __uint_as_float(r[j]);
                                 if (scaled) v *= row_scale[t];
                                 v += bias;
-                                if (P.epilogue == LIN_RELU) v = fmaxf(v, 0.0f);
-                                else if (P.epilogue == LIN_GELU) v = pk_gelu(v);
-                                else if ((!paired && P.epilogue == LIN_RESIDUAL) && valid) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
+                                if (epi == LIN_RELU) v = fmaxf(v, 0.0f);
+                                else if (epi == LIN_GELU) v = pk_gelu(v);
+                                else if ((!paired && epi == LIN_RESIDUAL) && valid) v += __bfloat162float(P.R[(size_t)t * P.N + n]);
                                 float stored = v;
-                                if (!P.out_f32) {
+                                if (!f32o) {
                                     const __nv_bfloat16 hb = __float2bfloat16_rn(v);
                                     stored = __bfloat162float(hb);
                                     if (valid) reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = hb;
@@ -585,7 +594,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 if (t < P.T) {
                                     const float sc = scaled ? row_scale[t] : 1.0f;
                                     const float v = pk_silu(__uint_as_float(r[j]) * sc) * (pair_smem[f * 17 + j] * sc);
-                                    if (P.out_f32) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
+                                    if (f32o) reinterpret_cast<float*>(P.Y)[(size_t)t * P.N + n] = v;
                                     else reinterpret_cast<__nv_bfloat16*>(P.Y)[(size_t)t * P.N + n] = __float2bfloat16_rn(v);
                                 }
                             }
@@ -685,7 +694,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             up[i] = g[i];
                             rr[i] = make_uint2(0u, 0u);
                             const int t = tb + TS * i;
-                            if ((!paired && P.epilogue == LIN_RESIDUAL) && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
+                            if ((!paired && epi == LIN_RESIDUAL) && valid && t < t_hi) rr[i] = *reinterpret_cast<const uint2*>(P.R + (size_t)t * P.N + n);
                         }
                         if (valid && local) {
 #pragma unroll
@@ -769,7 +778,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             const float sc = sc4[0];
                             float v[4] = {g[0].x * sc + bias4.x, g[0].y * sc + bias4.y, g[0].z * sc + bias4.z, g[0].w * sc + bias4.w};
                             float uu[4] = {up[0].x * sc, up[0].y * sc, up[0].z * sc, up[0].w * sc};
-                            if ((!paired && P.epilogue == LIN_RESIDUAL)) {
+                            if ((!paired && epi == LIN_RESIDUAL)) {
                                 v[0] += bf16lo(rr[0].x); v[1] += bf16hi(rr[0].x); v[2] += bf16lo(rr[0].y); v[3] += bf16hi(rr[0].y);
                             }
 #pragma unroll
@@ -781,10 +790,10 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                     v[0] = v[1]; v[1] = v[2]; v[2] = v[3]; v[3] = y;
                                     uu[0] = uu[1]; uu[1] = uu[2]; uu[2] = uu[3];
                                 }
-                            } else if (P.epilogue == LIN_RELU) {
+                            } else if (epi == LIN_RELU) {
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) v[j] = fmaxf(v[j], 0.0f);
-                            } else if (P.epilogue == LIN_GELU) {
+                            } else if (epi == LIN_GELU) {
 #pragma unroll 1
                                 for (int j = 0; j < 4; ++j) {  // one call site: the values take turns in v[0]
                                     const float y = pk_gelu(v[0]);
@@ -792,7 +801,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 }
                             }
                             float sq = 0.0f;
-                            if (P.out_f32) {
+                            if (f32o) {
                                 if (valid) *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.Y) + (size_t)t * P.N + n) = make_float4(v[0], v[1], v[2], v[3]);
                                 sq = (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
                             } else {
@@ -1135,9 +1144,16 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
                        : launch_packed<BN_, false, true>(mx, mx2, P, grid, cluster, a.chained, st);        \
     PK_GO(BN_)
     // the few-token launches without an exchange (the decode step of one GPU): an image per kind of tile
-    if (bn == 16 && !with_cl && !with_tp)
+    if (bn == 16 && !with_cl && !with_tp) {
+        const bool lean = !a.bias && !a.out_f32;  // the projections of a LLaMA-style decoder step have images of their own
+        if (lean && paired && a.ssq_in) return launch_packed<16, false, false, 4>(mx, mx2, P, grid, cluster, a.chained, st);
+        if (lean && !paired && a.epilogue == LIN_NONE && a.ssq_in && !a.ssq_out)
+            return launch_packed<16, false, false, 2>(mx, mx2, P, grid, cluster, a.chained, st);
+        if (lean && !paired && a.epilogue == LIN_RESIDUAL && !a.ssq_in && a.ssq_out)
+            return launch_packed<16, false, false, 3>(mx, mx2, P, grid, cluster, a.chained, st);
         return paired ? launch_packed<16, false, false, 1>(mx, mx2, P, grid, cluster, a.chained, st)
                       : launch_packed<16, false, false, 0>(mx, mx2, P, grid, cluster, a.chained, st);
+    }
     switch (bn) {
         case 16: PK_GO_TP(16);
         case 32: PK_GO_TP(32);

@@ -163,10 +163,10 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
 __device__ __forceinline__ int pk_chunk(int pair_ok, int left) { return (pair_ok && left >= 2) ? 2 : 1; }
 
 // CL: the instantiation contains the cluster path (launches of 32 tokens and more); the few-token kernel carries none of it.
-// TP: the instantiation contains the fused tensor-parallel exchange (push / reduce).  Code that a launch never runs still
-// costs it: the larger image made the one-GPU decode step 2 % slower (tails run once per launch and fetch their
-// instructions cold), so launches without an exchange run an image without it.
-template <int BN, bool CL, bool TP, int PRM>
+// TPM: what the instantiation contains of the fused tensor-parallel exchange (nothing / push / reduce / both).  Code that a
+// launch never runs still costs it - the step time follows the size of the image of every launch, 0.1 - 0.2 % per KB - so
+// launches without an exchange run an image without it, and the common launches have images of their own (PRM below).
+template <int BN, bool CL, int TPM, int PRM>
 __global__ void __launch_bounds__(PK_THREADS, 1)
     linear_packed_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x2, PkParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -199,9 +199,13 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     // scale, no bias, no activation, bf16 out (qkv); 3: plain tiles, residual added, per-tile sums of squares written, bf16
     // out (wo, down); 4: gate-up pairs with the row scale, bf16 out.  The host picks the image from the arguments; a launch
     // pays for the size of its image, so the common launches get the smallest ones.
+    // TPM: 0 = no tensor-parallel exchange in the image, 1 = it pushes its outputs, 2 = it reduces the ranks' slots into its
+    // token operand first, 3 = either, as the launch says.  PRM 5: the pushing projection (plain tiles, bf16, nothing else).
+    const bool tp_push = TPM == 1 || (TPM == 3 && P.tp_mode == 1);
+    const bool tp_reduce = TPM == 2 || (TPM == 3 && P.tp_mode == 2);
     constexpr bool FIX = PRM >= 2;
     const bool paired = PRM < 0 ? P.paired != 0 : (PRM == 1 || PRM == 4);
-    const bool has_ssq_in = FIX ? PRM != 3 : P.ssq_in != nullptr;
+    const bool has_ssq_in = FIX ? (PRM == 2 || PRM == 4) : P.ssq_in != nullptr;
     const bool f32o = FIX ? false : P.out_f32 != 0;
     const float* const biasp = FIX ? nullptr : P.bias;
     const int epi = FIX ? (PRM == 3 ? LIN_RESIDUAL : PRM == 4 ? LIN_SILU_MUL : LIN_NONE) : P.epilogue;
@@ -277,7 +281,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     } else if (warp == 6) {
         // ---- X producer: the token blocks of every stage, once the predecessor kernel has written them --------------
         if (lane == 0) {
-            if ((TP && P.tp_mode == 2)) {
+            if (tp_reduce) {
                 // X is the residual stream that the first CTAs of this launch are completing (h += the ranks' slots).  Its
                 // readiness is announced through an epoch word, not by the end of the predecessor kernel; then the generic
                 // writes of the reducing CTAs are ordered before the copy engine's reads.  Nothing else the X producer
@@ -366,7 +370,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
         int seg = 0, cl_syncs = 0;
         // R, Y, the row statistics, the workspace and the counters belong to the stream's other kernels: wait for the
         // predecessor now (the MMA warp is busy with the weight stream meanwhile) and prepare what does not need the accumulator.
-        if ((TP && P.tp_mode == 2)) {
+        if (tp_reduce) {
             // ---- tensor-parallel exchange, consumer side.  Every rank (this one included) has pushed its block of the
             // previous projection's output into its slot of this rank's buffer and released the exchange's epoch to this
             // rank's flag word for it.  The first CTAs of the launch (one per 128-column tile of h, while all CTAs stream
@@ -807,7 +811,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                             } else {
                                 uint2 o;
                                 o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-                                if ((TP && P.tp_mode == 1)) {
+                                if (tp_push) {
                                     // this rank's block of every rank's exchange buffer (plain stores; peers over NVLink)
                                     if (valid) {
                                         const size_t off = ((size_t)t * P.N + n) * 2;
@@ -826,7 +830,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         }
                     }
                 }
-                if (do_fold && (TP && P.tp_mode == 1)) {
+                if (do_fold && tp_push) {
                     // The barrier orders every thread's slot stores before thread 0, which releases them (device scope) through
                     // the launch's counter.  The CTA that completes the launch has thereby acquired every other CTA's stores;
                     // ONE system-scope fence then orders all of them before the epoch it stores (relaxed) into every rank's
@@ -996,7 +1000,7 @@ size_t linear_packed_ws_floats(int T, int N, int K, int paired) {
 static unsigned long long* g_trace_buf = nullptr;  // [launch][CTA][8]
 static int g_trace_cap = 0, g_trace_n = 0, g_trace_ctas = 0;
 
-template <int BN, bool CL, bool TP, int PRM = -1>
+template <int BN, bool CL, int TPM, int PRM = -1>
 static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, PkParams& P, int grid, int cluster, bool chained, cudaStream_t st) {
     constexpr int STAGE_BYTES = 2 * (PK_TILE_BYTES + BN * 128);
     // up to 64 tokens two CTAs share an SM (the successor kernel of a chain prefetches next to the running one)
@@ -1014,9 +1018,9 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaFuncAttributes fa;
-        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL, TP, PRM>));
+        JSM_CUDA_CHECK(cudaFuncGetAttributes(&fa, linear_packed_kernel<BN, CL, TPM, PRM>));
         // 227 KB per CTA in all: what the kernel's static arrays leave is open to the stage ring
-        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL, TP, PRM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        JSM_CUDA_CHECK(cudaFuncSetAttribute(linear_packed_kernel<BN, CL, TPM, PRM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             227 * 1024 - (int)fa.sharedSizeBytes));
         attr_done = true;
     }
@@ -1043,7 +1047,7 @@ static jsm_status launch_packed(const CUtensorMap& mx, const CUtensorMap& mx2, P
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL, TP, PRM>, mx, mx2, P));
+    JSM_CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_packed_kernel<BN, CL, TPM, PRM>, mx, mx2, P));
     g_launches.fetch_add(1);
     return JSM_OK;
 }
@@ -1136,23 +1140,28 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     const bool with_cl = cluster > 1 || a.T >= 32;
     const bool with_tp = P.tp_mode != 0;  // (at most 64 tokens: checked above)
 #define PK_GO(BN_)                                                                                  \
-    return with_cl ? launch_packed<BN_, true, false>(mx, mx2, P, grid, cluster, a.chained, st)     \
-                   : launch_packed<BN_, false, false>(mx, mx2, P, grid, cluster, a.chained, st)
+    return with_cl ? launch_packed<BN_, true, 0>(mx, mx2, P, grid, cluster, a.chained, st)     \
+                   : launch_packed<BN_, false, 0>(mx, mx2, P, grid, cluster, a.chained, st)
 #define PK_GO_TP(BN_)                                                                                        \
     if (with_tp)                                                                                             \
-        return with_cl ? launch_packed<BN_, true, true>(mx, mx2, P, grid, cluster, a.chained, st)           \
-                       : launch_packed<BN_, false, true>(mx, mx2, P, grid, cluster, a.chained, st);        \
+        return with_cl ? launch_packed<BN_, true, 3>(mx, mx2, P, grid, cluster, a.chained, st)           \
+                       : launch_packed<BN_, false, 3>(mx, mx2, P, grid, cluster, a.chained, st);        \
     PK_GO(BN_)
     // the few-token launches without an exchange (the decode step of one GPU): an image per kind of tile
     if (bn == 16 && !with_cl && !with_tp) {
         const bool lean = !a.bias && !a.out_f32;  // the projections of a LLaMA-style decoder step have images of their own
-        if (lean && paired && a.ssq_in) return launch_packed<16, false, false, 4>(mx, mx2, P, grid, cluster, a.chained, st);
+        if (lean && paired && a.ssq_in) return launch_packed<16, false, 0, 4>(mx, mx2, P, grid, cluster, a.chained, st);
         if (lean && !paired && a.epilogue == LIN_NONE && a.ssq_in && !a.ssq_out)
-            return launch_packed<16, false, false, 2>(mx, mx2, P, grid, cluster, a.chained, st);
+            return launch_packed<16, false, 0, 2>(mx, mx2, P, grid, cluster, a.chained, st);
         if (lean && !paired && a.epilogue == LIN_RESIDUAL && !a.ssq_in && a.ssq_out)
-            return launch_packed<16, false, false, 3>(mx, mx2, P, grid, cluster, a.chained, st);
-        return paired ? launch_packed<16, false, false, 1>(mx, mx2, P, grid, cluster, a.chained, st)
-                      : launch_packed<16, false, false, 0>(mx, mx2, P, grid, cluster, a.chained, st);
+            return launch_packed<16, false, 0, 3>(mx, mx2, P, grid, cluster, a.chained, st);
+        return paired ? launch_packed<16, false, 0, 1>(mx, mx2, P, grid, cluster, a.chained, st)
+                      : launch_packed<16, false, 0, 0>(mx, mx2, P, grid, cluster, a.chained, st);
+    }
+    if (bn == 16 && !with_cl && with_tp && !a.bias && !a.out_f32) {  // the decode step of a tensor-parallel rank
+        if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<16, false, 1, 5>(mx, mx2, P, grid, cluster, a.chained, st);  // (plain, nothing else: checked above)
+        if (paired) return launch_packed<16, false, 2, 4>(mx, mx2, P, grid, cluster, a.chained, st);
+        if (a.epilogue == LIN_NONE && !a.ssq_out) return launch_packed<16, false, 2, 2>(mx, mx2, P, grid, cluster, a.chained, st);
     }
     switch (bn) {
         case 16: PK_GO_TP(16);

@@ -415,12 +415,14 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 float sm[8];
 #pragma unroll
                                 for (int q = 0; q < 8; ++q) sm[q] = 0.0f;
+                                // rank order; one copy of the adds: the slots take turns in w[0] (short code, see the kernel's
+                                // template parameters)
+#pragma unroll 1
+                                for (int r = 0; r < P.tp_n; ++r) {
+                                    sm[0] += bf16lo(w[0].x); sm[1] += bf16hi(w[0].x); sm[2] += bf16lo(w[0].y); sm[3] += bf16hi(w[0].y);
+                                    sm[4] += bf16lo(w[0].z); sm[5] += bf16hi(w[0].z); sm[6] += bf16lo(w[0].w); sm[7] += bf16hi(w[0].w);
 #pragma unroll
-                                for (int r = 0; r < 8; ++r) {
-                                    if (r < P.tp_n) {
-                                        sm[0] += bf16lo(w[r].x); sm[1] += bf16hi(w[r].x); sm[2] += bf16lo(w[r].y); sm[3] += bf16hi(w[r].y);
-                                        sm[4] += bf16lo(w[r].z); sm[5] += bf16hi(w[r].z); sm[6] += bf16lo(w[r].w); sm[7] += bf16hi(w[r].w);
-                                    }
+                                    for (int q = 0; q < 7; ++q) w[q] = w[q + 1];
                                 }
                                 // the rank-local products were rounded to bf16 when they were pushed; their sum is rounded once
                                 // more (the all-reduce of a bf16 buffer) and then added to the residual stream
@@ -1158,6 +1160,23 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         return paired ? launch_packed<16, false, 0, 1>(mx, mx2, P, grid, cluster, a.chained, st)
                       : launch_packed<16, false, 0, 0>(mx, mx2, P, grid, cluster, a.chained, st);
     }
+    // 17 to 64 tokens without an exchange: the same three images per token block, with and without the cluster path
+    if ((bn == 32 || bn == 64) && !with_tp && !a.bias && !a.out_f32) {
+#define PK_LEAN(BN_, CL_)                                                                                                    \
+    do {                                                                                                                     \
+        if (paired && a.ssq_in) return launch_packed<BN_, CL_, 0, 4>(mx, mx2, P, grid, cluster, a.chained, st);              \
+        if (!paired && a.epilogue == LIN_NONE && a.ssq_in && !a.ssq_out)                                                     \
+            return launch_packed<BN_, CL_, 0, 2>(mx, mx2, P, grid, cluster, a.chained, st);                                  \
+        if (!paired && a.epilogue == LIN_RESIDUAL && !a.ssq_in && a.ssq_out)                                                 \
+            return launch_packed<BN_, CL_, 0, 3>(mx, mx2, P, grid, cluster, a.chained, st);                                  \
+    } while (0)
+        if (bn == 32) {
+            if (cluster > 1) PK_LEAN(32, true); else PK_LEAN(32, false);
+        } else {
+            if (cluster > 1) PK_LEAN(64, true); else PK_LEAN(64, false);
+        }
+#undef PK_LEAN
+    }
     if (bn == 16 && !with_cl && with_tp && !a.bias && !a.out_f32) {  // the decode step of a tensor-parallel rank
         if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<16, false, 1, 5>(mx, mx2, P, grid, cluster, a.chained, st);  // (plain, nothing else: checked above)
         if (paired) return launch_packed<16, false, 2, 4>(mx, mx2, P, grid, cluster, a.chained, st);
@@ -1279,7 +1298,6 @@ static jsm_status linear_bf16_packed_entry(const void* d_X, const void* d_packed
     JSM_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) JSM_FAIL(JSM_UNSUPPORTED, "jsm_linear_bf16_packed: device index %d", dev);
     cudaStream_t st = as_stream(stream);
-    const int paired = epilogue == LIN_SILU_MUL ? 1 : 0;
     PackedArgs a;
     a.X = d_X; a.Wp = d_packed; a.bias = d_bias; a.epilogue = epilogue; a.R = d_R; a.out_f32 = out_dtype == JSM_F32;
     a.N = N; a.K = K; a.x_row_stride = 0; a.chained = chained;

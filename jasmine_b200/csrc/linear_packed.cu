@@ -1136,9 +1136,9 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
             P.tp_mode = 2;
         }
     }
-    // the cluster path lives in instantiations of its own: launches without a cluster run a kernel that carries none of it
-    // (from 32 tokens on every launch runs the cluster-capable image, with cluster size 1 where no cluster forms: one
-    // kernel image per token block keeps the once-per-launch tail code warm in the instruction cache)
+    // A launch pays for the size of the image it runs.  The common launches of a decoder step (up to 64 tokens) have
+    // lean images of their own, chosen below; what remains runs the general images: with the cluster path from 32 tokens
+    // on (cluster size 1 where no cluster forms), with the exchange code when the launch pushes or reduces.
     const bool with_cl = cluster > 1 || a.T >= 32;
     const bool with_tp = P.tp_mode != 0;  // (at most 64 tokens: checked above)
 #define PK_GO(BN_)                                                                                  \

@@ -79,6 +79,8 @@ struct jsm_model {
     void* tp_regions[8] = {nullptr};
     int32_t* tp_state = nullptr;
     bool tp_connected = false;
+    unsigned long long* argmax_key = nullptr;  // split arg-max: best (value, index) key per row (self-resetting)
+    int32_t* argmax_ctr = nullptr;             // ... and the number of slices that have contributed
     float* best_val = nullptr;   // vocabulary-sharded lm_head: this rank's best logit per token
     int32_t* best_idx = nullptr;
     bool last_push = false;  // the last forward call exchanged by push (its final exchange is consumed by the logits projection)
@@ -286,6 +288,43 @@ __global__ void __launch_bounds__(256) row_ssq_kernel(const __nv_bfloat16* __res
     if (threadIdx.x == 0) ssq[blockIdx.x] = q;
 }
 
+// The start of a decode step in one launch: the bookkeeping of advance_kernel for sequence b = blockIdx.x, the embedding
+// row of its token and the row's sum of squares (what embedding_kernel and row_ssq_kernel do in two more launches; same
+// order of the additions).  Like advance_kernel it lets its dependents start only after its stores are in memory.
+__global__ void __launch_bounds__(256) decode_begin_kernel(int32_t* ctx, int32_t* pos, int32_t* seq_ids, int32_t* pass, int max_context,
+                                                           int* err, const __nv_bfloat16* __restrict__ table,
+                                                           const int32_t* __restrict__ ids, __nv_bfloat16* __restrict__ h,
+                                                           float* __restrict__ ssq, int d) {
+    __shared__ float smem[8];
+    chain_wait();
+    const int b = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int c = ctx[b];
+        if (c >= max_context) {
+            c = max_context - 1;
+            if (err) atomicCAS(err, 0, TC_CONTEXT_OVERFLOW);
+        }
+        pos[b] = c;
+        seq_ids[b] = b;
+        ctx[b] = c + 1;
+        if (b == 0 && pass) *pass = *pass + 1;
+    }
+    const __nv_bfloat16* src = table + (long long)ids[b] * d;
+    __nv_bfloat16* dst = h + (long long)b * d;
+    float q = 0.0f;
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+        const uint4 w = *reinterpret_cast<const uint4*>(src + c);
+        *reinterpret_cast<uint4*>(dst + c) = w;
+        const float f[8] = {bf16lo(w.x), bf16hi(w.x), bf16lo(w.y), bf16hi(w.y), bf16lo(w.z), bf16hi(w.z), bf16lo(w.w), bf16hi(w.w)};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q += f[j] * f[j];
+    }
+    q = block_sum_256(q, smem);
+    if (threadIdx.x == 0) ssq[b] = q;
+    __threadfence();
+    chain_trigger();
+}
+
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n) {
     __shared__ float sv[8];
     __shared__ int si[8];
@@ -310,6 +349,53 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
         for (int w = 1; w < 8; ++w)
             if (sv[w] > m || (sv[w] == m && si[w] < mi)) { m = sv[w]; mi = si[w]; }
         out[blockIdx.x] = mi == 0x7fffffff ? 0 : mi;
+    }
+}
+
+// The same arg-max with every row split over gridDim.x CTAs (a row of 32000 logits is too long for one CTA on the path of
+// a decode step): a slice's best (value, index) becomes one 64-bit key - the value's bits made monotone in the high word,
+// the complemented index in the low word, so that the larger key is the larger value and, among equal values, the lower
+// index - and goes into the row's key with atomicMax; the CTA that arrives last at the row's counter writes the token and
+// resets both words for the next launch.  Same result as argmax_rows_kernel (NaNs never win, all -inf gives 0).
+constexpr int ARGMAX_SPLIT = 16;
+__global__ void __launch_bounds__(256) argmax_rows_split_kernel(const float* __restrict__ x, int32_t* __restrict__ out, int n,
+                                                                unsigned long long* __restrict__ keys, int32_t* __restrict__ ctrs) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    chain_trigger();
+    chain_wait();
+    const int r = blockIdx.y;
+    const float* row = x + (long long)r * n;
+    const int lo = (int)((long long)blockIdx.x * n / gridDim.x), hi = (int)((long long)(blockIdx.x + 1) * n / gridDim.x);
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) {
+        const float v = row[i];
+        if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, m, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+        if (ov > m || (ov == m && oi < mi)) { m = ov; mi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = m; si[threadIdx.x >> 5] = mi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > m || (sv[w] == m && si[w] < mi)) { m = sv[w]; mi = si[w]; }
+        const uint32_t bits = __float_as_uint(m);
+        const uint32_t mono = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+        const unsigned long long key = ((unsigned long long)mono << 32) | (uint32_t)(0xffffffffu - (uint32_t)mi);
+        atomicMax(keys + r, key);
+        __threadfence();
+        if (atomicAdd(ctrs + r, 1) == (int)gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long best = atomicExch(keys + r, 0ull);  // (read and reset in one)
+            const uint32_t idx = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+            out[r] = idx == 0x7fffffffu ? 0 : (int32_t)idx;
+            ctrs[r] = 0;
+        }
     }
 }
 
@@ -486,13 +572,25 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
                       linear_packed_can_push(d, m->ffn_l, T);
     m->last_push = push;
     const bool stats = !tp || push;  // h carries row statistics instead of a normalised copy
-    jsm_status s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
+    jsm_status s = JSM_OK;
+    if (decode && stats && d % 8 == 0) {
+        // one launch: positions and context lengths of the step, the embedding rows and their statistics
+        JSM_CUDA_CHECK(launch_chained(decode_begin_kernel, dim3(batch), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, m->tp_state,
+                                      c.max_context, tc_error_word(), (const __nv_bfloat16*)m->emb, d_ids, m->h, m->ssq0, d));
+    } else {
+    if (decode) {
+        JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch,
+                                      m->tp_state, c.max_context, tc_error_word()));
+        JSM_LAUNCH_CHECK();
+    }
+    s = jsm_embedding(m->emb, nullptr, d_ids, nullptr, m->h, JSM_BF16, T, d, st);
     if (s != JSM_OK) return s;
     if (!stats) {
         JSM_CUDA_CHECK(launch_chained(fold_add_norm_kernel<2>, dim3(T), dim3(256), 0, st, m->h, nullptr, 0, 0, nullptr, nullptr,
                                       c.norm_eps, m->xn, d));
     } else {
         JSM_CUDA_CHECK(launch_chained(row_ssq_kernel, dim3(T), dim3(256), 0, st, (const __nv_bfloat16*)m->h, m->ssq0, d));
+    }
     }
     JSM_LAUNCH_CHECK();
     const __nv_bfloat16* x_in = stats ? m->h : m->xn;  // what the projections after a norm read
@@ -580,7 +678,11 @@ static jsm_status logits_and_argmax(jsm_model* m, int first, int rows, int T, in
     jsm_status s = run_linear(m, x, d, m->lm_head, m->c.vocab, d, LIN_NONE, nullptr, lg, true, rows, st, rs, T, push ? &f : nullptr);
     if (s != JSM_OK) return s;
     if (d_next) {
-        JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
+        if (rows <= m->c.max_batch && m->c.vocab >= 4096)
+            JSM_CUDA_CHECK(launch_chained(argmax_rows_split_kernel, dim3(ARGMAX_SPLIT, rows), dim3(256), 0, st, (const float*)lg, d_next,
+                                          m->c.vocab, m->argmax_key, m->argmax_ctr));
+        else
+            JSM_CUDA_CHECK(launch_chained(argmax_rows_kernel, dim3(rows), dim3(256), 0, st, (const float*)lg, d_next, m->c.vocab));
         JSM_LAUNCH_CHECK();
     }
     return JSM_OK;
@@ -747,6 +849,10 @@ static jsm_status llama_create_impl(const jsm_model_config* cfg, uint64_t seed, 
     JSM_TRY(dev_alloc(m, &m->attn_counters, (size_t)c.max_batch * m->Hkv_l));
     if (cudaMemset(m->attn_counters, 0, sizeof(int32_t) * c.max_batch * m->Hkv_l) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->logits, (size_t)c.max_batch * c.vocab));
+    JSM_TRY(dev_alloc(m, &m->argmax_key, (size_t)c.max_batch));
+    JSM_TRY(dev_alloc(m, &m->argmax_ctr, (size_t)c.max_batch));
+    if (cudaMemset(m->argmax_key, 0, sizeof(unsigned long long) * c.max_batch) != cudaSuccess ||
+        cudaMemset(m->argmax_ctr, 0, sizeof(int32_t) * c.max_batch) != cudaSuccess) { jsm_llama_destroy(m); JSM_FAIL(JSM_CUDA, "jsm_llama_create: memset failed"); }
     JSM_TRY(dev_alloc(m, &m->best_val, (size_t)c.max_batch));
     JSM_TRY(dev_alloc(m, &m->best_idx, (size_t)c.max_batch));
     JSM_TRY(dev_alloc(m, &m->ids_dev, (size_t)c.max_batch));
@@ -1007,10 +1113,7 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
     if (!m || !d_ids) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step: null argument");
     if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step: batch %d (1..%d)", batch, m->c.max_batch);
     cudaStream_t st = as_stream(stream);
-    JSM_CUDA_CHECK(launch_chained(advance_kernel, dim3((batch + 255) / 256), dim3(256), 0, st, m->ctx, m->pos, m->seq_ids, batch, m->tp_state,
-                                  m->c.max_context, tc_error_word()));
-    JSM_LAUNCH_CHECK();
-    jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);
+    jsm_status s = forward_tokens(m, d_ids, batch, true, batch, -1, st);  // (positions and context lengths advance in its first launch)
     if (s != JSM_OK) return s;
     return logits_and_argmax(m, 0, batch, batch, d_next, d_logits, st);
 }

@@ -1121,7 +1121,7 @@ jsm_status jsm_llama_decode_step(jsm_model* m, const int32_t* d_ids, int batch, 
 // The decode step for callers that hold their tokens in HOST memory (the reference's generation loop keeps everything
 // on the host, transformer_test.hpp:227-241): ids in, next tokens (and optionally logits) out.  The step itself is
 // captured once per batch size into a CUDA graph that the model owns (positions and context lengths live on the device,
-// so the same graph serves every step) and replayed: one graph launch instead of ~165 kernel launches per step.
+// so the same graph serves every step) and replayed: one graph launch instead of ~163 kernel launches per step.
 jsm_status jsm_llama_decode_step_host(jsm_model* m, const int32_t* h_ids, int batch, int32_t* h_next, float* h_logits, void* stream) {
     if (!m || !h_ids || !h_next) JSM_FAIL(JSM_INVALID_ARG, "jsm_llama_decode_step_host: null argument");
     if (batch <= 0 || batch > m->c.max_batch) JSM_FAIL(JSM_SHAPE, "jsm_llama_decode_step_host: batch %d (1..%d)", batch, m->c.max_batch);

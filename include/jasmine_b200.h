@@ -380,7 +380,12 @@ jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size,
  * of finished CTAs and reduced tiles, the epoch up to which h is reduced).  The ranks must run the same
  * sequence of (which_buffer alternating, site), epochs growing from call to call.  Workspace: as for
  * jsm_linear_bf16_packed (jsm_linear_pack / jsm_linear_packed_reserve).  A peer that does not arrive within the wait
- * limit leaves h as it is and raises JSM_TIMEOUT at the next jsm_check_device_errors. */
+ * limit leaves h as it is and raises JSM_TIMEOUT at the next jsm_check_device_errors.
+ * Exchanges of at most 16 tokens (T of the push and of the reduce, which must be the same) do not use the flags: the
+ * slot then holds 8-byte words {two bf16, epoch} - the epoch in a word says that the word has arrived, so the producer
+ * needs no counter of finished CTAs, no system-scope fence and no flag stores, and the consumer's load that polls is the
+ * load that fetches.  There a peer that stops in the middle of its pushes can leave the tiles that did arrive added to h
+ * (JSM_TIMEOUT is raised either way); a peer that never pushes leaves h as it is. */
 jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
                               int32_t* d_state, int site, int n_sites, const void* d_X, const void* d_packed, int T,
                               int N, int K, void* stream);

@@ -59,6 +59,12 @@ struct PackedArgs {
 };
 
 constexpr int TP_PUSH_MAX_T = 64;  // launches of at most this many tokens exchange by push; longer ones by the exchange kernel
+// Exchanges of at most this many tokens travel as 8-byte words {two bf16, epoch of the exchange} (4 bytes per element in
+// the slot): a word is written by one store, so its epoch says that the word has arrived - no flag, no fence, no counter of
+// finished CTAs on the producer's side, and the consumer's load that polls is the load that fetches.  Larger exchanges keep
+// plain bf16 slots and a flag per source rank (twice the bytes would cost them more than the flag does).  Producer and
+// consumer of an exchange must agree: both decide by the token count of the forward pass.
+constexpr int TP_INBAND_MAX_T = 16;
 struct TpFuse {
     int n_ranks = 0, rank = 0;
     const int* pass = nullptr;     // device: number of the forward pass
@@ -66,6 +72,7 @@ struct TpFuse {
     int* state = nullptr;          // device, local, 4 words, zero at first: [0] folding CTAs of a pushing launch done, [1] tiles of h
                                    // reduced (both self-resetting), [2] epoch up to which h is completely reduced
     // push
+    bool inband = false;           // {two bf16, epoch} words instead of bf16 slots and flags (TP_INBAND_MAX_T)
     bool push = false;
     void* push_dst[8] = {nullptr};   // per rank: where this rank's [T, N] block goes in that rank's memory
     int* push_flag[8] = {nullptr};   // per rank: that rank's flag word for this rank

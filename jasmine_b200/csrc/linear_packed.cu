@@ -82,6 +82,7 @@ struct PkParams {
     const int* tp_pass;
     int* tp_state;              // local: [0] folding CTAs done, [1] tiles of h reduced (self-resetting); [2] epoch up to which h is reduced
     int tp_expect;              // push: folding CTAs of this launch
+    int tp_inband;              // the pushed words carry the exchange's epoch ({two bf16, epoch} per 8 bytes): no flags
     uint8_t* tp_dst[8];
     int* tp_flag[8];
     const uint8_t* tp_slots;
@@ -105,6 +106,21 @@ __device__ __forceinline__ int pk_ld_acquire_gpu(const int* p) {
     return v;
 }
 __device__ __forceinline__ uint4 pk_ld_cg_v4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+// the words of an in-band exchange carry their own epoch: they are read and written with volatile (relaxed, system scope)
+// 16-byte accesses, each 8-byte half of which is one word
+__device__ __forceinline__ uint4 pk_ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int pk_ld_volatile(const void* p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void pk_st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 // generic-proxy writes to global memory (other CTAs' stores of h) before the copy engine's reads of the same bytes
 __device__ __forceinline__ void pk_fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 // One thread waits (bounded) until the word *p has reached epoch E; epochs only grow, the comparison is wrap-safe.  The
@@ -199,10 +215,12 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     // scale, no bias, no activation, bf16 out (qkv); 3: plain tiles, residual added, per-tile sums of squares written, bf16
     // out (wo, down); 4: gate-up pairs with the row scale, bf16 out.  The host picks the image from the arguments; a launch
     // pays for the size of its image, so the common launches get the smallest ones.
-    // TPM: 0 = no tensor-parallel exchange in the image, 1 = it pushes its outputs, 2 = it reduces the ranks' slots into its
-    // token operand first, 3 = either, as the launch says.  PRM 5: the pushing projection (plain tiles, bf16, nothing else).
-    const bool tp_push = TPM == 1 || (TPM == 3 && P.tp_mode == 1);
-    const bool tp_reduce = TPM == 2 || (TPM == 3 && P.tp_mode == 2);
+    // TPM: 0 = no tensor-parallel exchange in the image, 3 = push or reduce, with flags or in-band epochs, as the launch says,
+    // 4 = it pushes its outputs as in-band words, 5 = it reduces the ranks' in-band slots into its token operand first.
+    // PRM 5: the pushing projection (plain tiles, bf16, nothing else).
+    const bool tp_push = TPM == 4 || (TPM == 3 && P.tp_mode == 1);
+    const bool tp_reduce = TPM == 5 || (TPM == 3 && P.tp_mode == 2);
+    const bool tp_inband = BN == 16 && (TPM == 4 || TPM == 5 || (TPM == 3 && P.tp_inband != 0));  // (at most 16 tokens)
     constexpr bool FIX = PRM >= 2;
     const bool paired = PRM < 0 ? P.paired != 0 : (PRM == 1 || PRM == 4);
     const bool has_ssq_in = FIX ? (PRM == 2 || PRM == 4) : P.ssq_in != nullptr;
@@ -383,9 +401,13 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                 if (etid == 0) tp_ok_smem = 1;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid < P.tp_n) {
-                    const int* flag = P.tp_flags + etid;
+                    // flags: the rank's flag word.  In-band: the epoch of the first word of this CTA's tile in the rank's slot
+                    // (a cheap probe that keeps the polling traffic small; the loads below check every word they take)
+                    const int* flag = tp_inband ? reinterpret_cast<const int*>(P.tp_slots + (size_t)etid * P.tp_slot_stride +
+                                                                               (size_t)blockIdx.x * 128 * 4) + 1
+                                                : P.tp_flags + etid;
                     const long long t0 = clock64();
-                    while ((int)(pk_ld_acquire_sys(flag) - E) < 0) {
+                    while ((int)((tp_inband ? pk_ld_volatile(flag) : pk_ld_acquire_sys(flag)) - E) < 0) {
                         __nanosleep(64);
                         if (clock64() - t0 > P.tp_wait) {
                             tp_ok_smem = 0;
@@ -407,11 +429,39 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         if (in_range) {
                             const size_t off = ((size_t)t * P.K + c) * 2;
                             uint4 o = pk_ld_cg_v4(reinterpret_cast<const uint8_t*>(P.tp_h) + off);
-                            if (tp_ok) {
-                                uint4 w[8];
+                            bool ready = tp_ok;
+                            uint4 w[8];
+                            if (tp_ok && tp_inband) {
+                                // 8 bf16 of a slot = four words {two bf16, epoch} = 32 bytes; all ranks' loads go out together,
+                                // and again until every word is of this exchange (or later: the peers never run ahead by a
+                                // whole buffer cycle); the load that polls is the load that fetches
+                                const uint8_t* src = P.tp_slots + ((size_t)t * P.K + c) * 4;
+                                const long long t0 = clock64();
+                                while (true) {
+                                    int oldest = 0;
+#pragma unroll
+                                    for (int r = 0; r < 8; ++r) {
+                                        if (r < P.tp_n) {
+                                            const uint4 a = pk_ld_volatile_v4(src + (size_t)r * P.tp_slot_stride);
+                                            const uint4 b = pk_ld_volatile_v4(src + (size_t)r * P.tp_slot_stride + 16);
+                                            w[r] = make_uint4(a.x, a.z, b.x, b.z);
+                                            oldest = min(oldest, min(min((int)a.y - E, (int)a.w - E), min((int)b.y - E, (int)b.w - E)));
+                                        }
+                                    }
+                                    if (oldest >= 0) break;
+                                    if (clock64() - t0 > P.tp_wait) {  // (a rank that stopped in the middle of its pushes)
+                                        ready = false;
+                                        if (P.err) atomicCAS(P.err, 0, TP_TIMEOUT_CODE);
+                                        break;
+                                    }
+                                    __nanosleep(32);
+                                }
+                            } else if (tp_ok) {
 #pragma unroll
                                 for (int r = 0; r < 8; ++r)
                                     if (r < P.tp_n) w[r] = pk_ld_cg_v4(P.tp_slots + (size_t)r * P.tp_slot_stride + off);
+                            }
+                            if (ready) {
                                 float sm[8];
 #pragma unroll
                                 for (int q = 0; q < 8; ++q) sm[q] = 0.0f;
@@ -464,6 +514,8 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         chain_wait();
+        // the epoch an in-band push writes into its words (the pass number is in memory before any kernel of the pass starts)
+        const int tp_epoch = (tp_push && tp_inband) ? *reinterpret_cast<const volatile int*>(P.tp_pass) * P.tp_n_sites + P.tp_site + 1 : 0;
         // Row scale of a fused RMSNorm: X is the un-normalised residual stream and the norm's gain is folded into the packed
         // weights, so y[t, :] = (W' . x[t]) / sqrt(mean(x[t]^2) + eps); the mean comes from the per-tile sums of squares that
         // the kernel which wrote x left behind (added in tile order).
@@ -814,8 +866,15 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                                 uint2 o;
                                 o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
                                 if (tp_push) {
-                                    // this rank's block of every rank's exchange buffer (plain stores; peers over NVLink)
-                                    if (valid) {
+                                    // this rank's block of every rank's exchange buffer (peers over NVLink): plain stores, or two
+                                    // words {two bf16, epoch} per thread and token - the epoch in a word tells the reader that
+                                    // the word is there
+                                    if (valid && tp_inband) {
+                                        const size_t off = ((size_t)t * P.N + n) * 4;
+#pragma unroll
+                                        for (int r = 0; r < 8; ++r)
+                                            if (r < P.tp_n) pk_st_volatile_v4(P.tp_dst[r] + off, o.x, (uint32_t)tp_epoch, o.y, (uint32_t)tp_epoch);
+                                    } else if (valid) {
                                         const size_t off = ((size_t)t * P.N + n) * 2;
 #pragma unroll
                                         for (int r = 0; r < 8; ++r)
@@ -832,7 +891,7 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
                         }
                     }
                 }
-                if (do_fold && tp_push) {
+                if (do_fold && tp_push && !tp_inband) {
                     // The barrier orders every thread's slot stores before thread 0, which releases them (device scope) through
                     // the launch's counter.  The CTA that completes the launch has thereby acquired every other CTA's stores;
                     // ONE system-scope fence then orders all of them before the epoch it stores (relaxed) into every rank's
@@ -1107,6 +1166,7 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
     }
     const int cluster = linear_packed_cluster(a.N, a.K, paired, a.T);
     P.tp_mode = 0;
+    P.tp_inband = 0;
     if (tp_push || tp_reduce) {
         const TpFuse& f = *a.tp;
         if (tp_push && tp_reduce) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: a launch either pushes or reduces");
@@ -1115,6 +1175,9 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         if (a.T > TP_PUSH_MAX_T) JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: the fused exchange takes at most %d tokens (%d)", TP_PUSH_MAX_T, a.T);
         P.tp_n = f.n_ranks; P.tp_rank = f.rank; P.tp_site = f.site; P.tp_n_sites = f.n_sites; P.tp_pass = f.pass; P.tp_state = f.state;
         P.tp_wait = f.wait_limit;
+        if (f.inband && a.T > TP_INBAND_MAX_T)
+            JSM_FAIL(JSM_UNSUPPORTED, "linear_packed: in-band exchange words for at most %d tokens (%d)", TP_INBAND_MAX_T, a.T);
+        P.tp_inband = f.inband ? 1 : 0;
         for (int r = 0; r < 8; ++r) { P.tp_dst[r] = nullptr; P.tp_flag[r] = nullptr; }
         P.tp_slots = nullptr; P.tp_slot_stride = 0; P.tp_flags = nullptr; P.tp_h = nullptr; P.tp_ssq = nullptr; P.tp_expect = 0;
         if (tp_push) {
@@ -1177,10 +1240,10 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
         }
 #undef PK_LEAN
     }
-    if (bn == 16 && !with_cl && with_tp && !a.bias && !a.out_f32) {  // the decode step of a tensor-parallel rank
-        if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<16, false, 1, 5>(mx, mx2, P, grid, cluster, a.chained, st);  // (plain, nothing else: checked above)
-        if (paired) return launch_packed<16, false, 2, 4>(mx, mx2, P, grid, cluster, a.chained, st);
-        if (a.epilogue == LIN_NONE && !a.ssq_out) return launch_packed<16, false, 2, 2>(mx, mx2, P, grid, cluster, a.chained, st);
+    if (bn == 16 && !with_cl && with_tp && P.tp_inband && !a.bias && !a.out_f32) {  // the decode step of a tensor-parallel rank
+        if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<16, false, 4, 5>(mx, mx2, P, grid, cluster, a.chained, st);  // (plain, nothing else: checked above)
+        if (P.tp_mode == 2 && paired) return launch_packed<16, false, 5, 4>(mx, mx2, P, grid, cluster, a.chained, st);
+        if (P.tp_mode == 2 && a.epilogue == LIN_NONE && !a.ssq_out) return launch_packed<16, false, 5, 2>(mx, mx2, P, grid, cluster, a.chained, st);
     }
     switch (bn) {
         case 16: PK_GO_TP(16);
@@ -1353,6 +1416,7 @@ extern "C" jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int s
     f.n_ranks = size; f.rank = rank; f.pass = d_state; f.state = d_state + 1; f.site = site; f.n_sites = n_sites;
     f.wait_limit = tp_wait_limit_cycles();
     f.push = true;
+    f.inband = T <= TP_INBAND_MAX_T;
     const size_t off = tp_push_offset(which_buffer, max_tokens, N) + (size_t)rank * tp_slot_bytes(N);
     for (int r = 0; r < size; ++r) {
         if (!d_regions[r]) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_push: no region for rank %d", r);
@@ -1378,6 +1442,7 @@ extern "C" jsm_status jsm_tp_linear_reduce(void* d_region, int rank, int size, i
     f.n_ranks = size; f.rank = rank; f.pass = d_state; f.state = d_state + 1; f.site = site; f.n_sites = n_sites;
     f.wait_limit = tp_wait_limit_cycles();
     f.reduce = true;
+    f.inband = T <= TP_INBAND_MAX_T;
     f.slots = static_cast<const uint8_t*>(d_region) + tp_push_offset(which_buffer, max_tokens, d);
     f.slot_stride = tp_slot_bytes(d);
     f.flags = static_cast<const int*>(d_region) + tp_push_flag_word();

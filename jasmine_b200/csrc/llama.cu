@@ -84,6 +84,7 @@ struct jsm_model {
     float* best_val = nullptr;   // vocabulary-sharded lm_head: this rank's best logit per token
     int32_t* best_idx = nullptr;
     bool last_push = false;  // the last forward call exchanged by push (its final exchange is consumed by the logits projection)
+    bool last_inband = false;  // ... as words that carry the exchange's epoch (at most TP_INBAND_MAX_T tokens)
     jsm_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
     uint64_t weight_bytes = 0;
@@ -505,6 +506,7 @@ static TpFuse exchange_base(jsm_model* m, int site) {
     f.pass = m->tp_state; f.site = site; f.n_sites = 2 * m->c.n_layers + 1;  // two per layer and the arg-max exchange
     f.state = m->tp_state + 4;
     f.wait_limit = tp_wait_limit_cycles();
+    f.inband = m->last_inband;
     return f;
 }
 // The consumer side of a pushed exchange: the projection that reads rows [first, first + rows) of the residual stream
@@ -513,7 +515,7 @@ static TpFuse consume_exchange(jsm_model* m, int which, int site, float* stats, 
     TpFuse f = exchange_base(m, site);
     const int d = m->c.d_model;
     f.reduce = true;
-    f.slots = m->tp_region + tp_push_offset(which, m->max_tokens, d) + (size_t)first * d * sizeof(__nv_bfloat16);
+    f.slots = m->tp_region + tp_push_offset(which, m->max_tokens, d) + (size_t)first * d * (f.inband ? 4 : sizeof(__nv_bfloat16));
     f.slot_stride = tp_slot_bytes(d);
     f.flags = reinterpret_cast<const int*>(m->tp_region) + tp_push_flag_word();
     f.h = m->h + (size_t)first * d;
@@ -571,6 +573,7 @@ static jsm_status forward_tokens(jsm_model* m, const int32_t* d_ids, int T, bool
     const bool push = tp && m->tp_connected && T <= TP_PUSH_MAX_T && linear_packed_can_push(d, m->Hq_l * D, T) &&
                       linear_packed_can_push(d, m->ffn_l, T);
     m->last_push = push;
+    m->last_inband = push && T <= TP_INBAND_MAX_T;
     const bool stats = !tp || push;  // h carries row statistics instead of a normalised copy
     jsm_status s = JSM_OK;
     if (decode && stats && d % 8 == 0) {

@@ -32,7 +32,10 @@
 //           stores, off the critical path of the consumer - and leaves h and the tile's sums of squares behind; all CTAs
 //           then read h as their token operand with the RMSNorm applied as a row scale.
 // One NVLink traversal (store + flag) lies between the two projections instead of signal -> wait -> remote load, and no
-// kernel launch.  Region layout: [flags | buffer A | buffer B | push buffer 0: 8 slots | push buffer 1: 8 slots]; the
+// kernel launch.  Exchanges of at most TP_INBAND_MAX_T tokens (the decode step at small batches) drop the flag as well:
+// the slot holds 8-byte words {two bf16, epoch}, a word is written by one store, so its epoch says that it has arrived;
+// the producer then needs no counter of finished CTAs, no system-scope fence and no flag stores (its tail is that of a
+// plain projection), and the consumer's load that polls is the load that fetches (linear_bf16.cuh, TpFuse::inband).  Region layout: [flags | buffer A | buffer B | push buffer 0: 8 slots | push buffer 1: 8 slots]; the
 // push flags are the words TP_PUSH_FLAG_WORD.. of the flag block.  The same two-buffer argument holds: a rank pushes
 // into buffer 0 again only after it has consumed the exchange over buffer 1, which every peer pushed only after it had
 // finished reading buffer 0.

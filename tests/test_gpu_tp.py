@@ -96,8 +96,9 @@ def _rms_rows(h, eps):
                                         (3, 1, 256, 512, 256), (2, 64, 512, 1024, 384)])
 def test_fused_exchange_push_then_reduce(n, T, d, K, N2):
     """All "ranks" are regions of one device.  First every rank's producer projection runs (it stores its tiles into its
-    slot of every region and releases its flag), then every rank's consumer projection (it finds all flags set, adds the
-    slots to h and projects the normalised h): no kernel ever waits for another.  Three exchanges: buffers 0, 1, 0."""
+    slot of every region and releases its flag - or, at up to 16 tokens, tags every stored word with the exchange's
+    epoch), then every rank's consumer projection (it finds all flags set / all words of the epoch, adds the slots to h
+    and projects the normalised h): no kernel ever waits for another.  Three exchanges: buffers 0, 1, 0."""
     max_tokens = 64
     regions, ptrs = make_regions(n, max_tokens, d)
     states = [torch.zeros(80, dtype=torch.int32, device="cuda") for _ in range(n)]

@@ -216,10 +216,11 @@ __global__ void __launch_bounds__(PK_THREADS, 1)
     // out (wo, down); 4: gate-up pairs with the row scale, bf16 out.  The host picks the image from the arguments; a launch
     // pays for the size of its image, so the common launches get the smallest ones.
     // TPM: 0 = no tensor-parallel exchange in the image, 3 = push or reduce, with flags or in-band epochs, as the launch says,
-    // 4 = it pushes its outputs as in-band words, 5 = it reduces the ranks' in-band slots into its token operand first.
+    // 1 / 2 = it pushes its outputs / reduces the ranks' slots into its token operand first, with flags, 4 / 5 = the same
+    // with in-band epochs.
     // PRM 5: the pushing projection (plain tiles, bf16, nothing else).
-    const bool tp_push = TPM == 4 || (TPM == 3 && P.tp_mode == 1);
-    const bool tp_reduce = TPM == 5 || (TPM == 3 && P.tp_mode == 2);
+    const bool tp_push = TPM == 1 || TPM == 4 || (TPM == 3 && P.tp_mode == 1);
+    const bool tp_reduce = TPM == 2 || TPM == 5 || (TPM == 3 && P.tp_mode == 2);
     const bool tp_inband = BN == 16 && (TPM == 4 || TPM == 5 || (TPM == 3 && P.tp_inband != 0));  // (at most 16 tokens)
     constexpr bool FIX = PRM >= 2;
     const bool paired = PRM < 0 ? P.paired != 0 : (PRM == 1 || PRM == 4);
@@ -1239,6 +1240,22 @@ jsm_status linear_packed_launch(const PackedArgs& a, cudaStream_t st) {
             if (cluster > 1) PK_LEAN(64, true); else PK_LEAN(64, false);
         }
 #undef PK_LEAN
+    }
+    // 17 to 64 tokens of a tensor-parallel rank (flags): the pushing projection and the two reducing ones
+    if ((bn == 32 || bn == 64) && with_tp && !P.tp_inband && !a.bias && !a.out_f32) {
+#define PK_LEAN_TP(BN_, CL_)                                                                                                 \
+    do {                                                                                                                     \
+        if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<BN_, CL_, 1, 5>(mx, mx2, P, grid, cluster, a.chained, st);     \
+        if (P.tp_mode == 2 && paired) return launch_packed<BN_, CL_, 2, 4>(mx, mx2, P, grid, cluster, a.chained, st);        \
+        if (P.tp_mode == 2 && a.epilogue == LIN_NONE && !a.ssq_out)                                                          \
+            return launch_packed<BN_, CL_, 2, 2>(mx, mx2, P, grid, cluster, a.chained, st);                                  \
+    } while (0)
+        if (bn == 32) {
+            if (cluster > 1) PK_LEAN_TP(32, true); else PK_LEAN_TP(32, false);
+        } else {
+            if (cluster > 1) PK_LEAN_TP(64, true); else PK_LEAN_TP(64, false);
+        }
+#undef PK_LEAN_TP
     }
     if (bn == 16 && !with_cl && with_tp && P.tp_inband && !a.bias && !a.out_f32) {  // the decode step of a tensor-parallel rank
         if (P.tp_mode == 1 && !a.ssq_in) return launch_packed<16, false, 4, 5>(mx, mx2, P, grid, cluster, a.chained, st);  // (plain, nothing else: checked above)

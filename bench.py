@@ -332,14 +332,15 @@ def run_timeline(args):
         jb.check(jb.lib().jsm_upload(p, flags.data_ptr(), 192, jb.stream_ptr()))
         # exchanges of at most 16 tokens have no flags: their slots hold words {two bf16, epoch}.  The peers' slots of this
         # rank's two push buffers get zeros with a far-future epoch; this rank's own slots stay zero (its own kernels fill them)
-        d_model, slot = 4096, 64 * 4096 * 2
-        max_tokens = (nb.value - 1024 - 16 * slot) // (4 * d_model + 64)
+        d_model, slot = 4096, 16 * 4096 * 4
+        max_tokens = max(B, PROMPT)  # what the model sized its regions for (checked against the region's size)
+        assert jb.lib().jsm_tp_region_bytes(max_tokens, d_model) == nb.value, "exchange region: unexpected token capacity"
         words = torch.zeros(slot // 4, dtype=torch.int32)
         words[1::2] = 1 << 30
         words = words.pin_memory()
         for which in range(2):
             for r in range(1, tp):
-                off = 1024 + 4 * max_tokens * d_model + (which * 8 + r) * slot
+                off = jb.lib().jsm_tp_inband_slot_offset(which, r, max_tokens, d_model)
                 jb.check(jb.lib().jsm_upload(p.value + off, words.data_ptr(), slot, jb.stream_ptr()))
         torch.cuda.synchronize()
         jb.check(jb.lib().jsm_llama_tp_connect(m._h, ptrs))

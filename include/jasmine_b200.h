@@ -360,6 +360,10 @@ jsm_status jsm_llama_tp_connect(jsm_model* m, void* const* d_peer_regions);
  * keep their old h while a token whose CTA still saw the flag is updated: after JSM_TIMEOUT the step's result is invalid
  * as a whole.  The self-resetting counters of the projections stay consistent (no kernel leaves one half-counted). */
 size_t jsm_tp_region_bytes(int max_tokens, int d);
+/* Byte offset, inside a region, of the slot into which `rank` pushes the in-band words ({two bf16, epoch} per 8 bytes,
+ * 16 x d x 4 bytes per slot) of an exchange of at most 16 tokens over in-band buffer `which_buffer` (see
+ * jsm_tp_linear_push).  For tests and tools that stand in for a peer; 0 on invalid arguments. */
+size_t jsm_tp_inband_slot_offset(int which_buffer, int rank, int max_tokens, int d);
 jsm_status jsm_tp_set_wait_limit_ms(int ms);
 jsm_status jsm_tp_allreduce_add_norm(void* const* d_regions, int rank, int size, int which_buffer, int max_tokens,
                                      const int32_t* d_pass, int site, int n_sites, void* d_h, void* d_xn, float eps,

@@ -101,6 +101,7 @@ SYMBOLS = {
     "jsm_llama_tp_region": (_i, [_vp, C.POINTER(_vp), C.POINTER(_sz)]),
     "jsm_llama_tp_connect": (_i, [_vp, C.POINTER(_vp)]),
     "jsm_tp_region_bytes": (_sz, [_i, _i]),
+    "jsm_tp_inband_slot_offset": (_sz, [_i, _i, _i, _i]),
     "jsm_tp_set_wait_limit_ms": (_i, [_i]),
     "jsm_tp_allreduce_add_norm": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _f, _i, _i, _vp]),
     "jsm_tp_linear_push": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),

@@ -109,6 +109,8 @@ size_t tp_region_bytes(int max_tokens, int d);
 size_t tp_buffer_offset(int which, int max_tokens, int d);
 size_t tp_push_offset(int which, int max_tokens, int d);
 size_t tp_slot_bytes(int d);
+size_t tp_inband_offset(int which, int max_tokens, int d);
+size_t tp_inband_slot_bytes(int d);
 int tp_push_flag_word();
 long long tp_wait_limit_cycles();
 // whether a plain bf16 projection of this shape and token count can push its outputs (TpFuse::push)

@@ -1434,7 +1434,8 @@ extern "C" jsm_status jsm_tp_linear_push(void* const* d_regions, int rank, int s
     f.wait_limit = tp_wait_limit_cycles();
     f.push = true;
     f.inband = T <= TP_INBAND_MAX_T;
-    const size_t off = tp_push_offset(which_buffer, max_tokens, N) + (size_t)rank * tp_slot_bytes(N);
+    const size_t off = f.inband ? tp_inband_offset(which_buffer, max_tokens, N) + (size_t)rank * tp_inband_slot_bytes(N)
+                                : tp_push_offset(which_buffer, max_tokens, N) + (size_t)rank * tp_slot_bytes(N);
     for (int r = 0; r < size; ++r) {
         if (!d_regions[r]) JSM_FAIL(JSM_INVALID_ARG, "jsm_tp_linear_push: no region for rank %d", r);
         f.push_dst[r] = static_cast<uint8_t*>(d_regions[r]) + off;
@@ -1460,8 +1461,8 @@ extern "C" jsm_status jsm_tp_linear_reduce(void* d_region, int rank, int size, i
     f.wait_limit = tp_wait_limit_cycles();
     f.reduce = true;
     f.inband = T <= TP_INBAND_MAX_T;
-    f.slots = static_cast<const uint8_t*>(d_region) + tp_push_offset(which_buffer, max_tokens, d);
-    f.slot_stride = tp_slot_bytes(d);
+    f.slots = static_cast<const uint8_t*>(d_region) + (f.inband ? tp_inband_offset(which_buffer, max_tokens, d) : tp_push_offset(which_buffer, max_tokens, d));
+    f.slot_stride = f.inband ? tp_inband_slot_bytes(d) : tp_slot_bytes(d);
     f.flags = static_cast<const int*>(d_region) + tp_push_flag_word();
     f.h = d_h; f.ssq = d_ssq;
     PackedArgs a;

@@ -515,8 +515,9 @@ static TpFuse consume_exchange(jsm_model* m, int which, int site, float* stats, 
     TpFuse f = exchange_base(m, site);
     const int d = m->c.d_model;
     f.reduce = true;
-    f.slots = m->tp_region + tp_push_offset(which, m->max_tokens, d) + (size_t)first * d * (f.inband ? 4 : sizeof(__nv_bfloat16));
-    f.slot_stride = tp_slot_bytes(d);
+    f.slots = f.inband ? m->tp_region + tp_inband_offset(which, m->max_tokens, d) + (size_t)first * d * 4  // (4 bytes per element)
+                       : m->tp_region + tp_push_offset(which, m->max_tokens, d) + (size_t)first * d * sizeof(__nv_bfloat16);
+    f.slot_stride = f.inband ? tp_inband_slot_bytes(d) : tp_slot_bytes(d);
     f.flags = reinterpret_cast<const int*>(m->tp_region) + tp_push_flag_word();
     f.h = m->h + (size_t)first * d;
     f.ssq = stats + first;
@@ -536,7 +537,8 @@ static jsm_status project_into_residual(jsm_model* m, const __nv_bfloat16* X, co
         // exchange's epoch; the projection that reads h next adds the slots to h in its prologue (consume_exchange)
         TpFuse f = exchange_base(m, site);
         f.push = true;
-        const size_t off = tp_push_offset(which, m->max_tokens, d) + (size_t)m->c.tp_rank * tp_slot_bytes(d);
+        const size_t off = f.inband ? tp_inband_offset(which, m->max_tokens, d) + (size_t)m->c.tp_rank * tp_inband_slot_bytes(d)
+                                    : tp_push_offset(which, m->max_tokens, d) + (size_t)m->c.tp_rank * tp_slot_bytes(d);
         for (int r = 0; r < m->c.tp_size; ++r) {
             f.push_dst[r] = static_cast<uint8_t*>(m->tp_regions[r]) + off;
             f.push_flag[r] = static_cast<int*>(m->tp_regions[r]) + tp_push_flag_word() + m->c.tp_rank;

@@ -35,10 +35,13 @@
 // kernel launch.  Exchanges of at most TP_INBAND_MAX_T tokens (the decode step at small batches) drop the flag as well:
 // the slot holds 8-byte words {two bf16, epoch}, a word is written by one store, so its epoch says that it has arrived;
 // the producer then needs no counter of finished CTAs, no system-scope fence and no flag stores (its tail is that of a
-// plain projection), and the consumer's load that polls is the load that fetches (linear_bf16.cuh, TpFuse::inband).  Region layout: [flags | buffer A | buffer B | push buffer 0: 8 slots | push buffer 1: 8 slots]; the
-// push flags are the words TP_PUSH_FLAG_WORD.. of the flag block.  The same two-buffer argument holds: a rank pushes
-// into buffer 0 again only after it has consumed the exchange over buffer 1, which every peer pushed only after it had
-// finished reading buffer 0.
+// plain projection), and the consumer's load that polls is the load that fetches (linear_bf16.cuh, TpFuse::inband).  The
+// in-band words have buffers of their own: whatever a reader finds there is zero or a word of an earlier in-band exchange
+// (an older epoch), never plain data that could pass for an epoch.
+// Region layout: [flags | buffer A | buffer B | push buffer 0: 8 slots | push buffer 1: 8 slots | in-band buffer 0: 8 slots
+// | in-band buffer 1: 8 slots | arg-max slots]; the push flags are the words TP_PUSH_FLAG_WORD.. of the flag block.  The
+// same two-buffer argument holds: a rank pushes into buffer 0 again only after it has consumed the exchange over buffer
+// 1, which every peer pushed only after it had finished reading buffer 0.
 #include "tc_utils.cuh"
 #include "linear_bf16.cuh"
 #include <math.h>
@@ -186,8 +189,13 @@ size_t tp_push_offset(int which, int max_tokens, int d) {
 // The arg-max exchange of a vocabulary-sharded lm_head: every rank's (best logit, its index) per token, 8 slots of
 // max_tokens pairs behind the push buffers; flag words TP_ARGMAX_FLAG_WORD.. (one per source rank)
 constexpr int TP_ARGMAX_FLAG_WORD = 32;
+// in-band exchanges (at most TP_INBAND_MAX_T tokens): 4 bytes per element; slot 0 of in-band buffer `which`
+size_t tp_inband_slot_bytes(int d) { return (size_t)TP_INBAND_MAX_T * d * 4; }
+size_t tp_inband_offset(int which, int max_tokens, int d) {
+    return tp_push_offset(0, max_tokens, d) + 2 * (size_t)TP_MAX_RANKS * tp_slot_bytes(d) + (size_t)(which & 1) * TP_MAX_RANKS * tp_inband_slot_bytes(d);
+}
 size_t tp_argmax_offset(int max_tokens, int d) {
-    const size_t off = TP_FLAG_BYTES + 2 * (size_t)max_tokens * d * sizeof(__nv_bfloat16) + 2 * (size_t)TP_MAX_RANKS * tp_slot_bytes(d);
+    const size_t off = tp_inband_offset(0, max_tokens, d) + 2 * (size_t)TP_MAX_RANKS * tp_inband_slot_bytes(d);
     return (off + 255) & ~(size_t)255;
 }
 int tp_push_flag_word() { return TP_PUSH_FLAG_WORD; }
@@ -297,6 +305,11 @@ jsm_status tp_argmax_exchange_launch(void* const* regions, int rank, int size, i
 }  // namespace jsm
 
 using namespace jsm;
+
+extern "C" size_t jsm_tp_inband_slot_offset(int which_buffer, int rank, int max_tokens, int d) {
+    if (max_tokens <= 0 || d <= 0 || rank < 0 || rank >= TP_MAX_RANKS) return 0;
+    return tp_inband_offset(which_buffer, max_tokens, d) + (size_t)rank * tp_inband_slot_bytes(d);
+}
 
 extern "C" size_t jsm_tp_region_bytes(int max_tokens, int d) {
     if (max_tokens <= 0 || d <= 0) return 0;

@@ -146,7 +146,13 @@ def test_fused_exchange_gives_up_when_a_peer_never_pushes():
     h stays as it was, the host reads JSM_TIMEOUT and the device still answers."""
     n, T, d, N2, max_tokens = 2, 4, 512, 256, 64
     regions, ptrs = make_regions(n, max_tokens, d)
-    state = torch.zeros(80, dtype=torch.int32, device="cuda")   # epoch 1 is expected; no flag was ever released
+    # 4 tokens: the exchange would arrive as words that carry their epoch.  Those words have buffers of their own, so what
+    # larger (plain bf16) exchanges left in the push buffers - here: bytes that would read as a far-future epoch - can never
+    # pass for an arrived word
+    inband0 = jb.lib().jsm_tp_inband_slot_offset(0, 0, max_tokens, d)
+    assert 1024 < inband0 < regions[0].numel()
+    regions[0][1024:inband0] = 0x3f
+    state = torch.zeros(80, dtype=torch.int32, device="cuda")   # epoch 1 is expected; nothing was ever pushed
     W2p = jb.linear_pack(dev(cases.normal((N2, d), 950, 0, 0.05), torch.bfloat16), N2)
     h = dev(cases.normal((T, d), 951, 0), torch.bfloat16)
     before = h.clone()
